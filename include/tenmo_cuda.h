@@ -1,0 +1,170 @@
+/*
+ * libtenmo_cuda.so -- C ABI of the B200 (sm_100a) implementation of tenmo's dense fp32 training path.
+ *
+ * This is the boundary tenmo's Mojo host binds with OwnedDLHandle / get_function, the same way
+ * tenmo/blashandle.mojo:108-251 binds cblas_sgemm.  Each entry point names the reference interface
+ * it replaces (paths relative to the reference root).
+ *
+ * Conventions
+ *   - Every data pointer is a DEVICE pointer owned by the caller (tenmo's DeviceBuffer,
+ *     device.mojo:325-328).  Outputs are pre-allocated by the caller.  The library owns only its
+ *     context, an internal workspace and (optionally) an NCCL communicator.
+ *   - Shapes, strides and offsets are in ELEMENTS (int64), row-major, like NDBuffer
+ *     (ndbuffer.mojo:66-74).  Data is fp32; class labels are int64 (mnemonics.mojo:63) or int32.
+ *   - Calls are asynchronous on the context's stream (tenmo_cuda_set_stream) unless stated.
+ *   - Return value: TENMO_OK (0) or a negative tenmo_status; tenmo_cuda_last_error gives the message.
+ *     Bad shapes / strides / alignment are rejected on the host before any launch.  Nothing aborts.
+ *   - There is no CPU fallback: a layout the tensor-core kernel cannot take runs on the SIMT GPU kernel.
+ *   - One host thread per context.
+ */
+#ifndef TENMO_CUDA_H
+#define TENMO_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tenmo_ctx tenmo_ctx;
+
+typedef enum {
+    TENMO_OK = 0,
+    TENMO_ERR_INVALID = -1,      /* bad argument: shape, stride, null pointer, enum out of range */
+    TENMO_ERR_CUDA = -2,         /* a CUDA runtime/driver call failed; message has the CUDA error string */
+    TENMO_ERR_UNSUPPORTED = -3,  /* valid request this build cannot serve (e.g. algo forced on a bad layout) */
+    TENMO_ERR_NOMEM = -4,        /* workspace allocation failed */
+    TENMO_ERR_NCCL = -5,         /* NCCL load / call failed */
+    TENMO_ERR_TIMEOUT = -6,      /* a bounded device-side wait gave up; see tenmo_cuda_check_device_status */
+    TENMO_ERR_STATE = -7         /* call made in the wrong state (e.g. dp call before tenmo_dp_init) */
+} tenmo_status;
+
+/* ---- context ------------------------------------------------------------------------------------
+ * Replaces tenmo's GPU/DeviceContext wrapper (device.mojo:87-90) for the purposes of this path. */
+int tenmo_cuda_init(int device, tenmo_ctx** out);
+void tenmo_cuda_destroy(tenmo_ctx* ctx);
+const char* tenmo_cuda_last_error(tenmo_ctx* ctx); /* ctx may be NULL: returns the last init error */
+const char* tenmo_cuda_version(void);
+/* Stream handle of the caller's DeviceContext (a cudaStream_t); NULL selects the context's own stream. */
+int tenmo_cuda_set_stream(tenmo_ctx* ctx, void* cuda_stream);
+/* DeviceContext.synchronize (the `sync=True` argument of every launcher, matmul_kernel.mojo:277). */
+int tenmo_cuda_synchronize(tenmo_ctx* ctx);
+int tenmo_cuda_device_info(tenmo_ctx* ctx, int* sm_count, int* cc_major, int* cc_minor, int* sm_clock_khz);
+/* Synchronises, then reads the device status word kernels set when a bounded wait (mbarrier) gave up.
+ * Returns TENMO_OK or TENMO_ERR_TIMEOUT; the word is cleared. */
+int tenmo_cuda_check_device_status(tenmo_ctx* ctx);
+/* Counts kernel launches made through this context since the last reset (bookkeeping for benchmarks). */
+int64_t tenmo_cuda_launch_count(tenmo_ctx* ctx, int reset);
+
+/* ---- GEMM ---------------------------------------------------------------------------------------
+ * A strided, possibly batched matrix operand: element (b..., i, j) lives at
+ *   ptr[offset + sum_d coord_d * batch_stride[d] + i*row_stride + j*col_stride].
+ * Batch dims are right-aligned and broadcast NumPy-style; an operand's batch stride is applied only
+ * where its own batch dim is > 1 (matmul_cpu.mojo:706-724). */
+#define TENMO_MAX_BATCH_RANK 6 /* max_rank 8 (mnemonics.mojo:45) minus the two matrix dims */
+typedef struct {
+    const float* ptr;
+    int64_t offset;
+    int64_t row_stride, col_stride;
+    int32_t batch_rank;
+    int64_t batch_shape[TENMO_MAX_BATCH_RANK];
+    int64_t batch_stride[TENMO_MAX_BATCH_RANK];
+} tenmo_mat;
+
+enum { TENMO_ALGO_AUTO = -1, TENMO_ALGO_SIMT_FP32 = 0, TENMO_ALGO_TC_3XTF32 = 1 };
+enum { TENMO_ACT_NONE = 0, TENMO_ACT_RELU = 1, TENMO_ACT_SIGMOID = 2 };
+
+/* C[b] = act( A[b] . B[b] + bias ) (+ C[b] when beta == 1);  A is (M,K), B is (K,N), C is the
+ * contiguous (total_batch, M, N) output.
+ * Replaces NDBuffer.matmul_2d / matmul_nd GPU branch (ndbuffer.mojo:2404-2501) and
+ * MatmulNdGpu.launch (kernels/matmul_kernel.mojo:128-283); with transposed stride views as operands it
+ * is also the two backward GEMMs of Matmul2dBackward / MatmulNdBackward (matmul.mojo:24-54,101-137).
+ *   algo   TENMO_ALGO_SIMT_FP32: strict fp32, every output one k-ascending fmaf chain (bit-identical to
+ *          matmul_cpu.mojo paths 1a/1b).  TENMO_ALGO_TC_3XTF32: tcgen05 tensor cores, three TF32 products
+ *          per fp32 product.  TENMO_ALGO_AUTO picks the tensor-core kernel when the layout allows
+ *          (unit inner stride on one axis of each operand, 16-byte aligned rows) and the problem is
+ *          large enough, else SIMT.
+ *   beta   0 or 1.  beta == 1 is the Gradbox accumulate `grad += incoming` (ancestry.mojo:83-84,
+ *          kernels/binary_inplace_ops_kernel.mojo) folded into the epilogue.
+ *   bias   N floats or NULL: the Linear bias add (net.mojo:194-203, binary_ops_kernel.mojo:408-458).
+ *   act    applied after the bias: ReLU (relu.mojo:97-141) or Sigmoid (buffers.mojo:1147-1152).
+ *   aux    optional, same shape as C: the fp32 0/1 ReLU mask (x > 0) that relu.mojo stores for backward.
+ *   colsum optional, N floats, 2-D only: colsum[n] (+)= sum_k B[k,n], i.e. the bias gradient when this
+ *          call is dW = X^T . dY (broadcast.mojo:66-88); follows beta. */
+int tenmo_gemm_f32(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A,
+                   const tenmo_mat* B, float* C, float beta, const float* bias, int act, float* aux,
+                   float* colsum);
+/* Which kernel the last tenmo_gemm_f32 call on this context ran: TENMO_ALGO_SIMT_FP32 or _TC_3XTF32. */
+int tenmo_gemm_last_algo(tenmo_ctx* ctx);
+
+/* ---- elementwise neighbours of the GEMM (un-fused forms, for a host that calls op by op) ---------- */
+/* out[m,n] = x[m,n] + bias[n]; Adder.forward bias case (addition.mojo:71-112,
+ * binary_ops_kernel.mojo:778-807).  out may alias x. */
+int tenmo_add_bias_f32(tenmo_ctx* ctx, const float* x, const float* bias, float* out, int64_t M, int64_t N);
+/* out[i] += in[i]; Gradbox accumulate (gradbox.mojo:1358-1364, ndbuffer.mojo:1714-1719). */
+int tenmo_add_inplace_f32(tenmo_ctx* ctx, float* out, const float* in, int64_t n);
+/* x[i] = value; NDBuffer.fill used by zero_grad (optim.mojo:546-581, device.mojo:215-227). */
+int tenmo_fill_f32(tenmo_ctx* ctx, float* x, float value, int64_t n);
+/* ReLU.forward: out = max(x,0), mask = x>0 ? 1 : 0 (relu.mojo:50-95, unary_ops_kernel.mojo:220-298).
+ * mask may be NULL. */
+int tenmo_relu_fwd_f32(tenmo_ctx* ctx, const float* x, float* out, float* mask, int64_t n);
+/* ReLUBackward: dx = g * mask, (+= when beta == 1) (relu.mojo:19-46). */
+int tenmo_relu_bwd_f32(tenmo_ctx* ctx, const float* g, const float* mask, float* dx, float beta, int64_t n);
+/* Sigmoid.forward y = 1/(1+exp(-x)) (sigmoid.mojo:32-53, unary_ops_kernel.mojo:146-218). */
+int tenmo_sigmoid_fwd_f32(tenmo_ctx* ctx, const float* x, float* y, int64_t n);
+/* SigmoidBackward dx = g*y*(1-y) (sigmoid.mojo:9-29, binary_ops_kernel.mojo:29-68). */
+int tenmo_sigmoid_bwd_f32(tenmo_ctx* ctx, const float* g, const float* y, float* dx, float beta, int64_t n);
+
+/* ---- reductions ---------------------------------------------------------------------------------
+ * out[n] = sum_m x[m*ldx + n] (+ out[n] when beta == 1).  The bias gradient
+ * (broadcast.mojo:66-88 -> sum_mean_reduction.mojo:37-158, kernels/reduction_kernel.mojo:136-214) and,
+ * with M = leading batch and N = the rest, sum_over_broadcasted_axes (sum_mean_reduction.mojo:184-211). */
+int tenmo_colsum_f32(tenmo_ctx* ctx, const float* x, int64_t M, int64_t N, int64_t ldx, float* out, float beta);
+
+/* ---- softmax cross-entropy, class-index targets ---------------------------------------------------
+ * reduction: 0 mean, 1 sum, 2 none (shared/__init__.mojo:4-40).
+ * Forward (crossentropy.mojo:285-432, kernels/crossentropy_fused_kernel.mojo:39-160): per row max,
+ * exp, sum, loss; softmax_out (M,C) is kept for backward (may be NULL).  loss_dev receives 1 float
+ * (mean/sum) or M floats (none); valid_count_dev 1 int32 (rows whose label != ignore_index).
+ * Labels outside [0,C) other than ignore_index are a caller error (the host validates them,
+ * crossentropy.mojo:114-134); such a row contributes nothing and sets the device status word. */
+int tenmo_ce_fwd_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, const void* labels,
+                     int label_is_i64, int64_t M, int64_t C, int64_t ignore_index, float label_smoothing,
+                     int reduction, float* softmax_out, float* loss_dev, int32_t* valid_count_dev);
+/* Backward (crossentropy.mojo:664-823, crossentropy_fused_kernel.mojo:192-275):
+ * dlogits = (softmax - (1-ls)*onehot - ls/C) * valid * upstream / (mean ? valid_count : 1)
+ * (+= when beta == 1).  upstream_dev: 1 float (mean/sum) or M floats (none); NULL means 1.0. */
+int tenmo_ce_bwd_f32(tenmo_ctx* ctx, const float* softmax, const void* labels, int label_is_i64, int64_t M,
+                     int64_t C, int64_t ignore_index, float label_smoothing, int reduction,
+                     const float* upstream_dev, const int32_t* valid_count_dev, float* dlogits, float beta);
+
+/* ---- optimiser ----------------------------------------------------------------------------------
+ * SGD.step dense path for n_tensors parameters in ONE launch (optim.mojo:405-543,
+ * kernels/sgd_kernel.mojo:7-128):  g' = g*grad_scale; if wd>0: g' += p*wd;
+ * momentum>0: v = momentum*v + g'; p -= lr*v;   momentum==0: p -= lr*g'.
+ * p, g, v are HOST arrays of n_tensors device pointers (v may be NULL when momentum == 0). */
+int tenmo_sgd_step_f32(tenmo_ctx* ctx, int n_tensors, float* const* p, const float* const* g, float* const* v,
+                       const int64_t* numel, float lr, float momentum, float weight_decay, float grad_scale);
+
+/* ---- accuracy -----------------------------------------------------------------------------------
+ * Accuracy.compute (accuracy.mojo:7-85, kernels/accuracy_kernel.mojo:9-84): rows whose first-index
+ * argmax (strict >) equals the label.  Works for any M.  correct_dev: 1 int64 on the device, overwritten.
+ * If correct_host != NULL the call synchronises and copies the count there. */
+int tenmo_accuracy_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, const void* labels,
+                       int label_is_i64, int64_t M, int64_t C, int64_t* correct_dev, int64_t* correct_host);
+
+/* ---- data parallel (no counterpart in the reference: README.md:472-473 lists it as future work) ----
+ * One process per GPU.  Rank 0 obtains an id with tenmo_dp_get_unique_id and shares it out of band;
+ * every rank then calls tenmo_dp_init.  tenmo_dp_allreduce_sum_f32 sums `count` floats in place over
+ * all ranks on the context's stream (NCCL over NVLink / NVSwitch). */
+#define TENMO_DP_ID_BYTES 128
+int tenmo_dp_get_unique_id(tenmo_ctx* ctx, void* id_out, size_t id_bytes);
+int tenmo_dp_init(tenmo_ctx* ctx, int rank, int world, const void* id, size_t id_bytes);
+int tenmo_dp_allreduce_sum_f32(tenmo_ctx* ctx, float* buf, int64_t count);
+int tenmo_dp_finalize(tenmo_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TENMO_CUDA_H */

@@ -1,0 +1,299 @@
+// Softmax cross-entropy with class-index targets: fused forward and backward.
+//
+// Forward (restates crossentropy.mojo:285-432): per row  max -> e = exp(x - max), sum -> loss ->
+// softmax = e * (1/sum).  One warp owns a row; a row of up to 1024 classes is read from HBM once and
+// kept in registers (32 values per lane), so the algorithmic traffic of 4*M*C read + 4*M*C written is
+// also the real traffic.  Rows with few classes (C <= 32) are handled by one thread per row in
+// ascending class order, which reproduces the reference's sequential sum exactly.
+// The scalar loss is produced on the device: per-row losses go to a scratch row, and the last CTA to
+// finish (ticket counter) adds them in row order and divides by the valid count, so there is no host
+// read-back between forward and backward (the reference synchronises and reads two scalars back,
+// kernels/crossentropy_fused_kernel.mojo:359-375).
+// Roofline: HBM; forward 8*M*C + 8*M bytes, backward 8*M*C + 8*M bytes.
+#include "common.cuh"
+
+namespace {
+
+constexpr int CE_THREADS = 256;
+constexpr int CE_WARPS = CE_THREADS / 32;
+constexpr int CE_REG = 32;  // cached classes per lane
+
+struct CeFwdArgs {
+    const float* logits;
+    int64_t ld;
+    const void* labels;
+    int label_is_i64;
+    int64_t M, C;
+    int64_t ignore_index;
+    float ls;
+    int reduction;
+    float* softmax;
+    float* loss;          // 1 float (mean/sum) or M floats (none)
+    int32_t* valid_count;
+    float* row_loss;      // scratch, M floats (mean/sum only)
+    unsigned int* ticket; // one counter, zero between calls
+    uint32_t* status;
+};
+
+__device__ __forceinline__ int64_t load_label(const void* labels, int is_i64, int64_t row) {
+    return is_i64 ? reinterpret_cast<const int64_t*>(labels)[row] : (int64_t) reinterpret_cast<const int32_t*>(labels)[row];
+}
+
+// loss of one row from its statistics (crossentropy.mojo:368-389)
+__device__ __forceinline__ float row_loss_from_stats(const CeFwdArgs& p, int64_t row, float mx, float sum_exp,
+                                                     float sum_logits, bool* valid) {
+    const int64_t t = load_label(p.labels, p.label_is_i64, row);
+    *valid = false;
+    if (t == p.ignore_index) return 0.f;
+    if (t < 0 || t >= p.C) {
+        atomicOr(p.status, TENMO_DEV_BAD_LABEL);
+        return 0.f;
+    }
+    *valid = true;
+    const float lse = logf(fmaxf(sum_exp, 1e-7f));
+    const float logit_t = __ldg(p.logits + row * p.ld + t);
+    float loss = -((logit_t - mx) - lse);
+    if (p.ls > 0.f) {
+        const float inv_c = 1.f / (float)p.C;
+        const float mean_lsm = __fmul_rn(sum_logits, inv_c) - mx - lse;
+        loss = __fmul_rn(1.f - p.ls, loss) - __fmul_rn(p.ls, mean_lsm);
+    }
+    return loss;
+}
+
+// Final reduction by the last CTA: ascending row order for small M (matches the reference's
+// sequential `scalar_loss += loss`), fixed-shape tree otherwise.
+__device__ void ce_finalize(const CeFwdArgs& p, float* red_smem) {
+    const int tid = threadIdx.x;
+    if (p.M <= 2048) {
+        if (tid == 0) {
+            float s = 0.f;
+            int cnt = 0;
+            for (int64_t r = 0; r < p.M; ++r) {
+                if (p.reduction != 2) s += __ldcg(p.row_loss + r);
+                cnt += load_label(p.labels, p.label_is_i64, r) != p.ignore_index ? 1 : 0;
+            }
+            if (p.reduction == 0 && cnt > 0) s = s / (float)cnt;
+            if (p.reduction != 2) p.loss[0] = s;
+            *p.valid_count = cnt;
+        }
+        return;
+    }
+    float s = 0.f;
+    int cnt = 0;
+    for (int64_t r = tid; r < p.M; r += CE_THREADS) {
+        if (p.reduction != 2) s += __ldcg(p.row_loss + r);
+        cnt += load_label(p.labels, p.label_is_i64, r) != p.ignore_index ? 1 : 0;
+    }
+    s = tenmo_warp_sum(s);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    int* cnt_smem = reinterpret_cast<int*>(red_smem + CE_WARPS);
+    if ((tid & 31) == 0) { red_smem[tid >> 5] = s; cnt_smem[tid >> 5] = cnt; }
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        int c = 0;
+        for (int w = 0; w < CE_WARPS; ++w) { t += red_smem[w]; c += cnt_smem[w]; }
+        if (p.reduction == 0 && c > 0) t = t / (float)c;
+        if (p.reduction != 2) p.loss[0] = t;
+        *p.valid_count = c;
+    }
+}
+
+template <bool SMALL_C>
+__global__ void __launch_bounds__(CE_THREADS) ce_fwd_kernel(const CeFwdArgs p) {
+    __shared__ float red_smem[2 * CE_WARPS];
+    __shared__ bool is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (SMALL_C) {
+        // one thread per row, classes in ascending order
+        for (int64_t row = (int64_t)blockIdx.x * CE_THREADS + threadIdx.x; row < p.M;
+             row += (int64_t)gridDim.x * CE_THREADS) {
+            const float* x = p.logits + row * p.ld;
+            float v[32];
+            float mx = -3.4028234663852886e38f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+                if (c < p.C) { v[c] = __ldg(x + c); mx = fmaxf(mx, v[c]); }
+            float sum_exp = 0.f, sum_logits = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+                if (c < p.C) { sum_logits += v[c]; v[c] = expf(v[c] - mx); sum_exp += v[c]; }
+            bool valid;
+            const float loss = row_loss_from_stats(p, row, mx, sum_exp, sum_logits, &valid);
+            if (p.reduction == 2) p.loss[row] = loss; else p.row_loss[row] = loss;
+            if (p.softmax) {
+                const float inv = 1.f / sum_exp;
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    if (c < p.C) p.softmax[row * p.C + c] = v[c] * inv;
+            }
+        }
+    } else {
+        const bool cached = p.C <= 32 * CE_REG;
+        for (int64_t row = (int64_t)blockIdx.x * CE_WARPS + warp; row < p.M; row += (int64_t)gridDim.x * CE_WARPS) {
+            const float* x = p.logits + row * p.ld;
+            float v[CE_REG];
+            float mx = -3.4028234663852886e38f;
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < CE_REG; ++i) {
+                    const int64_t c = lane + 32 * i;
+                    v[i] = c < p.C ? __ldg(x + c) : -3.4028234663852886e38f;
+                    mx = fmaxf(mx, v[i]);
+                }
+            } else {
+                for (int64_t c = lane; c < p.C; c += 32) mx = fmaxf(mx, __ldg(x + c));
+            }
+            mx = tenmo_warp_max(mx);
+            float sum_exp = 0.f, sum_logits = 0.f;
+            if (cached) {
+#pragma unroll
+                for (int i = 0; i < CE_REG; ++i) {
+                    const int64_t c = lane + 32 * i;
+                    if (c < p.C) { sum_logits += v[i]; v[i] = expf(v[i] - mx); sum_exp += v[i]; }
+                }
+            } else {
+                for (int64_t c = lane; c < p.C; c += 32) {
+                    const float xv = __ldg(x + c);
+                    sum_logits += xv;
+                    sum_exp += expf(xv - mx);
+                }
+            }
+            sum_exp = tenmo_warp_sum(sum_exp);
+            sum_logits = tenmo_warp_sum(sum_logits);
+            if (lane == 0) {
+                bool valid;
+                const float loss = row_loss_from_stats(p, row, mx, sum_exp, sum_logits, &valid);
+                if (p.reduction == 2) p.loss[row] = loss; else p.row_loss[row] = loss;
+            }
+            if (p.softmax) {
+                const float inv = 1.f / sum_exp;
+                float* sm = p.softmax + row * p.C;
+                if (cached) {
+#pragma unroll
+                    for (int i = 0; i < CE_REG; ++i) {
+                        const int64_t c = lane + 32 * i;
+                        if (c < p.C) sm[c] = v[i] * inv;
+                    }
+                } else {
+                    for (int64_t c = lane; c < p.C; c += 32) sm[c] = expf(__ldg(x + c) - mx) * inv;
+                }
+            }
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(p.ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    ce_finalize(p, red_smem);
+    if (threadIdx.x == 0) *p.ticket = 0;
+}
+
+struct CeBwdArgs {
+    const float* softmax;
+    const void* labels;
+    int label_is_i64;
+    int64_t M, C;
+    int64_t ignore_index;
+    float ls;
+    int reduction;
+    const float* upstream;
+    const int32_t* valid_count;
+    float* dlogits;
+    float beta;
+};
+
+// dlogits = ((softmax - (1-ls)*onehot) - ls/C) * valid * (upstream / scale)   (crossentropy.mojo:742-766,473-481)
+__global__ void __launch_bounds__(CE_THREADS) ce_bwd_kernel(const CeBwdArgs p) {
+    const int64_t total = p.M * p.C;
+    float scale_mul = 1.f;
+    if (p.reduction != 2) {
+        const float ug = p.upstream ? __ldg(p.upstream) : 1.f;
+        const int vc = p.valid_count ? *p.valid_count : 0;
+        const float scale = (p.reduction == 0 && vc > 0) ? (float)vc : 1.f;
+        scale_mul = ug / scale;
+    }
+    const float ls_uniform = p.ls / (float)p.C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / p.C, c = i - row * p.C;
+        const int64_t t = load_label(p.labels, p.label_is_i64, row);
+        const bool ignored = t == p.ignore_index;
+        const float onehot = (!ignored && t == c) ? 1.f : 0.f;
+        float g = __ldg(p.softmax + i);
+        if (p.ls > 0.f) g = (g - __fmul_rn(onehot, 1.f - p.ls)) - ls_uniform;
+        else g = g - onehot;
+        g = g * (ignored ? 0.f : 1.f);
+        const float m = p.reduction == 2 ? (p.upstream ? __ldg(p.upstream + row) : 1.f) : scale_mul;
+        g = __fmul_rn(g, m);
+        p.dlogits[i] = p.beta != 0.f ? p.dlogits[i] + g : g;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int tenmo_ce_fwd_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, const void* labels, int label_is_i64,
+                     int64_t M, int64_t C, int64_t ignore_index, float label_smoothing, int reduction,
+                     float* softmax_out, float* loss_dev, int32_t* valid_count_dev) {
+    TENMO_CHECK_CTX(ctx);
+    if (M < 0 || C <= 0) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_fwd: bad shape (M=%lld, C=%lld)", (long long)M, (long long)C);
+    if (reduction < 0 || reduction > 2) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_fwd: reduction must be 0 (mean), 1 (sum) or 2 (none)");
+    if (label_smoothing < 0.f || label_smoothing > 1.f) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_fwd: label_smoothing outside [0,1]");
+    if (!loss_dev || !valid_count_dev || (M > 0 && (!logits || !labels)))
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_fwd: NULL pointer");
+    if (M > 0 && ld_logits < C) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_fwd: ld_logits < C");
+    TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (M == 0) {
+        if (reduction != 2) TENMO_CUDA_TRY(ctx, cudaMemsetAsync(loss_dev, 0, sizeof(float), ctx->stream));
+        TENMO_CUDA_TRY(ctx, cudaMemsetAsync(valid_count_dev, 0, sizeof(int32_t), ctx->stream));
+        return TENMO_OK;
+    }
+    CeFwdArgs p;
+    p.logits = logits; p.ld = ld_logits; p.labels = labels; p.label_is_i64 = label_is_i64;
+    p.M = M; p.C = C; p.ignore_index = ignore_index; p.ls = label_smoothing; p.reduction = reduction;
+    p.softmax = softmax_out; p.loss = loss_dev; p.valid_count = valid_count_dev;
+    p.row_loss = nullptr;
+    if (reduction != 2) {
+        void* ws = nullptr;
+        int st = tenmo_workspace(ctx, (size_t)M * sizeof(float), &ws);
+        if (st != TENMO_OK) return st;
+        p.row_loss = static_cast<float*>(ws);
+    }
+    p.ticket = reinterpret_cast<unsigned int*>(ctx->dev_status + 8);
+    p.status = ctx->dev_status;
+    if (C <= 32) {
+        const int grid = tenmo_stream_grid(ctx, M, CE_THREADS, 4);
+        ce_fwd_kernel<true><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
+    } else {
+        const int grid = tenmo_stream_grid(ctx, M, CE_WARPS, 8);
+        ce_fwd_kernel<false><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
+    }
+    TENMO_LAUNCH_CHECK(ctx, "ce_fwd_kernel");
+    return TENMO_OK;
+}
+
+int tenmo_ce_bwd_f32(tenmo_ctx* ctx, const float* softmax, const void* labels, int label_is_i64, int64_t M, int64_t C,
+                     int64_t ignore_index, float label_smoothing, int reduction, const float* upstream_dev,
+                     const int32_t* valid_count_dev, float* dlogits, float beta) {
+    TENMO_CHECK_CTX(ctx);
+    if (M < 0 || C <= 0) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_bwd: bad shape");
+    if (reduction < 0 || reduction > 2) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_bwd: reduction must be 0, 1 or 2");
+    if (beta != 0.f && beta != 1.f) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_bwd: beta must be 0 or 1");
+    if (M == 0) return TENMO_OK;
+    if (!softmax || !labels || !dlogits) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_bwd: NULL pointer");
+    if (reduction == 0 && !valid_count_dev) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_bwd: mean reduction needs valid_count_dev");
+    CeBwdArgs p{softmax, labels, label_is_i64, M, C, ignore_index, label_smoothing, reduction, upstream_dev,
+                valid_count_dev, dlogits, beta};
+    TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const int grid = tenmo_stream_grid(ctx, M * C, CE_THREADS * 4, 8);
+    ce_bwd_kernel<<<grid, CE_THREADS, 0, ctx->stream>>>(p);
+    TENMO_LAUNCH_CHECK(ctx, "ce_bwd_kernel");
+    return TENMO_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,90 @@
+// Shared declarations of libtenmo_cuda: the context object, error plumbing and small device helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/tenmo_cuda.h"
+
+// Device status word bits (tenmo_cuda_check_device_status).
+#define TENMO_DEV_TIMEOUT 1u    // a bounded mbarrier / flag wait ran out of iterations
+#define TENMO_DEV_BAD_LABEL 2u  // cross-entropy saw a label outside [0, C) that is not ignore_index
+
+struct tenmo_ctx {
+    int device = 0;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    int sm_clock_khz = 0;
+    size_t smem_optin = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    char err[512] = {0};
+    int64_t launches = 0;
+    int last_gemm_algo = -1;
+    // workspace (grown on demand, never shrunk): lo planes for the 3xTF32 kernel, reduction partials
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    // small fixed device scratch: [0] status word, [8..15] cross-entropy tickets/accumulators
+    uint32_t* dev_status = nullptr;
+    // ticket counters of the split column-sum kernel: zero between calls (the last CTA resets its own)
+    unsigned int* tickets = nullptr;
+    int tickets_cap = 0;
+    // multi-tensor SGD descriptor staging (pinned host + device)
+    void* sgd_desc_host = nullptr;
+    void* sgd_desc_dev = nullptr;
+    size_t sgd_desc_bytes = 0;
+    // tcgen05 GEMM state (tensor-map encoder entry point, opt-in smem set)
+    void* encode_tiled = nullptr;
+    bool tc_ready = false;
+    // NCCL
+    void* nccl_lib = nullptr;
+    void* nccl_comm = nullptr;
+    int dp_rank = 0, dp_world = 1;
+};
+
+int tenmo_set_error(tenmo_ctx* ctx, int status, const char* fmt, ...);
+int tenmo_workspace(tenmo_ctx* ctx, size_t bytes, void** out);
+
+#define TENMO_CHECK_CTX(ctx)             \
+    do {                                 \
+        if (!(ctx)) return TENMO_ERR_INVALID; \
+    } while (0)
+
+#define TENMO_CUDA_TRY(ctx, expr)                                                                  \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return tenmo_set_error((ctx), TENMO_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+// Every launch goes through this so the context can count launches and surface launch errors.
+#define TENMO_LAUNCH_CHECK(ctx, name)                                                              \
+    do {                                                                                           \
+        (ctx)->launches++;                                                                         \
+        cudaError_t _e = cudaGetLastError();                                                       \
+        if (_e != cudaSuccess)                                                                     \
+            return tenmo_set_error((ctx), TENMO_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \
+    } while (0)
+
+// Grid size for grid-stride, bandwidth-bound kernels: a multiple of the SM count.
+static inline int tenmo_stream_grid(const tenmo_ctx* ctx, int64_t work_items, int items_per_block, int ctas_per_sm) {
+    int64_t want = (work_items + items_per_block - 1) / items_per_block;
+    int64_t cap = (int64_t)ctx->sm_count * ctas_per_sm;
+    if (want < 1) want = 1;
+    return (int)(want < cap ? want : cap);
+}
+
+__device__ __forceinline__ float tenmo_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float tenmo_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}

@@ -1,0 +1,93 @@
+// tenmo_gemm_f32: argument validation, batch broadcasting and kernel selection.
+#include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+
+namespace {
+
+int build_batch(tenmo_ctx* ctx, const tenmo_mat* A, const tenmo_mat* B, TenmoBatch* out, int64_t* total) {
+    const int ra = A->batch_rank, rb = B->batch_rank;
+    if (ra < 0 || rb < 0 || ra > TENMO_MAX_BATCH_RANK || rb > TENMO_MAX_BATCH_RANK)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: batch rank out of range (A %d, B %d, max %d)", ra, rb,
+                               TENMO_MAX_BATCH_RANK);
+    const int r = ra > rb ? ra : rb;
+    out->rank = r;
+    int64_t t = 1;
+    for (int d = 0; d < r; ++d) {
+        const int ad = d - (r - ra), bd = d - (r - rb);
+        const int64_t sa = ad >= 0 ? A->batch_shape[ad] : 1;
+        const int64_t sb = bd >= 0 ? B->batch_shape[bd] : 1;
+        if (sa < 0 || sb < 0 || (sa != sb && sa != 1 && sb != 1))
+            return tenmo_set_error(ctx, TENMO_ERR_INVALID,
+                                   "gemm: batch shapes not broadcastable at dim %d (%lld vs %lld)", d, (long long)sa,
+                                   (long long)sb);
+        out->shape[d] = sa > sb ? sa : sb;
+        out->a_stride[d] = (ad >= 0 && sa > 1) ? A->batch_stride[ad] : 0;
+        out->b_stride[d] = (bd >= 0 && sb > 1) ? B->batch_stride[bd] : 0;
+        t *= out->shape[d];
+    }
+    for (int d = r; d < TENMO_MAX_BATCH_RANK; ++d) {
+        out->shape[d] = 1;
+        out->a_stride[d] = out->b_stride[d] = 0;
+    }
+    *total = t;
+    return TENMO_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tenmo_gemm_last_algo(tenmo_ctx* ctx) { return ctx ? ctx->last_gemm_algo : -1; }
+
+int tenmo_gemm_f32(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A, const tenmo_mat* B,
+                   float* C, float beta, const float* bias, int act, float* aux, float* colsum) {
+    TENMO_CHECK_CTX(ctx);
+    if (!A || !B) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: NULL operand descriptor");
+    if (M < 0 || N < 0 || K < 0)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: negative dimension (M=%lld N=%lld K=%lld)", (long long)M,
+                               (long long)N, (long long)K);
+    if (algo < TENMO_ALGO_AUTO || algo > TENMO_ALGO_TC_3XTF32)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: unknown algo %d", algo);
+    if (act < TENMO_ACT_NONE || act > TENMO_ACT_SIGMOID)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: unknown activation %d", act);
+    if (beta != 0.f && beta != 1.f) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: beta must be 0 or 1");
+    TenmoGemmParams p;
+    memset(&p, 0, sizeof(p));
+    int st = build_batch(ctx, A, B, &p.batch, &p.total_batch);
+    if (st != TENMO_OK) return st;
+    if (colsum && p.batch.rank != 0)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: colsum output is defined for 2-D operands only");
+    if (M == 0 || N == 0 || p.total_batch == 0) return TENMO_OK;  // empty output: nothing to do
+    if (!C) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: C is NULL");
+    if (K > 0 && (!A->ptr || !B->ptr)) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: NULL operand pointer");
+    p.A = A->ptr ? A->ptr + A->offset : nullptr;
+    p.B = B->ptr ? B->ptr + B->offset : nullptr;
+    p.C = C;
+    p.M = M; p.N = N; p.K = K;
+    p.a_rs = A->row_stride; p.a_cs = A->col_stride;
+    p.b_rs = B->row_stride; p.b_cs = B->col_stride;
+    p.beta = beta; p.bias = bias; p.act = act; p.aux = aux;
+
+    TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    int chosen = TENMO_ALGO_SIMT_FP32;
+    if (algo != TENMO_ALGO_SIMT_FP32) {
+        char why[160] = {0};
+        const bool ok = tenmo_gemm_tc_supported(ctx, p, why, sizeof(why));
+        if (algo == TENMO_ALGO_TC_3XTF32 && !ok)
+            return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm: tensor-core kernel cannot take this call: %s", why);
+        if (ok && (algo == TENMO_ALGO_TC_3XTF32 || tenmo_gemm_tc_profitable(ctx, p))) chosen = TENMO_ALGO_TC_3XTF32;
+    }
+    if (chosen == TENMO_ALGO_TC_3XTF32) st = tenmo_gemm_tc_launch(ctx, p);
+    else st = tenmo_gemm_simt_launch(ctx, p);
+    if (st != TENMO_OK) return st;
+    ctx->last_gemm_algo = chosen;
+    if (colsum) {
+        // column sums of the right operand: db when this call is dW = X^T . dY
+        if (B->col_stride != 1)
+            return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm: colsum needs a unit column stride on B");
+        st = tenmo_colsum_f32(ctx, p.B, K, N, B->row_stride, colsum, beta);
+    }
+    return st;
+}
+
+}  // extern "C"

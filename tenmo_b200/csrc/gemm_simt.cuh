@@ -1,0 +1,34 @@
+// Strict-FP32 SIMT GEMM: every output element is ONE k-ascending fmaf chain, which makes it
+// bit-identical to tenmo's CPU paths 1a/1b (matmul_cpu.mojo:275-312: acc = fma(a_ik, b_kj, acc) for
+// k ascending, partial sums parked exactly in C between k tiles).  Operands are arbitrary strided
+// views (transposed views included) with NumPy-style broadcast batching decoded in the kernel, so
+// nothing is materialised and no per-call offset table is uploaded (the reference uploads one per
+// call, kernels/matmul_kernel.mojo:187-239).
+#pragma once
+#include "common.cuh"
+
+struct TenmoBatch {
+    int rank;
+    int64_t shape[TENMO_MAX_BATCH_RANK];     // broadcast batch shape
+    int64_t a_stride[TENMO_MAX_BATCH_RANK];  // 0 where A's dim is 1 or absent
+    int64_t b_stride[TENMO_MAX_BATCH_RANK];
+};
+
+struct TenmoGemmParams {
+    const float* A;  // already advanced by the view offset
+    const float* B;
+    float* C;
+    int64_t M, N, K;
+    int64_t a_rs, a_cs, b_rs, b_cs;
+    int a_vec, b_vec;  // 16-byte vector loads legal along the operand's unit-stride axis
+    int c_vec;         // float4 stores legal on C / aux
+    float beta;
+    const float* bias;
+    int act;
+    float* aux;
+    int tiles_m, tiles_n;
+    int64_t total_batch;
+    TenmoBatch batch;
+};
+
+int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p);

@@ -1,0 +1,170 @@
+// Column sum  out[n] = sum_m x[m, n]  -- the bias gradient and the sum over a broadcast batch.
+//
+// HBM-bound: reads 4*M*N bytes once, coalesced (a warp reads 512 contiguous bytes of a row per step,
+// where the reference's reduction kernel strides down a column, kernels/reduction_kernel.mojo:136-214).
+// Two shapes of kernel:
+//   * few rows (M <= COLSUM_SEQ_ROWS): one thread per column adds its rows in ascending order, which
+//     is bit-identical to tenmo's CPU reduction (sum_mean_reduction.mojo:143-156);
+//   * many rows: the rows are split over CTAs; each CTA reduces its slab of a 128-column strip and
+//     parks a partial in scratch memory, and the last CTA of a strip to finish (ticket counter) adds
+//     the partials in slab order, so the result does not depend on scheduling.
+#include "common.cuh"
+#include "reduce.cuh"
+
+namespace {
+
+constexpr int CS_THREADS = 256;
+constexpr int CS_WARPS = CS_THREADS / 32;
+
+__global__ void __launch_bounds__(CS_THREADS) colsum_seq_kernel(const float* __restrict__ x, int64_t M, int64_t N,
+                                                               int64_t ldx, float* __restrict__ out, float beta) {
+    const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float acc = 0.f;
+    for (int64_t m = 0; m < M; ++m) acc += __ldg(x + m * ldx + n);
+    out[n] = beta != 0.f ? out[n] + acc : acc;
+}
+
+// VEC = 4: float4 loads (needs N % 4 == 0, ldx % 4 == 0, aligned base); VEC = 1: scalar loads.
+template <int VEC>
+__global__ void __launch_bounds__(CS_THREADS)
+colsum_split_kernel(const float* __restrict__ x, int64_t M, int64_t N, int64_t ldx, float* __restrict__ out,
+                    float beta, float* __restrict__ partials, unsigned int* __restrict__ tickets, int rows_per_slab) {
+    constexpr int STRIP = 32 * VEC;
+    __shared__ float red[CS_WARPS][STRIP];
+    __shared__ bool is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int strip = blockIdx.x, slab = blockIdx.y, slabs = gridDim.y;
+    const int64_t n0 = (int64_t)strip * STRIP + lane * VEC;
+    const int64_t m_begin = (int64_t)slab * rows_per_slab;
+    const int64_t m_end = min(m_begin + (int64_t)rows_per_slab, M);
+    float acc[VEC];
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[q] = 0.f;
+    if (n0 < N) {
+        // 4 rows in flight per warp step to cover HBM latency
+        int64_t m = m_begin + warp;
+        for (; m + 3 * CS_WARPS < m_end; m += 4 * CS_WARPS) {
+            if (VEC == 4) {
+                const float4 a = __ldg(reinterpret_cast<const float4*>(x + m * ldx + n0));
+                const float4 b = __ldg(reinterpret_cast<const float4*>(x + (m + CS_WARPS) * ldx + n0));
+                const float4 c = __ldg(reinterpret_cast<const float4*>(x + (m + 2 * CS_WARPS) * ldx + n0));
+                const float4 d = __ldg(reinterpret_cast<const float4*>(x + (m + 3 * CS_WARPS) * ldx + n0));
+                acc[0] += (a.x + b.x) + (c.x + d.x);
+                acc[1 % VEC] += (a.y + b.y) + (c.y + d.y);
+                acc[2 % VEC] += (a.z + b.z) + (c.z + d.z);
+                acc[3 % VEC] += (a.w + b.w) + (c.w + d.w);
+            } else {
+                const float a = __ldg(x + m * ldx + n0), b = __ldg(x + (m + CS_WARPS) * ldx + n0);
+                const float c = __ldg(x + (m + 2 * CS_WARPS) * ldx + n0), d = __ldg(x + (m + 3 * CS_WARPS) * ldx + n0);
+                acc[0] += (a + b) + (c + d);
+            }
+        }
+        for (; m < m_end; m += CS_WARPS) {
+            if (VEC == 4) {
+                const float4 a = __ldg(reinterpret_cast<const float4*>(x + m * ldx + n0));
+                acc[0] += a.x; acc[1 % VEC] += a.y; acc[2 % VEC] += a.z; acc[3 % VEC] += a.w;
+            } else {
+                acc[0] += __ldg(x + m * ldx + n0);
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) red[warp][lane * VEC + q] = acc[q];
+    __syncthreads();
+    // one partial per column of the strip for this slab
+    if (threadIdx.x < STRIP) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < CS_WARPS; ++w) s += red[w][threadIdx.x];
+        const int64_t n = (int64_t)strip * STRIP + threadIdx.x;
+        if (n < N) partials[(int64_t)slab * N + n] = s;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int t = atomicAdd(&tickets[strip], 1u);
+        is_last = (t == (unsigned int)slabs - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (threadIdx.x < STRIP) {
+        const int64_t n = (int64_t)strip * STRIP + threadIdx.x;
+        if (n < N) {
+            float s = 0.f;
+            for (int sl = 0; sl < slabs; ++sl) s += __ldcg(partials + (int64_t)sl * N + n);
+            out[n] = beta != 0.f ? out[n] + s : s;
+        }
+    }
+    if (threadIdx.x == 0) tickets[strip] = 0;  // ready for the next call
+}
+
+}  // namespace
+
+void tenmo_colsum_plan(int sm_count, int64_t M, int64_t N, bool vec, int* strips, int* slabs, int* rows_per_slab) {
+    const int strip_w = vec ? 128 : 32;
+    const int64_t ns = (N + strip_w - 1) / strip_w;
+    // aim for ~4 CTAs per SM in total, at least 64 rows per slab
+    int64_t want = ((int64_t)sm_count * 4 + ns - 1) / ns;
+    int64_t max_slabs = (M + 63) / 64;
+    if (want > max_slabs) want = max_slabs;
+    if (want < 1) want = 1;
+    if (want > 1024) want = 1024;
+    int64_t rps = (M + want - 1) / want;
+    rps = (rps + CS_WARPS - 1) / CS_WARPS * CS_WARPS;
+    *strips = (int)ns;
+    *rows_per_slab = (int)rps;
+    *slabs = (int)((M + rps - 1) / rps);
+}
+
+int tenmo_colsum_launch(tenmo_ctx* ctx, const float* x, int64_t M, int64_t N, int64_t ldx, float* out, float beta,
+                        float* partials, unsigned int* tickets, int strips, int slabs, int rows_per_slab, bool vec) {
+    dim3 grid((unsigned)strips, (unsigned)slabs);
+    if (vec)
+        colsum_split_kernel<4><<<grid, CS_THREADS, 0, ctx->stream>>>(x, M, N, ldx, out, beta, partials, tickets,
+                                                                      rows_per_slab);
+    else
+        colsum_split_kernel<1><<<grid, CS_THREADS, 0, ctx->stream>>>(x, M, N, ldx, out, beta, partials, tickets,
+                                                                      rows_per_slab);
+    TENMO_LAUNCH_CHECK(ctx, "colsum_split_kernel");
+    return TENMO_OK;
+}
+
+extern "C" int tenmo_colsum_f32(tenmo_ctx* ctx, const float* x, int64_t M, int64_t N, int64_t ldx, float* out,
+                                float beta) {
+    TENMO_CHECK_CTX(ctx);
+    if (M < 0 || N < 0) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "colsum: negative shape");
+    if (beta != 0.f && beta != 1.f) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "colsum: beta must be 0 or 1");
+    if (N == 0) return TENMO_OK;
+    if (!out || (M > 0 && !x)) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "colsum: NULL pointer");
+    if (M > 0 && ldx < N) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "colsum: ldx (%lld) < N (%lld)", (long long)ldx, (long long)N);
+    TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (M <= TENMO_COLSUM_SEQ_ROWS) {
+        const int grid = (int)((N + CS_THREADS - 1) / CS_THREADS);
+        colsum_seq_kernel<<<grid, CS_THREADS, 0, ctx->stream>>>(x, M, N, ldx, out, beta);
+        TENMO_LAUNCH_CHECK(ctx, "colsum_seq_kernel");
+        return TENMO_OK;
+    }
+    const bool vec = (N % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
+    int strips, slabs, rps;
+    tenmo_colsum_plan(ctx->sm_count, M, N, vec, &strips, &slabs, &rps);
+    // scratch: slabs*N partial sums (workspace) and one ticket counter per strip (kept at zero between calls)
+    void* ws = nullptr;
+    int st = tenmo_workspace(ctx, (size_t)slabs * (size_t)N * sizeof(float), &ws);
+    if (st != TENMO_OK) return st;
+    if (strips > ctx->tickets_cap) {
+        if (ctx->tickets) {
+            TENMO_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            cudaFree(ctx->tickets);
+            ctx->tickets = nullptr;
+            ctx->tickets_cap = 0;
+        }
+        const int cap = strips < 1024 ? 1024 : strips;
+        TENMO_CUDA_TRY(ctx, cudaMalloc(&ctx->tickets, (size_t)cap * sizeof(unsigned int)));
+        TENMO_CUDA_TRY(ctx, cudaMemset(ctx->tickets, 0, (size_t)cap * sizeof(unsigned int)));
+        ctx->tickets_cap = cap;
+    }
+    unsigned int* tickets = ctx->tickets;
+    return tenmo_colsum_launch(ctx, x, M, N, ldx, out, beta, static_cast<float*>(ws), tickets, strips, slabs, rps, vec);
+}

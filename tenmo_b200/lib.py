@@ -1,0 +1,247 @@
+"""ctypes binding of ``libtenmo_cuda.so`` -- the C ABI declared in ``include/tenmo_cuda.h``.
+
+Plays the role ``BLASHandle`` plays in the reference (tenmo/blashandle.mojo:176-251): the shared
+library is opened once, a failure to load is kept as an error string (``is_initialized()`` false)
+and any call on an uninitialised handle raises.  There is no CPU fallback: without the CUDA
+library nothing on this path runs.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("TENMO_CUDA_PATH", os.path.join(_HERE, "libtenmo_cuda.so"))
+
+MAX_BATCH_RANK = 6
+ALGO_AUTO, ALGO_SIMT_FP32, ALGO_TC_3XTF32 = -1, 0, 1
+ACT_NONE, ACT_RELU, ACT_SIGMOID = 0, 1, 2
+REDUCTION = {"mean": 0, "sum": 1, "none": 2}  # shared/__init__.mojo:4-40
+DP_ID_BYTES = 128
+
+# every symbol include/tenmo_cuda.h declares
+EXPORTS = [
+    "tenmo_cuda_init", "tenmo_cuda_destroy", "tenmo_cuda_last_error", "tenmo_cuda_version", "tenmo_cuda_set_stream",
+    "tenmo_cuda_synchronize", "tenmo_cuda_device_info", "tenmo_cuda_check_device_status", "tenmo_cuda_launch_count",
+    "tenmo_gemm_f32", "tenmo_gemm_last_algo", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
+    "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
+    "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
+    "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
+]
+
+
+class TenmoError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"tenmo_cuda status {status}: {message}")
+        self.status = status
+
+
+class Mat(C.Structure):
+    """``tenmo_mat``: a strided, possibly batched fp32 matrix view in device memory."""
+
+    _fields_ = [
+        ("ptr", C.c_void_p),
+        ("offset", C.c_int64),
+        ("row_stride", C.c_int64),
+        ("col_stride", C.c_int64),
+        ("batch_rank", C.c_int32),
+        ("batch_shape", C.c_int64 * MAX_BATCH_RANK),
+        ("batch_stride", C.c_int64 * MAX_BATCH_RANK),
+    ]
+
+
+def make_mat(ptr: int, shape, strides, offset: int = 0) -> Mat:
+    if len(shape) < 2 or len(shape) != len(strides):
+        raise ValueError("make_mat needs rank >= 2 and one stride per dim")
+    if len(shape) - 2 > MAX_BATCH_RANK:
+        raise ValueError(f"at most {MAX_BATCH_RANK} batch dims")
+    m = Mat()
+    m.ptr = ptr
+    m.offset = offset
+    m.row_stride, m.col_stride = strides[-2], strides[-1]
+    m.batch_rank = len(shape) - 2
+    for d in range(m.batch_rank):
+        m.batch_shape[d] = shape[d]
+        m.batch_stride[d] = strides[d]
+    return m
+
+
+def _bind(lib):
+    P, I, I64, F = C.c_void_p, C.c_int, C.c_int64, C.c_float
+    sig = {
+        "tenmo_cuda_init": (I, [I, C.POINTER(P)]),
+        "tenmo_cuda_destroy": (None, [P]),
+        "tenmo_cuda_last_error": (C.c_char_p, [P]),
+        "tenmo_cuda_version": (C.c_char_p, []),
+        "tenmo_cuda_set_stream": (I, [P, P]),
+        "tenmo_cuda_synchronize": (I, [P]),
+        "tenmo_cuda_device_info": (I, [P, C.POINTER(I), C.POINTER(I), C.POINTER(I), C.POINTER(I)]),
+        "tenmo_cuda_check_device_status": (I, [P]),
+        "tenmo_cuda_launch_count": (I64, [P, I]),
+        "tenmo_gemm_f32": (I, [P, I, I64, I64, I64, C.POINTER(Mat), C.POINTER(Mat), P, F, P, I, P, P]),
+        "tenmo_gemm_last_algo": (I, [P]),
+        "tenmo_add_bias_f32": (I, [P, P, P, P, I64, I64]),
+        "tenmo_add_inplace_f32": (I, [P, P, P, I64]),
+        "tenmo_fill_f32": (I, [P, P, F, I64]),
+        "tenmo_relu_fwd_f32": (I, [P, P, P, P, I64]),
+        "tenmo_relu_bwd_f32": (I, [P, P, P, P, F, I64]),
+        "tenmo_sigmoid_fwd_f32": (I, [P, P, P, I64]),
+        "tenmo_sigmoid_bwd_f32": (I, [P, P, P, P, F, I64]),
+        "tenmo_colsum_f32": (I, [P, P, I64, I64, I64, P, F]),
+        "tenmo_ce_fwd_f32": (I, [P, P, I64, P, I, I64, I64, I64, F, I, P, P, P]),
+        "tenmo_ce_bwd_f32": (I, [P, P, P, I, I64, I64, I64, F, I, P, P, P, F]),
+        "tenmo_sgd_step_f32": (I, [P, I, P, P, P, P, F, F, F, F]),
+        "tenmo_accuracy_f32": (I, [P, P, I64, P, I, I64, I64, P, P]),
+        "tenmo_dp_get_unique_id": (I, [P, P, C.c_size_t]),
+        "tenmo_dp_init": (I, [P, I, I, P, C.c_size_t]),
+        "tenmo_dp_allreduce_sum_f32": (I, [P, P, I64]),
+        "tenmo_dp_finalize": (I, [P]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+
+
+class TenmoCuda:
+    """One context on one device.  ``TenmoCuda(device)`` never raises on load failure; check
+    ``is_initialized()`` / ``get_error()`` like the reference's BLAS handle, or use ``require()``."""
+
+    def __init__(self, device: int = 0, path: str | None = None):
+        self._lib = None
+        self._ctx = C.c_void_p()
+        self._error = ""
+        self.path = path or LIB_PATH
+        try:
+            self._lib = C.CDLL(self.path)
+            _bind(self._lib)
+        except (OSError, AttributeError) as e:
+            self._lib = None
+            self._error = f"Failed to load tenmo CUDA library {self.path}: {e}"
+            return
+        st = self._lib.tenmo_cuda_init(device, C.byref(self._ctx))
+        if st != 0:
+            self._error = self._lib.tenmo_cuda_last_error(None).decode()
+            self._ctx = C.c_void_p()
+
+    # -- handle state -------------------------------------------------------------------------------
+    def is_initialized(self) -> bool:
+        return self._lib is not None and bool(self._ctx)
+
+    def get_error(self) -> str:
+        return self._error
+
+    def require(self) -> "TenmoCuda":
+        if not self.is_initialized():
+            raise TenmoError(-2, self._error or "tenmo CUDA library not initialised")
+        return self
+
+    def close(self):
+        if self.is_initialized():
+            self._lib.tenmo_cuda_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+    def _ck(self, st: int):
+        if st != 0:
+            raise TenmoError(st, self._lib.tenmo_cuda_last_error(self._ctx).decode())
+
+    def _call(self, name: str, *args):
+        if not self.is_initialized():
+            raise TenmoError(-2, self._error or "tenmo CUDA library not initialised")
+        self._ck(getattr(self._lib, name)(self._ctx, *args))
+
+    # -- context ------------------------------------------------------------------------------------
+    def version(self) -> str:
+        return self.require()._lib.tenmo_cuda_version().decode()
+
+    def set_stream(self, cuda_stream: int | None):
+        self._call("tenmo_cuda_set_stream", C.c_void_p(cuda_stream or 0))
+
+    def synchronize(self):
+        self._call("tenmo_cuda_synchronize")
+
+    def device_info(self) -> dict:
+        v = [C.c_int() for _ in range(4)]
+        self._call("tenmo_cuda_device_info", *[C.byref(x) for x in v])
+        return dict(sm_count=v[0].value, cc_major=v[1].value, cc_minor=v[2].value, sm_clock_khz=v[3].value)
+
+    def check_device_status(self):
+        self._call("tenmo_cuda_check_device_status")
+
+    def launch_count(self, reset: bool = False) -> int:
+        return int(self.require()._lib.tenmo_cuda_launch_count(self._ctx, 1 if reset else 0))
+
+    # -- ops (raw device pointers as ints) ------------------------------------------------------------
+    def gemm(self, M, N, K, A: Mat, B: Mat, c_ptr, *, algo=ALGO_AUTO, beta=0.0, bias=0, act=ACT_NONE, aux=0, colsum=0):
+        self._call("tenmo_gemm_f32", algo, M, N, K, C.byref(A), C.byref(B), c_ptr, beta, bias or None, act,
+                   aux or None, colsum or None)
+
+    def gemm_last_algo(self) -> int:
+        return int(self.require()._lib.tenmo_gemm_last_algo(self._ctx))
+
+    def add_bias(self, x, bias, out, M, N):
+        self._call("tenmo_add_bias_f32", x, bias, out, M, N)
+
+    def add_inplace(self, out, inp, n):
+        self._call("tenmo_add_inplace_f32", out, inp, n)
+
+    def fill(self, x, value, n):
+        self._call("tenmo_fill_f32", x, value, n)
+
+    def relu_fwd(self, x, out, mask, n):
+        self._call("tenmo_relu_fwd_f32", x, out, mask or None, n)
+
+    def relu_bwd(self, g, mask, dx, n, beta=0.0):
+        self._call("tenmo_relu_bwd_f32", g, mask, dx, beta, n)
+
+    def sigmoid_fwd(self, x, y, n):
+        self._call("tenmo_sigmoid_fwd_f32", x, y, n)
+
+    def sigmoid_bwd(self, g, y, dx, n, beta=0.0):
+        self._call("tenmo_sigmoid_bwd_f32", g, y, dx, beta, n)
+
+    def colsum(self, x, M, N, ldx, out, beta=0.0):
+        self._call("tenmo_colsum_f32", x, M, N, ldx, out, beta)
+
+    def ce_fwd(self, logits, ld, labels, label_is_i64, M, Cn, ignore_index, label_smoothing, reduction, softmax,
+               loss, valid_count):
+        self._call("tenmo_ce_fwd_f32", logits, ld, labels, 1 if label_is_i64 else 0, M, Cn, ignore_index,
+                   label_smoothing, reduction, softmax or None, loss, valid_count)
+
+    def ce_bwd(self, softmax, labels, label_is_i64, M, Cn, ignore_index, label_smoothing, reduction, upstream,
+               valid_count, dlogits, beta=0.0):
+        self._call("tenmo_ce_bwd_f32", softmax, labels, 1 if label_is_i64 else 0, M, Cn, ignore_index,
+                   label_smoothing, reduction, upstream or None, valid_count or None, dlogits, beta)
+
+    def sgd_step(self, p_ptrs, g_ptrs, v_ptrs, numels, lr, momentum=0.0, weight_decay=0.0, grad_scale=1.0):
+        n = len(p_ptrs)
+        arr = lambda xs: (C.c_void_p * n)(*xs)
+        pa, ga = arr(p_ptrs), arr(g_ptrs)
+        va = arr(v_ptrs) if v_ptrs is not None else None
+        na = (C.c_int64 * n)(*numels)
+        self._call("tenmo_sgd_step_f32", n, pa, ga, va, na, lr, momentum, weight_decay, grad_scale)
+
+    def accuracy(self, logits, ld, labels, label_is_i64, M, Cn, correct_dev) -> int:
+        host = C.c_int64(0)
+        self._call("tenmo_accuracy_f32", logits, ld, labels, 1 if label_is_i64 else 0, M, Cn, correct_dev,
+                   C.byref(host))
+        return int(host.value)
+
+    def accuracy_async(self, logits, ld, labels, label_is_i64, M, Cn, correct_dev):
+        self._call("tenmo_accuracy_f32", logits, ld, labels, 1 if label_is_i64 else 0, M, Cn, correct_dev, None)
+
+    # -- data parallel ---------------------------------------------------------------------------------
+    def dp_get_unique_id(self) -> bytes:
+        buf = C.create_string_buffer(DP_ID_BYTES)
+        self._call("tenmo_dp_get_unique_id", buf, DP_ID_BYTES)
+        return buf.raw
+
+    def dp_init(self, rank: int, world: int, uid: bytes | None):
+        buf = C.create_string_buffer(uid, DP_ID_BYTES) if uid else None
+        self._call("tenmo_dp_init", rank, world, buf, DP_ID_BYTES if uid else 0)
+
+    def dp_allreduce_sum(self, buf, count):
+        self._call("tenmo_dp_allreduce_sum_f32", buf, count)
+
+    def dp_finalize(self):
+        self._call("tenmo_dp_finalize")
