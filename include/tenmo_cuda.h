@@ -46,7 +46,9 @@ int tenmo_cuda_init(int device, tenmo_ctx** out);
 void tenmo_cuda_destroy(tenmo_ctx* ctx);
 const char* tenmo_cuda_last_error(tenmo_ctx* ctx); /* ctx may be NULL: returns the last init error */
 const char* tenmo_cuda_version(void);
-/* Stream handle of the caller's DeviceContext (a cudaStream_t); NULL selects the context's own stream. */
+/* Stream handle of the caller's DeviceContext (a cudaStream_t, taken verbatim: NULL is CUDA's default
+ * stream).  A new context runs on a stream of its own; TENMO_STREAM_OWN selects that one again. */
+#define TENMO_STREAM_OWN ((void*)(intptr_t)-1)
 int tenmo_cuda_set_stream(tenmo_ctx* ctx, void* cuda_stream);
 /* DeviceContext.synchronize (the `sync=True` argument of every launcher, matmul_kernel.mojo:277). */
 int tenmo_cuda_synchronize(tenmo_ctx* ctx);

@@ -98,7 +98,7 @@ const char* tenmo_cuda_last_error(tenmo_ctx* ctx) { return ctx ? ctx->err : g_in
 
 int tenmo_cuda_set_stream(tenmo_ctx* ctx, void* cuda_stream) {
     TENMO_CHECK_CTX(ctx);
-    ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+    ctx->stream = cuda_stream == TENMO_STREAM_OWN ? ctx->own_stream : (cudaStream_t)cuda_stream;
     return TENMO_OK;
 }
 

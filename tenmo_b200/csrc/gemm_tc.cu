@@ -1,5 +1,617 @@
-// placeholder until the tcgen05 kernel lands
+// tcgen05 / TMEM tensor-core GEMM with 3xTF32 error compensation (fp32 in, fp32 out).
+//
+// Arithmetic.  Each fp32 operand x is split as x = hi + lo with hi = x truncated to TF32 (the tensor
+// core reads only the top 19 bits of an fp32 word, so the raw operand IS the hi plane) and
+// lo = tf32(x - hi).  A product a*b is formed as  a_lo*b_hi + a_hi*b_lo + a_hi*b_hi  by three
+// tcgen05.mma.kind::tf32 instructions into one fp32 accumulator in tensor memory; the dropped
+// a_lo*b_lo term is below 2^-20 relative.  The lo planes are produced by a bandwidth-bound split
+// kernel into the context workspace (one read + one write per operand element).
+//
+// Kernel.  Persistent, one CTA per SM, 192 threads, warp-specialised:
+//   warp 0   TMA producer   cp.async.bulk.tensor (no multicast) of the A, A_lo, B, B_lo tiles of a
+//                           k-block into a ring of shared-memory stages, 128-byte swizzle
+//   warp 1   MMA issuer     one elected thread issues 4 k-steps x 3 products of 128 x BN x 8 per stage,
+//                           tcgen05.commit releases the stage and, at the end of a tile, publishes the
+//                           accumulator; also owns the TMEM allocation (2 accumulators, double buffered)
+//   warps 2-5 epilogue      tcgen05.ld the accumulator (one TMEM lane = one row per thread), add bias,
+//                           activation / ReLU mask / beta accumulate, store to C
+// Operand layouts.  "K-major" = the contraction index is the unit-stride axis (row-major A, or B given
+// as a transposed view); "MN-major" = the other axis is (A given as a transposed view, row-major B).
+// Both are native tcgen05 shared-memory layouts, so transposed stride views need no copy: only the
+// tensor-map box and the descriptor change (this is what the two backward GEMMs use).
+// Every wait on an mbarrier is bounded in wall-clock time; on expiry the kernel raises the context's
+// device status word, drains its outstanding copies, frees its tensor memory and returns.
+// Roofline: tensor pipe; the useful work is 2*M*N*K flop (the 3x is not counted).
+#include <cuda.h>
+
+#include <cstdlib>
+
 #include "gemm_tc.cuh"
-bool tenmo_gemm_tc_supported(tenmo_ctx*, const TenmoGemmParams&, char* why, size_t n) { snprintf(why, n, "not built"); return false; }
-bool tenmo_gemm_tc_profitable(tenmo_ctx*, const TenmoGemmParams&) { return false; }
-int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams&) { return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "not built"); }
+
+namespace {
+
+constexpr int TC_THREADS = 192;
+constexpr int BM = 128;
+constexpr int BK = 32;                       // fp32 elements per k-block = one 128-byte swizzle row
+constexpr int UMMA_K = 8;                    // tf32 k per instruction
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+
+template <int BN>
+struct TcCfg {
+    static constexpr int A_TILE = BM * BK * 4;   // bytes of one plane of A per stage
+    static constexpr int B_TILE = BN * BK * 4;
+    static constexpr int STAGE = 2 * A_TILE + 2 * B_TILE;
+    static constexpr int STAGES = (BN == 256) ? 2 : 3;
+    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = 2 * BN;     // two accumulators
+};
+
+struct TcParams {
+    float* C;
+    float* aux;
+    const float* bias;
+    int64_t M, N, K;
+    int64_t total_batch;
+    int tiles_m, tiles_n;
+    int a_batched, b_batched;  // 0: operand is broadcast over the batch (coordinate 0), 1: one slice per batch
+    float beta;
+    int act;
+    int c_vec;
+    uint32_t* status;
+};
+
+// ---------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false when another role aborted or the time limit ran out (then *abort is raised).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((it & 255u) == 255u) {
+            if (*abort) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) { *abort = 1; return false; }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in
+// 16-byte units, descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // version
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ float act_apply(float v, int act) {
+    if (act == TENMO_ACT_RELU) return v > 0.f ? v : 0.f;
+    if (act == TENMO_ACT_SIGMOID) return 1.f / (1.f + expf(-v));
+    return v;
+}
+
+// Tile order: groups of GROUP_M row tiles are walked column by column, so that the tiles running at
+// the same time share A and B panels in L2.
+constexpr int GROUP_M = 16;
+__device__ __forceinline__ void tile_coords(int64_t tile, int tiles_m, int tiles_n, int64_t* batch, int* tm, int* tn) {
+    const int64_t per_batch = (int64_t)tiles_m * tiles_n;
+    *batch = tile / per_batch;
+    const int t = (int)(tile % per_batch);
+    const int group = t / (GROUP_M * tiles_n);
+    const int first_m = group * GROUP_M;
+    const int rows = min(GROUP_M, tiles_m - first_m);
+    const int in_group = t - group * GROUP_M * tiles_n;
+    *tm = first_m + in_group % rows;
+    *tn = in_group / rows;
+}
+
+// A_MN / B_MN: the operand's unit-stride axis is m (resp. n) instead of k.
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo,
+               const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b_lo, const TcParams p) {
+    using Cfg = TcCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 128B swizzle wants 1024-byte alignment
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + Cfg::STAGES * Cfg::STAGE;
+    // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem ptr, abort flag
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::STAGES + 2 + a); };
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + Cfg::STAGES * Cfg::STAGE + 8 * (2 * Cfg::STAGES + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t num_tiles = (int64_t)p.tiles_m * p.tiles_n * p.total_batch;
+    const int num_kb = (int)((p.K + BK - 1) / BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr_smem)),
+                     "r"((uint32_t)Cfg::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t armed = 0;  // stages whose full barrier was armed at least once
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int64_t batch; int tm, tn;
+                tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
+                const int m0 = tm * BM, n0 = tn * BN;
+                const int ba = p.a_batched ? (int)batch : 0, bb = p.b_batched ? (int)batch : 0;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * Cfg::STAGE;
+                    const uint32_t sal = sa + Cfg::A_TILE, sb = sa + 2 * Cfg::A_TILE, sbl = sb + Cfg::B_TILE;
+                    const uint32_t bar = full_bar(stage);
+                    mbar_expect_tx(bar, (uint32_t)Cfg::STAGE);
+                    armed |= 1u << stage;
+                    const int k0 = kb * BK;
+                    if (!A_MN) {
+                        tma_load_3d(sa, &map_a, bar, k0, m0, ba);
+                        tma_load_3d(sal, &map_a_lo, bar, k0, m0, ba);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 32; ++j) {
+                            tma_load_3d(sa + j * 4096, &map_a, bar, m0 + 32 * j, k0, ba);
+                            tma_load_3d(sal + j * 4096, &map_a_lo, bar, m0 + 32 * j, k0, ba);
+                        }
+                    }
+                    if (!B_MN) {
+                        tma_load_3d(sb, &map_b, bar, k0, n0, bb);
+                        tma_load_3d(sbl, &map_b_lo, bar, k0, n0, bb);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 32; ++j) {
+                            tma_load_3d(sb + j * 4096, &map_b, bar, n0 + 32 * j, k0, bb);
+                            tma_load_3d(sbl + j * 4096, &map_b_lo, bar, n0 + 32 * j, k0, bb);
+                        }
+                    }
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Drain: let every copy already issued land before the CTA gives its shared memory back.
+                // A stage's last armed phase: stages < `stage` were armed in the current phase, the rest in the previous.
+                for (int s = 0; s < Cfg::STAGES; ++s) {
+                    if (!(armed & (1u << s))) continue;
+                    const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
+                    const uint64_t t0 = globaltimer_ns();
+                    for (;;) {
+                        uint32_t done;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                            : "=r"(done) : "r"(full_bar(s)), "r"(ph) : "memory");
+                        if (done || globaltimer_ns() - t0 > WAIT_LIMIT_NS) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer -------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                                       ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // K-major: rows of 128 B, 8-row groups 1024 B apart, k-step = 32 B inside the swizzle row.
+            // MN-major: 32-wide chunks 4096 B apart (LBO), 8-k groups 1024 B apart (SBO), k-step = 1024 B.
+            constexpr uint32_t A_LBO = A_MN ? 4096u : 16u, A_SBO = 1024u, A_KSTEP = A_MN ? 1024u : 32u;
+            constexpr uint32_t B_LBO = B_MN ? 4096u : 16u, B_SBO = 1024u, B_KSTEP = B_MN ? 1024u : 32u;
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t acc_phase[2] = {0, 0};
+            int acc = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_base + stage * Cfg::STAGE;
+                    const uint32_t sal = sa + Cfg::A_TILE, sb = sa + 2 * Cfg::A_TILE, sbl = sb + Cfg::B_TILE;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t da = make_desc(sa + k * A_KSTEP, A_LBO, A_SBO);
+                        const uint64_t dal = make_desc(sal + k * A_KSTEP, A_LBO, A_SBO);
+                        const uint64_t db = make_desc(sb + k * B_KSTEP, B_LBO, B_SBO);
+                        const uint64_t dbl = make_desc(sbl + k * B_KSTEP, B_LBO, B_SBO);
+                        umma_tf32(d_tmem, dal, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);  // a_lo * b_hi
+                        umma_tf32(d_tmem, da, dbl, idesc, 1u);                             // a_hi * b_lo
+                        umma_tf32(d_tmem, da, db, idesc, 1u);                              // a_hi * b_hi
+                    }
+                    umma_commit(empty_bar(stage));  // stage is free once these MMAs have read it
+                    if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(acc));  // accumulator complete
+                acc_phase[acc] ^= 1u;
+                acc ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------- epilogue (warps 2..5) -------------------------------
+        const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
+        uint32_t acc_phase[2] = {0, 0};
+        int acc = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int64_t batch; int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
+            if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag)) { ok = false; break; }
+            tcgen05_fence_after();
+            const int64_t m = (int64_t)tm * BM + quarter * 32 + lane;
+            const int64_t n_base = (int64_t)tn * BN;
+            float* crow = p.C + (batch * p.M + m) * p.N;
+            float* auxrow = p.aux ? p.aux + (batch * p.M + m) * p.N : nullptr;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(taddr + (uint32_t)(c * 32), r);
+                tmem_ld_wait();
+                const int64_t n0 = n_base + c * 32;
+                if (m < p.M && n0 < p.N) {
+#pragma unroll
+                    for (int q = 0; q < 32; q += 4) {
+                        const int64_t n = n0 + q;
+                        if (n >= p.N) break;
+                        float v[4], mk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float x = __uint_as_float(r[q + e]);
+                            if (p.bias && n + e < p.N) x += __ldg(p.bias + n + e);
+                            mk[e] = x > 0.f ? 1.f : 0.f;
+                            v[e] = act_apply(x, p.act);
+                        }
+                        if (p.c_vec && n + 3 < p.N) {
+                            float4 o = make_float4(v[0], v[1], v[2], v[3]);
+                            if (p.beta != 0.f) {
+                                const float4 old = *reinterpret_cast<const float4*>(crow + n);
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            *reinterpret_cast<float4*>(crow + n) = o;
+                            if (auxrow) *reinterpret_cast<float4*>(auxrow + n) = make_float4(mk[0], mk[1], mk[2], mk[3]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (n + e < p.N) {
+                                    crow[n + e] = p.beta != 0.f ? crow[n + e] + v[e] : v[e];
+                                    if (auxrow) auxrow[n + e] = mk[e];
+                                }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            acc_phase[acc] ^= 1u;
+            acc ^= 1;
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, TENMO_DEV_TIMEOUT);
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// lo-plane split:  lo = tf32_rna(x - trunc_tf32(x)), written compactly (rows x inner, ld = ld_lo)
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float tf32_lo(float x) {
+    const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+    const float d = x - hi;
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(d));
+    return __uint_as_float(r);
+}
+
+__global__ void __launch_bounds__(256)
+split_lo_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t rows, int64_t inner, int64_t ld_src,
+                int64_t ld_dst, int64_t batches, int64_t bstride_src, int64_t bstride_dst) {
+    const int64_t vec_per_row = ld_dst / 4;  // ld_dst is a multiple of 4; the pad columns are written as zeros
+    const int64_t total = batches * rows * vec_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t v = i % vec_per_row;
+        const int64_t rb = i / vec_per_row;
+        const int64_t r = rb % rows, b = rb / rows;
+        const int64_t c = v * 4;
+        const float* s = src + b * bstride_src + r * ld_src + c;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c + 3 < inner) {
+            x = __ldg(reinterpret_cast<const float4*>(s));
+        } else {
+            if (c + 0 < inner) x.x = __ldg(s);
+            if (c + 1 < inner) x.y = __ldg(s + 1);
+            if (c + 2 < inner) x.z = __ldg(s + 2);
+        }
+        float4 o = make_float4(tf32_lo(x.x), tf32_lo(x.y), tf32_lo(x.z), tf32_lo(x.w));
+        *reinterpret_cast<float4*>(dst + b * bstride_dst + r * ld_dst + c) = o;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct OperandPlan {
+    bool mn_major;        // unit-stride axis is m / n (not k)
+    int64_t inner, outer; // extents of the storage matrix (inner = unit-stride axis)
+    int64_t ld;           // elements between consecutive `outer` indices
+    int batched;          // 1: one slice per batch with a uniform stride, 0: broadcast
+    int64_t batch_stride; // elements
+    int64_t batches;      // slices that exist in memory (1 when broadcast)
+    int64_t ld_lo, bstride_lo;
+};
+
+// Collapse an operand's (possibly broadcast) batch dims into "one uniform stride" or "broadcast".
+bool collapse_batch(const TenmoBatch& b, const int64_t* stride, int64_t total, int* batched, int64_t* bstride) {
+    if (total == 1) { *batched = 0; *bstride = 0; return true; }
+    bool all_zero = true;
+    for (int d = 0; d < b.rank; ++d)
+        if (b.shape[d] > 1 && stride[d] != 0) all_zero = false;
+    if (all_zero) { *batched = 0; *bstride = 0; return true; }
+    // every dim of extent > 1 must be present with stride = stride[next] * shape[next]
+    int64_t expect = -1;
+    for (int d = b.rank - 1; d >= 0; --d) {
+        if (b.shape[d] == 1) continue;
+        if (stride[d] == 0) return false;  // broadcast in some dims only
+        if (expect < 0) { *bstride = stride[d]; expect = stride[d] * b.shape[d]; }
+        else { if (stride[d] != expect) return false; expect *= b.shape[d]; }
+    }
+    *batched = 1;
+    return true;
+}
+
+bool plan_operand(int64_t rows, int64_t cols, int64_t rs, int64_t cs, bool rows_are_k, const float* ptr,
+                  const TenmoBatch& b, const int64_t* bstrides, int64_t total_batch, OperandPlan* o, const char* name,
+                  char* why, size_t why_len) {
+    // rows x cols view; k is the row index when rows_are_k (operand B) else the column index (operand A)
+    bool unit_cols = (cs == 1) || cols == 1, unit_rows = (rs == 1) || rows == 1;
+    int64_t inner, outer, ld;
+    bool inner_is_k;
+    if (unit_cols && (rs >= cols || rows == 1)) { inner = cols; outer = rows; ld = rows == 1 ? cols : rs; inner_is_k = !rows_are_k; }
+    else if (unit_rows && (cs >= rows || cols == 1)) { inner = rows; outer = cols; ld = cols == 1 ? rows : cs; inner_is_k = rows_are_k; }
+    else { snprintf(why, why_len, "%s has no unit-stride axis", name); return false; }
+    if (ld % 4 != 0 || (reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) {
+        snprintf(why, why_len, "%s is not 16-byte aligned (leading stride %lld elements)", name, (long long)ld);
+        return false;
+    }
+    if (ld < inner) { snprintf(why, why_len, "%s rows overlap", name); return false; }
+    if (!collapse_batch(b, bstrides, total_batch, &o->batched, &o->batch_stride)) {
+        snprintf(why, why_len, "%s batch dims do not collapse to one stride", name);
+        return false;
+    }
+    if (o->batched && (o->batch_stride % 4 != 0 || o->batch_stride <= 0)) {
+        snprintf(why, why_len, "%s batch stride is not a positive multiple of 4 elements", name);
+        return false;
+    }
+    o->mn_major = !inner_is_k;
+    o->inner = inner; o->outer = outer; o->ld = ld;
+    o->batches = o->batched ? total_batch : 1;
+    o->ld_lo = (inner + 3) / 4 * 4;
+    o->bstride_lo = o->ld_lo * outer;
+    return true;
+}
+
+bool make_plan(const TenmoGemmParams& p, OperandPlan* a, OperandPlan* b, char* why, size_t why_len) {
+    if (p.K < 1) { snprintf(why, why_len, "K == 0"); return false; }
+    if (p.M > 0x7fffffffLL || p.N > 0x7fffffffLL || p.K > 0x7fffffffLL || p.total_batch > 0x7fffffffLL) {
+        snprintf(why, why_len, "dimension exceeds 2^31"); return false;
+    }
+    if (!plan_operand(p.M, p.K, p.a_rs, p.a_cs, false, p.A, p.batch, p.batch.a_stride, p.total_batch, a, "A", why, why_len)) return false;
+    if (!plan_operand(p.K, p.N, p.b_rs, p.b_cs, true, p.B, p.batch, p.batch.b_stride, p.total_batch, b, "B", why, why_len)) return false;
+    return true;
+}
+
+int encode_map(tenmo_ctx* ctx, CUtensorMap* map, const float* base, const OperandPlan& o, bool lo, int box_outer) {
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    const int64_t ld = lo ? o.ld_lo : o.ld;
+    const int64_t bs = lo ? o.bstride_lo : (o.batched ? o.batch_stride : ld * o.outer);
+    cuuint64_t dims[3] = {(cuuint64_t)o.inner, (cuuint64_t)o.outer, (cuuint64_t)o.batches};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)bs * 4};
+    if (o.batches == 1) strides[1] = (cuuint64_t)ld * 4 * (cuuint64_t)o.outer;  // unused, but must be a legal stride
+    if (strides[1] % 16 != 0) strides[1] = (strides[1] + 15) / 16 * 16;
+    cuuint32_t box[3] = {32u, (cuuint32_t)box_outer, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return tenmo_set_error(ctx, TENMO_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (inner %lld outer %lld ld %lld)", (int)r,
+                               (long long)o.inner, (long long)o.outer, (long long)ld);
+    return TENMO_OK;
+}
+
+template <int BN>
+cudaError_t launch_tc(bool a_mn, bool b_mn, int grid, cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mal,
+                      const CUtensorMap& mb, const CUtensorMap& mbl, const TcParams& tp) {
+    const int smem = TcCfg<BN>::SMEM;
+#define TC_LAUNCH(AM, BMJ)                                                                                          \
+    {                                                                                                               \
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, AM, BMJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+        if (e != cudaSuccess) return e;                                                                             \
+        gemm_tc_kernel<BN, AM, BMJ><<<grid, TC_THREADS, smem, s>>>(ma, mal, mb, mbl, tp);                           \
+    }
+    if (a_mn) { if (b_mn) TC_LAUNCH(true, true) else TC_LAUNCH(true, false) }
+    else { if (b_mn) TC_LAUNCH(false, true) else TC_LAUNCH(false, false) }
+#undef TC_LAUNCH
+    return cudaGetLastError();
+}
+
+int tc_init(tenmo_ctx* ctx) {
+    if (ctx->tc_ready) return TENMO_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+        cudaGetLastError();
+        return tenmo_set_error(ctx, TENMO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    }
+    ctx->encode_tiled = fn;
+    ctx->tc_ready = true;
+    return TENMO_OK;
+}
+
+}  // namespace
+
+bool tenmo_gemm_tc_supported(tenmo_ctx* ctx, const TenmoGemmParams& p, char* why, size_t why_len) {
+    (void)ctx;
+    OperandPlan a, b;
+    return make_plan(p, &a, &b, why, why_len);
+}
+
+bool tenmo_gemm_tc_profitable(tenmo_ctx* ctx, const TenmoGemmParams& p) {
+    (void)ctx;
+    const double flop = 2.0 * (double)p.M * (double)p.N * (double)p.K * (double)p.total_batch;
+    return flop >= 2.0e9 && p.M >= 128 && p.N >= 64 && p.K >= 64;
+}
+
+int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
+    int st = tc_init(ctx);
+    if (st != TENMO_OK) return st;
+    OperandPlan a, b;
+    char why[160];
+    if (!make_plan(p, &a, &b, why, sizeof(why))) return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm_tc: %s", why);
+
+    // workspace: [A_lo | B_lo]
+    const size_t a_lo_bytes = ((size_t)a.bstride_lo * a.batches * 4 + 1023) & ~(size_t)1023;
+    const size_t b_lo_bytes = ((size_t)b.bstride_lo * b.batches * 4 + 1023) & ~(size_t)1023;
+    void* ws = nullptr;
+    st = tenmo_workspace(ctx, a_lo_bytes + b_lo_bytes, &ws);
+    if (st != TENMO_OK) return st;
+    float* a_lo = static_cast<float*>(ws);
+    float* b_lo = reinterpret_cast<float*>(static_cast<char*>(ws) + a_lo_bytes);
+
+    auto split = [&](const float* src, float* dst, const OperandPlan& o) -> int {
+        const int64_t work = o.batches * o.outer * (o.ld_lo / 4);
+        const int grid = tenmo_stream_grid(ctx, work, 256 * 4, 8);
+        split_lo_kernel<<<grid, 256, 0, ctx->stream>>>(src, dst, o.outer, o.inner, o.ld, o.ld_lo, o.batches,
+                                                       o.batched ? o.batch_stride : 0, o.bstride_lo);
+        TENMO_LAUNCH_CHECK(ctx, "split_lo_kernel");
+        return TENMO_OK;
+    };
+    if ((st = split(p.A, a_lo, a)) != TENMO_OK) return st;
+    if ((st = split(p.B, b_lo, b)) != TENMO_OK) return st;
+
+    const char* env_bn = getenv("TENMO_TC_BN");
+    int bn = 256;
+    if (env_bn && atoi(env_bn) == 128) bn = 128;
+    if (p.N <= 128) bn = 128;
+
+    CUtensorMap ma, mal, mb, mbl;
+    const int a_box = a.mn_major ? 32 : BM;
+    const int b_box = b.mn_major ? 32 : bn;
+    if ((st = encode_map(ctx, &ma, p.A, a, false, a_box)) != TENMO_OK) return st;
+    if ((st = encode_map(ctx, &mal, a_lo, a, true, a_box)) != TENMO_OK) return st;
+    if ((st = encode_map(ctx, &mb, p.B, b, false, b_box)) != TENMO_OK) return st;
+    if ((st = encode_map(ctx, &mbl, b_lo, b, true, b_box)) != TENMO_OK) return st;
+
+    TcParams tp;
+    tp.C = p.C; tp.aux = p.aux; tp.bias = p.bias;
+    tp.M = p.M; tp.N = p.N; tp.K = p.K; tp.total_batch = p.total_batch;
+    tp.tiles_m = (int)((p.M + BM - 1) / BM);
+    tp.tiles_n = (int)((p.N + bn - 1) / bn);
+    tp.a_batched = a.batched; tp.b_batched = b.batched;
+    tp.beta = p.beta; tp.act = p.act;
+    tp.c_vec = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) &&
+               (!p.aux || (reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0);
+    tp.status = ctx->dev_status;
+    const int64_t tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.total_batch;
+    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    cudaError_t e = (bn == 256) ? launch_tc<256>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
+                                : launch_tc<128>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp);
+    ctx->launches++;
+    if (e != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_tc_kernel failed: %s", cudaGetErrorString(e));
+    return TENMO_OK;
+}

@@ -155,7 +155,8 @@ class TenmoCuda:
         return self.require()._lib.tenmo_cuda_version().decode()
 
     def set_stream(self, cuda_stream: int | None):
-        self._call("tenmo_cuda_set_stream", C.c_void_p(cuda_stream or 0))
+        """``cuda_stream`` is a raw cudaStream_t (0 = CUDA's default stream); ``None`` = the context's own."""
+        self._call("tenmo_cuda_set_stream", C.c_void_p(-1 if cuda_stream is None else cuda_stream))
 
     def synchronize(self):
         self._call("tenmo_cuda_synchronize")

@@ -1,0 +1,132 @@
+"""Parity of the tcgen05 3xTF32 GEMM with the CPU oracle.
+
+Bar: max relative error <= 1e-4, measured per element against the oracle's fp32 result and normalised by
+sum_k |a_ik||b_kj| (the scale every backward-stable GEMM error bound is stated in); the fp64 product is
+checked at the same bar so that the oracle's own rounding does not mask anything.  In practice the kernel
+lands near 1e-6.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+TC = 1
+TOL = 1e-4
+
+
+@pytest.fixture(scope="module")
+def g():
+    from tests import gpu_util
+
+    gpu_util.handle()
+    return gpu_util
+
+
+def rel_err(C, ref, absA, absB):
+    scale = absA.astype(np.float64) @ absB.astype(np.float64)
+    return float(np.max(np.abs(C.astype(np.float64) - ref) / np.maximum(scale, 1e-30)))
+
+
+def layouts(oracle, A, B, layout):
+    Av, Bv = oracle.View.of(A), oracle.View.of(B)
+    if layout in ("tn", "tt"):
+        Av = oracle.View.of(np.ascontiguousarray(A.T)).t()
+    if layout in ("nt", "tt"):
+        Bv = oracle.View.of(np.ascontiguousarray(B.T)).t()
+    return Av, Bv
+
+
+SHAPES = [(128, 32, 256), (128, 64, 128), (256, 128, 512), (384, 96, 640), (200, 100, 300), (1000, 260, 132),
+          (129, 36, 260), (512, 784, 128), (2048, 512, 1024), (640, 2052, 388)]
+
+
+@pytest.mark.parametrize("mkn", SHAPES, ids=str)
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn", "tt"])
+def test_tc_matches_oracle(g, oracle, mkn, layout):
+    M, K, N = mkn
+    if layout in ("tn", "tt") and M % 4:
+        pytest.skip("transposed A needs a 16-byte aligned leading stride")
+    rng = np.random.default_rng(M * 31 + K * 7 + N)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32)
+    Av, Bv = layouts(oracle, A, B, layout)
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert g.handle().gemm_last_algo() == TC
+    g.handle().check_device_status()
+    ref32 = oracle.matmul(Av, Bv, threads=4)
+    e32 = rel_err(C, ref32.astype(np.float64), np.abs(A), np.abs(B))
+    e64 = rel_err(C, A.astype(np.float64) @ B.astype(np.float64), np.abs(A), np.abs(B))
+    assert e32 <= TOL and e64 <= TOL, (e32, e64)
+    assert e64 <= 4e-6, f"3xTF32 should be close to fp32 accuracy, got {e64}"
+
+
+def test_tc_epilogue_and_accumulate(g, oracle):
+    M, K, N = 384, 200, 512
+    rng = np.random.default_rng(9)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32) * 0.1
+    bias = rng.standard_normal(N).astype(np.float32)
+    Av, Bv = oracle.View.of(A), oracle.View.of(B)
+    z = oracle.add_bias(oracle.matmul(A, B), bias)
+    C, aux, _ = g.gpu_matmul(Av, Bv, algo=TC, bias=bias, act=1, want_aux=True)
+    out, mask = oracle.relu_fwd(z)
+    near_zero = np.abs(z) < 1e-4  # the sign of a pre-activation within rounding of 0 is not defined
+    assert np.allclose(C, out, rtol=1e-5, atol=1e-4)
+    assert np.array_equal(aux[~near_zero], mask[~near_zero])
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=TC, bias=bias, act=2)
+    assert np.allclose(C, oracle.sigmoid_fwd(z), rtol=1e-5, atol=1e-5)
+    init = rng.standard_normal((M, N), np.float32)
+    C, _, cs = g.gpu_matmul(Av.t(), oracle.View.of(init), algo=TC, beta=1.0, c_init=np.ones((K, N), np.float32),
+                            colsum=True)
+    ref = 1.0 + A.T.astype(np.float64) @ init.astype(np.float64)
+    assert rel_err(C - 1.0, ref - 1.0, np.abs(A.T), np.abs(init)) <= TOL
+    assert np.allclose(cs, 0.0 + oracle.colsum(init), rtol=1e-5, atol=1e-4)
+
+
+def test_tc_batched(g, oracle):
+    rng = np.random.default_rng(4)
+    # (B,M,K) @ (1,K,N): broadcast right operand
+    A = rng.standard_normal((6, 256, 64), np.float32)
+    B = rng.standard_normal((1, 64, 128), np.float32)
+    C, _, _ = g.gpu_matmul(oracle.View.of(A), oracle.View.of(B), algo=TC)
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    assert np.max(np.abs(C - ref)) <= TOL * 64 * 4
+    # attention-shaped with a stride-permuted K^T, then P @ V
+    BH, S, D = 8, 256, 64
+    Q, Kt, V = (rng.standard_normal((BH, S, D), np.float32) * 0.125 for _ in range(3))
+    Kv = oracle.View.of(Kt).t()
+    scores, _, _ = g.gpu_matmul(oracle.View.of(Q), Kv, algo=TC)
+    ref = Q.astype(np.float64) @ np.swapaxes(Kt, 1, 2).astype(np.float64)
+    assert np.max(np.abs(scores - ref)) <= 1e-5
+    assert np.max(np.abs(scores - oracle.matmul(oracle.View.of(Q), Kv, threads=4))) <= 1e-5
+    ctx, _, _ = g.gpu_matmul(oracle.View.of(scores), oracle.View.of(V), algo=TC)
+    assert np.max(np.abs(ctx - scores.astype(np.float64) @ V.astype(np.float64))) <= 1e-4
+    # 4-D batch that collapses to one stride
+    A4 = rng.standard_normal((2, 3, 128, 32), np.float32)
+    B4 = rng.standard_normal((2, 3, 32, 64), np.float32)
+    C4, _, _ = g.gpu_matmul(oracle.View.of(A4), oracle.View.of(B4), algo=TC)
+    assert np.max(np.abs(C4 - A4.astype(np.float64) @ B4.astype(np.float64))) <= 1e-4
+
+
+def test_tc_refuses_what_it_cannot_take_and_auto_falls_back(g, oracle):
+    from tenmo_b200 import TenmoError
+
+    rng = np.random.default_rng(1)
+    A, B = rng.standard_normal((128, 30), np.float32), rng.standard_normal((30, 64), np.float32)  # ld 30: rows not 16-byte aligned
+    with pytest.raises(TenmoError) as e:
+        g.gpu_matmul(oracle.View.of(A), oracle.View.of(B), algo=TC)
+    assert e.value.status == -3
+    C, _, _ = g.gpu_matmul(oracle.View.of(A), oracle.View.of(B), algo=-1)  # auto -> SIMT on the GPU, never the CPU
+    assert g.handle().gemm_last_algo() == 0 and np.array_equal(C, oracle.matmul(A, B))
+    # auto picks the tensor-core kernel for a large aligned problem
+    A, B = rng.standard_normal((1024, 1024), np.float32), rng.standard_normal((1024, 1024), np.float32)
+    C, _, _ = g.gpu_matmul(oracle.View.of(A), oracle.View.of(B), algo=-1)
+    assert g.handle().gemm_last_algo() == 1
+    assert rel_err(C, A.astype(np.float64) @ B.astype(np.float64), np.abs(A), np.abs(B)) <= TOL
+
+
+def test_tc_run_to_run_identical(g, oracle):
+    rng = np.random.default_rng(8)
+    A, B = rng.standard_normal((512, 512), np.float32), rng.standard_normal((512, 768), np.float32)
+    C1, _, _ = g.gpu_matmul(oracle.View.of(A), oracle.View.of(B), algo=TC)
+    C2, _, _ = g.gpu_matmul(oracle.View.of(A), oracle.View.of(B), algo=TC)
+    assert np.array_equal(C1, C2)
