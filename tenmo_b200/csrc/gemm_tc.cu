@@ -138,13 +138,15 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in
 // 16-byte units, descriptor version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// layout_type: 2 = 128-byte swizzle of 16-byte chunks (K-major tiles), 1 = 128-byte swizzle of 32-byte
+// chunks, the only swizzled layout tcgen05 takes for an MN-major 32-bit operand.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr >> 4) & 0x3FFF);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= (uint64_t)1 << 46;  // version
-    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    d |= (uint64_t)layout_type << 61;
     return d;
 }
 
@@ -273,10 +275,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
                                        ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            // K-major: rows of 128 B, 8-row groups 1024 B apart, k-step = 32 B inside the swizzle row.
-            // MN-major: 32-wide chunks 4096 B apart (LBO), 8-k groups 1024 B apart (SBO), k-step = 1024 B.
-            constexpr uint32_t A_LBO = A_MN ? 4096u : 16u, A_SBO = 1024u, A_KSTEP = A_MN ? 1024u : 32u;
-            constexpr uint32_t B_LBO = B_MN ? 4096u : 16u, B_SBO = 1024u, B_KSTEP = B_MN ? 1024u : 32u;
+            // K-major: rows of 128 B, 8-row groups 1024 B apart (SBO), k-step = 32 B inside the swizzle row.
+            // MN-major: a tile is [32-wide mn chunk][k row of 128 B]; chunks are 4096 B apart (LBO), the
+            // swizzle pattern repeats every 4 k rows = 512 B (SBO), one k-step of 8 rows = 1024 B.
+            constexpr uint32_t A_LBO = A_MN ? 4096u : 16u, A_SBO = A_MN ? 512u : 1024u, A_KSTEP = A_MN ? 1024u : 32u;
+            constexpr uint32_t B_LBO = B_MN ? 4096u : 16u, B_SBO = B_MN ? 512u : 1024u, B_KSTEP = B_MN ? 1024u : 32u;
+            constexpr uint32_t A_LT = A_MN ? 1u : 2u, B_LT = B_MN ? 1u : 2u;
             int stage = 0;
             uint32_t phase = 0;
             uint32_t acc_phase[2] = {0, 0};
@@ -293,10 +297,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t sal = sa + Cfg::A_TILE, sb = sa + 2 * Cfg::A_TILE, sbl = sb + Cfg::B_TILE;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t da = make_desc(sa + k * A_KSTEP, A_LBO, A_SBO);
-                        const uint64_t dal = make_desc(sal + k * A_KSTEP, A_LBO, A_SBO);
-                        const uint64_t db = make_desc(sb + k * B_KSTEP, B_LBO, B_SBO);
-                        const uint64_t dbl = make_desc(sbl + k * B_KSTEP, B_LBO, B_SBO);
+                        const uint64_t da = make_desc(sa + k * A_KSTEP, A_LBO, A_SBO, A_LT);
+                        const uint64_t dal = make_desc(sal + k * A_KSTEP, A_LBO, A_SBO, A_LT);
+                        const uint64_t db = make_desc(sb + k * B_KSTEP, B_LBO, B_SBO, B_LT);
+                        const uint64_t dbl = make_desc(sbl + k * B_KSTEP, B_LBO, B_SBO, B_LT);
                         umma_tf32(d_tmem, dal, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);  // a_lo * b_hi
                         umma_tf32(d_tmem, da, dbl, idesc, 1u);                             // a_hi * b_lo
                         umma_tf32(d_tmem, da, db, idesc, 1u);                              // a_hi * b_hi
@@ -505,7 +509,9 @@ int encode_map(tenmo_ctx* ctx, CUtensorMap* map, const float* base, const Operan
     cuuint32_t box[3] = {32u, (cuuint32_t)box_outer, 1u};
     cuuint32_t estr[3] = {1u, 1u, 1u};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    o.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return tenmo_set_error(ctx, TENMO_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (inner %lld outer %lld ld %lld)", (int)r,
