@@ -1,0 +1,321 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: fp32 GEMM forward + backward (C = A.B, dA = dC.B^T, dB = A^T.dC).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--size 8192] [--impl reference]
+
+One "step" is one forward+backward pass (three GEMMs, transposed operands as stride views) over one
+set of seeded synthetic matrices, N(0,1), row-major.  With N > 1 (launched by torch.distributed.run,
+one process per GPU) every rank runs its own replica of the step -- the standalone GEMM has no
+cross-GPU dependency -- and the reported value is the sum over ranks (weak scaling).
+
+The one JSON line printed by rank 0 carries:
+  value      device-resident throughput, 6*M*N*K flop per step, CUDA-event timed, max over ranks
+  e2e        the same step through the host-facing call: inputs in pinned host memory, H2D copies,
+             the three GEMMs, D2H of the three results, all inside the timed region
+  roofline   the tcgen05 GEMM kernel alone (event pairs recorded around each launch by the library)
+             against the measured tensor peak: TF32 runs at half the measured bf16 rate and 3xTF32
+             spends three tensor-core products per fp32 product, so peak = bf16 / 2 / 3
+  cpu_baseline   the CPU oracle (restated tenmo CPU path) on this host's cores, on a bounded sample
+--impl reference times that CPU path alone (the reference is Mojo and cannot be built here, so the
+oracle port is the reference arm).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "fp32_gemm_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(source="measured", hbm_gbs=d["hbm_gbs"], bf16_burst=d["bf16_tflops"],
+                    bf16_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]))
+    return dict(source="fallback", hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0)
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the oracle port, bounded sample
+# ---------------------------------------------------------------------------------------------------
+def cpu_fwd_bwd(size: int, threads: int, seed: int = 0) -> float:
+    """Seconds for one forward+backward at size^3 through the oracle (stride views for the transposes)."""
+    import numpy as np
+
+    from oracle import ref
+
+    rng = np.random.default_rng(seed)
+    A, B, dC = (rng.standard_normal((size, size), np.float32) for _ in range(3))
+    Av, Bv, dCv = ref.View.of(A), ref.View.of(B), ref.View.of(dC)
+    t0 = time.perf_counter()
+    ref.matmul(Av, Bv, threads=threads)
+    ref.matmul(dCv, Bv.t(), threads=threads)  # dA = dC.B^T: B^T is a stride view -> the scalar path, as in the reference
+    ref.matmul(Av.t(), dCv, threads=threads)  # dB = A^T.dC
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(budget_s: float = 20.0):
+    threads = host_cores()
+    size = 512
+    secs = cpu_fwd_bwd(size, threads)
+    # grow the sample while the next size is predicted to stay inside the budget (work grows 8x per doubling)
+    while size < 4096 and secs * 8 < budget_s:
+        size *= 2
+        secs = cpu_fwd_bwd(size, threads)
+    flops = 6.0 * size ** 3
+    return dict(value=flops / secs / 1e12, unit=UNIT, cores=threads, kind="port",
+                sample=f"one fwd+bwd at {size}^3 ({secs:.2f} s), oracle port of matmul_cpu.mojo, {threads} threads over row tiles")
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = host_cores()
+    size = args.ref_size
+    for _ in range(args.warmup):
+        cpu_fwd_bwd(size, threads)
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        cpu_fwd_bwd(size, threads, seed=s)
+    dt = time.perf_counter() - t0
+    flops = 6.0 * size ** 3 * args.steps
+    value = flops / dt / 1e12
+    sample = f"each step = one fwd+bwd at {size}^3 on {threads} host threads (oracle port; the Mojo reference cannot be built here)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"fp32 GEMM fwd+bwd, CPU sample {size}^3 of the {args.size}^3 workload", "size": size},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks sampler
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        # the GPU idles between launches of this process only before and after the timed region; take the
+        # median of the upper half so that idle samples at the edges do not drag the figure down
+        busy = sm[len(sm) // 2:] if sm else []
+        med = busy[len(busy) // 2] if busy else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from tenmo_b200 import ALGO_SIMT_FP32, ALGO_TC_3XTF32, TenmoCuda, make_mat
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    h = TenmoCuda(local_rank).require()  # fails loudly if the CUDA library is missing: there is no fallback
+    stream = torch.cuda.current_stream()
+    h.set_stream(stream.cuda_stream)
+    algo = ALGO_SIMT_FP32 if args.algo == "simt" else ALGO_TC_3XTF32
+
+    S = args.size
+    M = N = K = S
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    host_in = [torch.randn(S, S, generator=gen, dtype=torch.float32).pin_memory() for _ in range(3)]  # A, B, dC
+    host_out = [torch.empty(S, S, dtype=torch.float32).pin_memory() for _ in range(3)]               # C, dA, dB
+    A, B, dC = (t.cuda(non_blocking=True) for t in host_in)
+    C, dA, dB = (torch.empty(S, S, device="cuda") for _ in range(3))
+    torch.cuda.synchronize()
+
+    def mats(a, b, dc):
+        mA = make_mat(a.data_ptr(), (M, K), (K, 1))
+        mB = make_mat(b.data_ptr(), (K, N), (N, 1))
+        mBt = make_mat(b.data_ptr(), (N, K), (1, N))    # B^T as a stride view
+        mAt = make_mat(a.data_ptr(), (K, M), (1, K))    # A^T as a stride view
+        mdC = make_mat(dc.data_ptr(), (M, N), (N, 1))
+        return mA, mB, mBt, mAt, mdC
+
+    mA, mB, mBt, mAt, mdC = mats(A, B, dC)
+
+    def step_device():
+        h.gemm(M, N, K, mA, mB, C.data_ptr(), algo=algo)       # C  = A . B
+        h.gemm(M, K, N, mdC, mBt, dA.data_ptr(), algo=algo)    # dA = dC . B^T
+        h.gemm(K, N, M, mAt, mdC, dB.data_ptr(), algo=algo)    # dB = A^T . dC
+
+    def step_e2e():
+        A.copy_(host_in[0], non_blocking=True)
+        B.copy_(host_in[1], non_blocking=True)
+        dC.copy_(host_in[2], non_blocking=True)
+        step_device()
+        host_out[0].copy_(C, non_blocking=True)
+        host_out[1].copy_(dA, non_blocking=True)
+        host_out[2].copy_(dB, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        barrier()
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    h.launch_count(reset=True)
+    h.profile_begin()
+    ms_dev = timed(step_device, args.steps)
+    launches = h.launch_count(reset=True)
+    n_kernel, kernel_ms = h.profile_end()
+    clocks = sampler.stop() if rank == 0 else None
+
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    h.check_device_status()
+
+    flop_step = 6.0 * M * N * K
+    value = flop_step * world * args.steps / (ms_dev * 1e-3) / 1e12
+    e2e_value = flop_step * world * args.steps / (ms_e2e * 1e-3) / 1e12
+    peaks = load_peaks()
+    if args.algo == "simt":
+        info = h.device_info()
+        peak = 2.0 * 128 * info["sm_count"] * info["sm_clock_khz"] * 1e3 / 1e12
+        peak_note = "strict-FP32 SIMT peak = 2 x 128 lanes x SMs x max SM clock"
+        kernel = "gemm_simt_kernel"
+    else:
+        peak = peaks["bf16_sustained"] / 2.0 / 3.0
+        peak_note = (f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']:.1f} TFLOP/s / 2 (TF32 rate) / 3 "
+                     f"(three products per fp32 product); burst-based figure {peaks['bf16_burst'] / 6.0:.1f}")
+        kernel = "gemm_tc_kernel"
+    achieved = (2.0 * M * N * K) / ((kernel_ms / max(n_kernel, 1)) * 1e-3) / 1e12 if n_kernel else None
+
+    out = None
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"fp32 GEMM fwd+bwd (C=A.B, dA=dC.B^T, dB=A^T.dC) at M=N=K={S}, N(0,1) seeded, "
+                                   f"transposes as stride views", "size": S, "algo": "3xtf32-tcgen05" if algo == 1 else "simt-fp32",
+                       "parallelism": f"replicas x{world}", "l2": "inputs (3 x %.0f MB) exceed the 126 MB L2" % (S * S * 4 / 1e6)},
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": 3 * S * S * 4, "d2h_bytes_per_step": 3 * S * S * 4},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "tensor" if algo == 1 else "fp32", "kernel": kernel, "achieved": achieved, "peak": peak,
+                         "unit": UNIT, "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "launches_timed": n_kernel, "avg_launch_ms": kernel_ms / max(n_kernel, 1), "peak_note": peak_note},
+        }
+        if world == 1 and not args.no_cpu:
+            out["cpu_baseline"] = cpu_baseline(args.cpu_budget)
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--size", type=int, default=8192)
+    ap.add_argument("--algo", choices=["tc", "simt"], default="tc")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--ref-size", type=int, default=1024, help="CPU sample size for --impl reference")
+    ap.add_argument("--cpu-budget", type=float, default=20.0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

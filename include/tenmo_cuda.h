@@ -58,6 +58,13 @@ int tenmo_cuda_device_info(tenmo_ctx* ctx, int* sm_count, int* cc_major, int* cc
 int tenmo_cuda_check_device_status(tenmo_ctx* ctx);
 /* Counts kernel launches made through this context since the last reset (bookkeeping for benchmarks). */
 int64_t tenmo_cuda_launch_count(tenmo_ctx* ctx, int reset);
+/* Device timing of the GEMM main kernels (not the split / reduction helpers around them): between
+ * begin and end every such launch is bracketed by a CUDA event pair on the context's stream (at most
+ * 4096 launches are recorded).  end synchronises and returns the number of launches and the sum of
+ * their durations.  Takes the place of the reference's hand timing with perf_counter_ns
+ * (profile_gpu.mojo:36-65). */
+int tenmo_cuda_profile_begin(tenmo_ctx* ctx);
+int tenmo_cuda_profile_end(tenmo_ctx* ctx, int64_t* launches, double* total_ms);
 
 /* ---- GEMM ---------------------------------------------------------------------------------------
  * A strided, possibly batched matrix operand: element (b..., i, j) lives at

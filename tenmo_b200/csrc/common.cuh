@@ -40,6 +40,10 @@ struct tenmo_ctx {
     // tcgen05 GEMM state (tensor-map encoder entry point, opt-in smem set)
     void* encode_tiled = nullptr;
     bool tc_ready = false;
+    // optional device timing of the GEMM kernels (tenmo_cuda_profile_begin/end)
+    bool prof_on = false;
+    cudaEvent_t* prof_ev = nullptr;  // pairs: [2*i] before, [2*i+1] after
+    int prof_n = 0, prof_cap = 0;
     // NCCL
     void* nccl_lib = nullptr;
     void* nccl_comm = nullptr;
@@ -48,6 +52,9 @@ struct tenmo_ctx {
 
 int tenmo_set_error(tenmo_ctx* ctx, int status, const char* fmt, ...);
 int tenmo_workspace(tenmo_ctx* ctx, size_t bytes, void** out);
+// Event pair around a GEMM kernel launch while profiling is on (no-ops otherwise).
+void tenmo_prof_before(tenmo_ctx* ctx);
+void tenmo_prof_after(tenmo_ctx* ctx);
 
 #define TENMO_CHECK_CTX(ctx)             \
     do {                                 \

@@ -34,7 +34,46 @@ int tenmo_workspace(tenmo_ctx* ctx, size_t bytes, void** out) {
     return TENMO_OK;
 }
 
+void tenmo_prof_before(tenmo_ctx* ctx) {
+    if (!ctx->prof_on || ctx->prof_n >= ctx->prof_cap) return;
+    cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
+}
+void tenmo_prof_after(tenmo_ctx* ctx) {
+    if (!ctx->prof_on || ctx->prof_n >= ctx->prof_cap) return;
+    cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);
+    ctx->prof_n++;
+}
+
 extern "C" {
+
+int tenmo_cuda_profile_begin(tenmo_ctx* ctx) {
+    TENMO_CHECK_CTX(ctx);
+    if (!ctx->prof_ev) {
+        const int cap = 4096;
+        ctx->prof_ev = new cudaEvent_t[2 * cap];
+        for (int i = 0; i < 2 * cap; ++i) TENMO_CUDA_TRY(ctx, cudaEventCreate(&ctx->prof_ev[i]));
+        ctx->prof_cap = cap;
+    }
+    ctx->prof_n = 0;
+    ctx->prof_on = true;
+    return TENMO_OK;
+}
+
+int tenmo_cuda_profile_end(tenmo_ctx* ctx, int64_t* launches, double* total_ms) {
+    TENMO_CHECK_CTX(ctx);
+    ctx->prof_on = false;
+    TENMO_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    double sum = 0.0;
+    for (int i = 0; i < ctx->prof_n; ++i) {
+        float ms = 0.f;
+        TENMO_CUDA_TRY(ctx, cudaEventElapsedTime(&ms, ctx->prof_ev[2 * i], ctx->prof_ev[2 * i + 1]));
+        sum += ms;
+    }
+    if (launches) *launches = ctx->prof_n;
+    if (total_ms) *total_ms = sum;
+    ctx->prof_n = 0;
+    return TENMO_OK;
+}
 
 const char* tenmo_cuda_version(void) { return "tenmo_cuda 0.1 (sm_100a)"; }
 
@@ -90,6 +129,10 @@ void tenmo_cuda_destroy(tenmo_ctx* ctx) {
     if (ctx->tickets) cudaFree(ctx->tickets);
     if (ctx->sgd_desc_dev) cudaFree(ctx->sgd_desc_dev);
     if (ctx->sgd_desc_host) cudaFreeHost(ctx->sgd_desc_host);
+    if (ctx->prof_ev) {
+        for (int i = 0; i < 2 * ctx->prof_cap; ++i) cudaEventDestroy(ctx->prof_ev[i]);
+        delete[] ctx->prof_ev;
+    }
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
 }

@@ -281,9 +281,11 @@ int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p_in) {
     if (grid <= 0 || grid > 0x7fffffffLL)
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: grid of %lld tiles is out of range", (long long)grid);
     cudaError_t e;
+    tenmo_prof_before(ctx);
     if (cfg == 128) e = launch_cfg<128, 128, 16, 8, 8>(p, a_inner_k, b_inner_k, grid, ctx->stream);
     else if (cfg == 64) e = launch_cfg<64, 64, 16, 4, 4>(p, a_inner_k, b_inner_k, grid, ctx->stream);
     else e = launch_cfg<32, 32, 32, 2, 2>(p, a_inner_k, b_inner_k, grid, ctx->stream);
+    tenmo_prof_after(ctx);
     ctx->launches++;
     if (e != cudaSuccess)
         return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_simt_kernel failed: %s", cudaGetErrorString(e));

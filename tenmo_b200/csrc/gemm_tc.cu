@@ -615,8 +615,10 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     tp.status = ctx->dev_status;
     const int64_t tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.total_batch;
     const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    tenmo_prof_before(ctx);
     cudaError_t e = (bn == 256) ? launch_tc<256>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
                                 : launch_tc<128>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp);
+    tenmo_prof_after(ctx);
     ctx->launches++;
     if (e != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_tc_kernel failed: %s", cudaGetErrorString(e));
     return TENMO_OK;

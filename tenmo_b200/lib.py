@@ -23,6 +23,7 @@ DP_ID_BYTES = 128
 EXPORTS = [
     "tenmo_cuda_init", "tenmo_cuda_destroy", "tenmo_cuda_last_error", "tenmo_cuda_version", "tenmo_cuda_set_stream",
     "tenmo_cuda_synchronize", "tenmo_cuda_device_info", "tenmo_cuda_check_device_status", "tenmo_cuda_launch_count",
+    "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end",
     "tenmo_gemm_f32", "tenmo_gemm_last_algo", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
     "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
@@ -78,6 +79,8 @@ def _bind(lib):
         "tenmo_cuda_device_info": (I, [P, C.POINTER(I), C.POINTER(I), C.POINTER(I), C.POINTER(I)]),
         "tenmo_cuda_check_device_status": (I, [P]),
         "tenmo_cuda_launch_count": (I64, [P, I]),
+        "tenmo_cuda_profile_begin": (I, [P]),
+        "tenmo_cuda_profile_end": (I, [P, C.POINTER(I64), C.POINTER(C.c_double)]),
         "tenmo_gemm_f32": (I, [P, I, I64, I64, I64, C.POINTER(Mat), C.POINTER(Mat), P, F, P, I, P, P]),
         "tenmo_gemm_last_algo": (I, [P]),
         "tenmo_add_bias_f32": (I, [P, P, P, P, I64, I64]),
@@ -171,6 +174,15 @@ class TenmoCuda:
 
     def launch_count(self, reset: bool = False) -> int:
         return int(self.require()._lib.tenmo_cuda_launch_count(self._ctx, 1 if reset else 0))
+
+    def profile_begin(self):
+        self._call("tenmo_cuda_profile_begin")
+
+    def profile_end(self):
+        """Returns (launches, total_ms) of the GEMM main kernels since profile_begin."""
+        n, ms = C.c_int64(0), C.c_double(0.0)
+        self._call("tenmo_cuda_profile_end", C.byref(n), C.byref(ms))
+        return int(n.value), float(ms.value)
 
     # -- ops (raw device pointers as ints) ------------------------------------------------------------
     def gemm(self, M, N, K, A: Mat, B: Mat, c_ptr, *, algo=ALGO_AUTO, beta=0.0, bias=0, act=ACT_NONE, aux=0, colsum=0):
