@@ -135,9 +135,14 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
+    def wait_first(self, timeout=3.0):
+        t0 = time.time()
+        while self.proc and not self.lines and time.time() - t0 < timeout:
+            time.sleep(0.02)
+
+    def stop(self, t_begin=None, t_end=None):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -147,7 +152,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ts, ln in self.lines:
+            if t_begin is not None and not (t_begin <= ts <= t_end + 0.1):
+                continue  # keep only samples taken while the timed region ran
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 6:
                 continue
@@ -160,10 +167,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(nm)
         sm.sort()
-        # the GPU idles between launches of this process only before and after the timed region; take the
-        # median of the upper half so that idle samples at the edges do not drag the figure down
-        busy = sm[len(sm) // 2:] if sm else []
-        med = busy[len(busy) // 2] if busy else None
+        med = sm[len(sm) // 2] if sm else None
         return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
@@ -239,19 +243,22 @@ def run_gpu_arm(args):
         barrier()
         return float(ms.item())
 
-    for _ in range(max(args.warmup, 3)):
-        step_device()
-    torch.cuda.synchronize()
-
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    torch.cuda.synchronize()
+    if rank == 0:
+        sampler.wait_first()
     h.launch_count(reset=True)
     h.profile_begin()
+    t_begin = time.time()
     ms_dev = timed(step_device, args.steps)
+    t_end = time.time()
     launches = h.launch_count(reset=True)
     n_kernel, kernel_ms = h.profile_end()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
 
     for _ in range(2):
         step_e2e()
@@ -302,12 +309,12 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--algo", choices=["tc", "simt"], default="tc")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--ref-size", type=int, default=1024, help="CPU sample size for --impl reference")
+    ap.add_argument("--ref-size", type=int, default=2048, help="CPU sample size for --impl reference")
     ap.add_argument("--cpu-budget", type=float, default=20.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     args = ap.parse_args()
