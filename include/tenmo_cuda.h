@@ -131,6 +131,22 @@ int tenmo_sigmoid_bwd_f32(tenmo_ctx* ctx, const float* g, const float* y, float*
  * with M = leading batch and N = the rest, sum_over_broadcasted_axes (sum_mean_reduction.mojo:184-211). */
 int tenmo_colsum_f32(tenmo_ctx* ctx, const float* x, int64_t M, int64_t N, int64_t ldx, float* out, float beta);
 
+/* The same column sum for callers that must not let the library allocate (no counterpart in the
+ * reference).  A host that owns all device memory through its own pool, or a loop that cannot afford
+ * the device-wide synchronisation of cudaMalloc / cudaFree, cannot use the entry point above, which
+ * grows a workspace on first use.  This one needs no context and calls no allocator: its scratch (the
+ * partial sums and ticket counters of the split kernel) is a fixed array inside the loaded module,
+ * about 4 MiB, held by every GPU that loads the library until the process exits.
+ *   - Limit: N <= 16384 columns (any M, any ldx >= N); beyond that it returns TENMO_ERR_UNSUPPORTED and
+ *     tenmo_cuda_last_error(NULL) says so.
+ *   - Runs on the CURRENT device, on `cuda_stream` (a cudaStream_t; NULL = default stream).
+ *   - The first call on each device resolves the array's device address; make that first call outside
+ *     any stream capture.
+ *   - All calls share the one array.  What must start at zero is cleared on the stream before each
+ *     launch, but two calls whose kernels overlap on the GPU (different streams) race on it. */
+int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int64_t ldx, float* out, float beta,
+                            void* cuda_stream);
+
 /* ---- softmax cross-entropy, class-index targets ---------------------------------------------------
  * reduction: 0 mean, 1 sum, 2 none (shared/__init__.mojo:4-40).
  * Forward (crossentropy.mojo:285-432, kernels/crossentropy_fused_kernel.mojo:39-160): per row max,

@@ -168,3 +168,92 @@ extern "C" int tenmo_colsum_f32(tenmo_ctx* ctx, const float* x, int64_t M, int64
     unsigned int* tickets = ctx->tickets;
     return tenmo_colsum_launch(ctx, x, M, N, ldx, out, beta, static_cast<float*>(ws), tickets, strips, slabs, rps, vec);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Column sum for callers that must not allocate.
+//
+// Some hosts of this library cannot let it call cudaMalloc: a runtime that has handed the whole device
+// to its own buffer pool (tenmo's DeviceContext caches and re-issues device buffers, so a second
+// allocator competing for what is left can fail at any time), or a serving / training loop that must
+// not meet the device-wide synchronisation an allocation or a free implies.  The regular entry point
+// grows a workspace on first use; this one keeps its scratch -- the per-slab partial sums and the
+// per-strip ticket counters of the split kernel above -- in a fixed array that is part of the loaded
+// module.  Every GPU that loads the library holds those TENMO_STATIC_SCRATCH_BYTES until exit.
+// ---------------------------------------------------------------------------------------------------
+#define TENMO_STATIC_MAX_COLS 16384   // widest matrix the fixed scratch serves
+#define TENMO_STATIC_MAX_SLABS 64     // row slabs (partial sums per column)
+#define TENMO_STATIC_MAX_STRIPS 512   // 16384 columns / 32-column scalar strips
+#define TENMO_STATIC_PARTIAL_FLOATS (TENMO_STATIC_MAX_COLS * TENMO_STATIC_MAX_SLABS)
+#define TENMO_STATIC_SCRATCH_BYTES (TENMO_STATIC_PARTIAL_FLOATS * 4 + TENMO_STATIC_MAX_STRIPS * 4)
+
+// [0, PARTIAL_FLOATS) partial sums as float, then MAX_STRIPS ticket counters.  In host code this name is
+// only a handle for cudaGetSymbolAddress; the kernel is always given the address obtained from it.
+static __device__ __align__(256) unsigned int tenmo_static_scratch[TENMO_STATIC_PARTIAL_FLOATS + TENMO_STATIC_MAX_STRIPS];
+
+namespace {
+constexpr int STATIC_MAX_DEVICES = 64;
+void* g_static_scratch_addr[STATIC_MAX_DEVICES] = {nullptr};  // per device, filled on its first call
+int g_static_sm_count[STATIC_MAX_DEVICES] = {0};
+}  // namespace
+
+extern "C" int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int64_t ldx, float* out, float beta,
+                                       void* cuda_stream) {
+    if (M < 0 || N < 0) return tenmo_set_error(nullptr, TENMO_ERR_INVALID, "colsum_static: negative shape");
+    if (beta != 0.f && beta != 1.f) return tenmo_set_error(nullptr, TENMO_ERR_INVALID, "colsum_static: beta must be 0 or 1");
+    if (N == 0) return TENMO_OK;
+    if (!out || (M > 0 && !x)) return tenmo_set_error(nullptr, TENMO_ERR_INVALID, "colsum_static: NULL pointer");
+    if (M > 0 && ldx < N)
+        return tenmo_set_error(nullptr, TENMO_ERR_INVALID, "colsum_static: ldx (%lld) < N (%lld)", (long long)ldx, (long long)N);
+    if (N > TENMO_STATIC_MAX_COLS)
+        return tenmo_set_error(nullptr, TENMO_ERR_UNSUPPORTED,
+                               "colsum_static: N = %lld exceeds the %d columns the fixed scratch serves; use tenmo_colsum_f32",
+                               (long long)N, TENMO_STATIC_MAX_COLS);
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return tenmo_set_error(nullptr, TENMO_ERR_CUDA, "colsum_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES)
+        return tenmo_set_error(nullptr, TENMO_ERR_UNSUPPORTED, "colsum_static: device ordinal %d is beyond %d", dev, STATIC_MAX_DEVICES);
+    if (!g_static_scratch_addr[dev]) {
+        // Set-up, once per device, with that device current: resolve the module's array to a device address.
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, tenmo_static_scratch);
+        if (e != cudaSuccess || !addr)
+            return tenmo_set_error(nullptr, TENMO_ERR_CUDA, "colsum_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || sms <= 0)
+            return tenmo_set_error(nullptr, TENMO_ERR_CUDA, "colsum_static: SM count query: %s", cudaGetErrorString(e));
+        g_static_sm_count[dev] = sms;
+        g_static_scratch_addr[dev] = addr;
+    }
+    if (M <= TENMO_COLSUM_SEQ_ROWS) {  // few rows: one thread per column, no scratch at all
+        const int grid = (int)((N + CS_THREADS - 1) / CS_THREADS);
+        colsum_seq_kernel<<<grid, CS_THREADS, 0, stream>>>(x, M, N, ldx, out, beta);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return tenmo_set_error(nullptr, TENMO_ERR_CUDA, "colsum_static: launch: %s", cudaGetErrorString(e));
+        return TENMO_OK;
+    }
+    const bool vec = (N % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
+    int strips, slabs, rps;
+    tenmo_colsum_plan(g_static_sm_count[dev], M, N, vec, &strips, &slabs, &rps);
+    if (slabs > TENMO_STATIC_MAX_SLABS) {  // fewer, taller slabs so that the partials fit
+        const int64_t rows = (M + TENMO_STATIC_MAX_SLABS - 1) / TENMO_STATIC_MAX_SLABS;
+        rps = (int)((rows + CS_WARPS - 1) / CS_WARPS * CS_WARPS);
+        slabs = (int)((M + rps - 1) / rps);
+    }
+    if (strips > TENMO_STATIC_MAX_STRIPS || (int64_t)slabs * N > TENMO_STATIC_PARTIAL_FLOATS)
+        return tenmo_set_error(nullptr, TENMO_ERR_UNSUPPORTED, "colsum_static: %d strips x %d slabs do not fit the fixed scratch", strips, slabs);
+    float* partials = static_cast<float*>(g_static_scratch_addr[dev]);
+    unsigned int* tickets = static_cast<unsigned int*>(g_static_scratch_addr[dev]) + TENMO_STATIC_PARTIAL_FLOATS;
+    // The array keeps whatever the previous call left.  The partials are rewritten before they are read;
+    // the tickets must start at zero, so they are cleared on the stream ahead of the kernel.
+    e = cudaMemsetAsync(tickets, 0, (size_t)strips * sizeof(unsigned int), stream);
+    if (e != cudaSuccess) return tenmo_set_error(nullptr, TENMO_ERR_CUDA, "colsum_static: clearing tickets: %s", cudaGetErrorString(e));
+    dim3 grid((unsigned)strips, (unsigned)slabs);
+    if (vec) colsum_split_kernel<4><<<grid, CS_THREADS, 0, stream>>>(x, M, N, ldx, out, beta, partials, tickets, rps);
+    else colsum_split_kernel<1><<<grid, CS_THREADS, 0, stream>>>(x, M, N, ldx, out, beta, partials, tickets, rps);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return tenmo_set_error(nullptr, TENMO_ERR_CUDA, "colsum_static: launch: %s", cudaGetErrorString(e));
+    return TENMO_OK;
+}
