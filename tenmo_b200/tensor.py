@@ -1,0 +1,487 @@
+"""Host-side mirror of tenmo's data model for the dense fp32 training path.
+
+``NDBuffer`` = shape + element strides + element offset over a device allocation
+(tenmo/ndbuffer.mojo:66-74); ``Tensor`` = NDBuffer + requires_grad + gradbox + ancestry
+(tenmo/tensor.mojo); ``Tensor.backward`` = DFS topological order + fan-in counted ready queue
+(tenmo/tensor.mojo:3154-3247) with the integer-tag dispatch of ``Backward.invoke``
+(tenmo/backpropagation.mojo:278-519).  Every device operation goes through the C ABI of
+libtenmo_cuda.so; torch only owns the device allocations.  Names, argument meaning and error
+behaviour follow the reference so that the parity tests read like the reference's own tests.
+"""
+from __future__ import annotations
+
+from collections import deque
+
+import numpy as np
+import torch
+
+from . import lib as _lib
+from .lib import TenmoCuda, make_mat
+
+# op tags, values as in tenmo/backpropagation.mojo:30-96
+BACKWARD_RELU = 2
+BACKWARD_MATMUL_ND = 3
+BACKWARD_MATMUL_2D = 4
+BACKWARD_SIGMOID = 7
+BACKWARD_CE_CLASS_INDICES_INT32 = 9
+BACKWARD_SUM = 16
+BACKWARD_ADD_BROADCAST = 23
+BACKWARD_CE_CLASS_INDICES_INT64 = 66
+
+_handles: dict[int, TenmoCuda] = {}
+_gemm_algo = _lib.ALGO_AUTO
+
+
+def handle(device: int | None = None) -> TenmoCuda:
+    """The process-wide context of a device, bound to torch's current stream.  Raises if the CUDA
+    library or the GPU is missing -- there is no CPU path behind it."""
+    dev = torch.cuda.current_device() if device is None else device
+    h = _handles.get(dev)
+    if h is None:
+        h = TenmoCuda(dev).require()
+        _handles[dev] = h
+    h.set_stream(torch.cuda.current_stream(dev).cuda_stream)
+    return h
+
+
+def set_gemm_algo(name: str):
+    """'auto' | 'simt' (strict fp32) | '3xtf32' (tcgen05): the run-time switch TENMO_CUDA_GEMM."""
+    global _gemm_algo
+    _gemm_algo = {"auto": _lib.ALGO_AUTO, "simt": _lib.ALGO_SIMT_FP32, "3xtf32": _lib.ALGO_TC_3XTF32}[name]
+
+
+def panic(*parts):
+    """tenmo/common_utils.mojo:97-106 aborts; here a host error that tests can catch."""
+    raise RuntimeError(" ".join(str(p) for p in parts))
+
+
+def _contig_strides(shape):
+    st, acc = [], 1
+    for s in reversed(shape):
+        st.append(acc)
+        acc *= s
+    return tuple(reversed(st))
+
+
+class NDBuffer:
+    """A strided fp32 (or integer label) view of a flat device allocation."""
+
+    def __init__(self, storage: torch.Tensor, shape, strides=None, offset: int = 0):
+        self.storage = storage
+        self.shape = tuple(int(s) for s in shape)
+        self.strides = tuple(int(s) for s in (strides if strides is not None else _contig_strides(self.shape)))
+        self.offset = int(offset)
+
+    # -- construction ------------------------------------------------------------------------------
+    @staticmethod
+    def zeros(shape, dtype=torch.float32) -> "NDBuffer":
+        n = int(np.prod(shape)) if len(shape) else 1
+        return NDBuffer(torch.zeros(max(n, 1), dtype=dtype, device="cuda"), shape)
+
+    @staticmethod
+    def empty(shape) -> "NDBuffer":
+        n = int(np.prod(shape)) if len(shape) else 1
+        return NDBuffer(torch.empty(max(n, 1), dtype=torch.float32, device="cuda"), shape)
+
+    @staticmethod
+    def from_numpy(a, dtype=np.float32) -> "NDBuffer":
+        a = np.ascontiguousarray(a, dtype=dtype)
+        return NDBuffer(torch.from_numpy(a.reshape(-1).copy()).cuda(), a.shape)
+
+    # -- queries -------------------------------------------------------------------------------------
+    def numels(self) -> int:
+        return int(np.prod(self.shape)) if self.shape else 1
+
+    def rank(self) -> int:
+        return len(self.shape)
+
+    def is_contiguous(self) -> bool:
+        # strides.mojo:239-264: C-order strides for every dim of size > 1
+        expect = 1
+        for s, st in zip(reversed(self.shape), reversed(self.strides)):
+            if s > 1 and st != expect:
+                return False
+            expect *= s
+        return True
+
+    def data_ptr(self) -> int:
+        return self.storage.data_ptr() + self.offset * self.storage.element_size()
+
+    def mat(self):
+        return make_mat(self.storage.data_ptr(), self.shape, self.strides, self.offset)
+
+    def numpy(self) -> np.ndarray:
+        flat = self.storage.detach().cpu().numpy()
+        item = flat.dtype.itemsize
+        view = np.lib.stride_tricks.as_strided(flat[self.offset:], shape=self.shape,
+                                               strides=tuple(item * s for s in self.strides), writeable=False)
+        return np.array(view)
+
+    # -- views ---------------------------------------------------------------------------------------
+    def transpose(self, axes=(-1, -2)) -> "NDBuffer":
+        """Stride view, no copy (what matmul.mojo:37,47 passes to the backward GEMMs)."""
+        a, b = (ax % len(self.shape) for ax in axes)
+        sh, st = list(self.shape), list(self.strides)
+        sh[a], sh[b] = sh[b], sh[a]
+        st[a], st[b] = st[b], st[a]
+        return NDBuffer(self.storage, sh, st, self.offset)
+
+    def view(self, shape, strides, offset=0) -> "NDBuffer":
+        return NDBuffer(self.storage, shape, strides, self.offset + offset)
+
+    def reshape(self, shape) -> "NDBuffer":
+        if not self.is_contiguous():
+            return self.contiguous().reshape(shape)
+        return NDBuffer(self.storage, shape, None, self.offset)
+
+    def contiguous(self) -> "NDBuffer":
+        if self.is_contiguous():
+            return self
+        t = torch.as_strided(self.storage, self.shape, self.strides, self.offset).contiguous()
+        return NDBuffer(t.reshape(-1), self.shape)
+
+    # -- the hot path ----------------------------------------------------------------------------------
+    def matmul_2d(self, other: "NDBuffer") -> "NDBuffer":
+        """NDBuffer.matmul_2d (ndbuffer.mojo:2404-2443)."""
+        if self.rank() != 2 or other.rank() != 2:
+            panic("NDBuffer -> matmul_2d: both operands must be rank 2, got", self.shape, "and", other.shape)
+        return self.matmul_nd(other)
+
+    def matmul_nd(self, other: "NDBuffer") -> "NDBuffer":
+        """NDBuffer.matmul_nd (ndbuffer.mojo:2445-2501): batch dims broadcast NumPy-style."""
+        if self.rank() < 2 or other.rank() < 2:
+            panic("NDBuffer -> matmul_nd: operands must have rank >= 2")
+        m, k = self.shape[-2:]
+        k2, p = other.shape[-2:]
+        if k != k2:
+            panic("NDBuffer -> matmul_nd: inner dims must match, got", k, "and", k2)
+        try:
+            bshape = tuple(np.broadcast_shapes(self.shape[:-2], other.shape[:-2]))
+        except ValueError:
+            panic("NDBuffer -> matmul_nd: batch shapes not broadcastable:", self.shape[:-2], "vs", other.shape[:-2])
+        out = NDBuffer.empty(bshape + (m, p))
+        handle().gemm(m, p, k, self.mat(), other.mat(), out.data_ptr(), algo=_gemm_algo)
+        return out
+
+    def add_bias(self, bias: "NDBuffer") -> "NDBuffer":
+        """arithmetic_ops[Add] with a trailing-dim broadcast right operand (ndbuffer.mojo:1856-1909)."""
+        x = self.contiguous()
+        n = bias.shape[-1]
+        if x.shape[-1] != n or bias.numels() != n:
+            panic("NDBuffer -> add: shapes not broadcastable:", self.shape, "and", bias.shape)
+        out = NDBuffer.empty(x.shape)
+        handle().add_bias(x.data_ptr(), bias.contiguous().data_ptr(), out.data_ptr(), x.numels() // n, n)
+        return out
+
+    def inplace_add(self, other: "NDBuffer"):
+        """inplace_ops[Add]: the Gradbox accumulate (ndbuffer.mojo:1698-1732)."""
+        if self.shape != other.shape or not self.is_contiguous():
+            panic("NDBuffer -> inplace add: shape mismatch", self.shape, other.shape)
+        handle().add_inplace(self.data_ptr(), other.contiguous().data_ptr(), self.numels())
+
+    def fill(self, value: float):
+        handle().fill(self.data_ptr(), value, self.numels())
+
+    def sum_leading(self, target_shape) -> "NDBuffer":
+        """sum_over_broadcasted_axes (sum_mean_reduction.mojo:184-211) for the cases the path produces:
+        extra or size-1 LEADING dims (bias gradient, broadcast batch)."""
+        if tuple(self.shape) == tuple(target_shape):
+            return self
+        x = self.contiguous()
+        cols = int(np.prod(target_shape)) if len(target_shape) else 1
+        total = x.numels()
+        lead = total // cols
+        # the target must equal the trailing dims of x, up to leading 1s
+        t_core = tuple(target_shape)
+        while t_core and t_core[0] == 1:
+            t_core = t_core[1:]
+        if tuple(x.shape[len(x.shape) - len(t_core):]) != t_core or lead * cols != total:
+            panic("sum_over_broadcasted_axes: only leading axes are summed here:", self.shape, "->", target_shape)
+        out = NDBuffer.empty(target_shape)
+        handle().colsum(x.data_ptr(), lead, cols, cols, out.data_ptr())
+        return out
+
+
+class Ancestry:
+    """BackwardFnArg + parents (backpropagation.mojo:138-209, tensor.mojo:1007-1028)."""
+
+    def __init__(self, op_code: int, parents, arg=None):
+        self.op_code = op_code
+        self.parents = list(parents)
+        self.arg = arg
+
+
+class Tensor:
+    _next_id = 0
+
+    def __init__(self, buffer: NDBuffer, requires_grad: bool = False):
+        self.buffer = buffer
+        self.requires_grad = requires_grad
+        self.gradbox: NDBuffer | None = None
+        self.ancestry: Ancestry | None = None
+        Tensor._next_id += 1
+        self._id = Tensor._next_id
+
+    # -- construction ----------------------------------------------------------------------------------
+    @staticmethod
+    def from_numpy(a, requires_grad=False) -> "Tensor":
+        return Tensor(NDBuffer.from_numpy(a), requires_grad)
+
+    @staticmethod
+    def d2(rows, requires_grad=False) -> "Tensor":
+        return Tensor.from_numpy(np.asarray(rows, np.float32), requires_grad)
+
+    d1 = d3 = d2
+
+    @staticmethod
+    def zeros(*shape, requires_grad=False) -> "Tensor":
+        return Tensor(NDBuffer.zeros(shape), requires_grad)
+
+    @staticmethod
+    def ones(*shape, requires_grad=False) -> "Tensor":
+        return Tensor.from_numpy(np.ones(shape, np.float32), requires_grad)
+
+    @staticmethod
+    def labels(values, dtype=np.int64) -> "Tensor":
+        """Class-index targets; int64 is the reference's DEFAULT_INDEX_DTYPE (mnemonics.mojo:63)."""
+        return Tensor(NDBuffer.from_numpy(values, dtype=dtype))
+
+    # -- queries -----------------------------------------------------------------------------------------
+    def shape(self):
+        return self.buffer.shape
+
+    def strides(self):
+        return self.buffer.strides
+
+    def numpy(self) -> np.ndarray:
+        return self.buffer.numpy()
+
+    def item(self) -> float:
+        return float(self.buffer.numpy().reshape(-1)[0])
+
+    def grad(self) -> "Tensor":
+        if self.gradbox is None:
+            panic("Tensor -> grad: requires_grad is False or no gradient has been accumulated")
+        return Tensor(self.gradbox)
+
+    def all_close(self, other, rtol=1e-5, atol=1e-8) -> bool:
+        # buffers.mojo:1909-1946: |a - b| <= atol + rtol * |b|
+        a = self.numpy().astype(np.float64)
+        b = (other.numpy() if isinstance(other, Tensor) else np.asarray(other)).astype(np.float64)
+        return a.shape == b.shape and bool(np.all(np.abs(a - b) <= atol + rtol * np.abs(b)))
+
+    # -- views -------------------------------------------------------------------------------------------
+    def transpose(self, axes=(-1, -2)) -> "Tensor":
+        return Tensor(self.buffer.transpose(axes), requires_grad=False)
+
+    def view(self, shape, strides, offset=0) -> "Tensor":
+        return Tensor(self.buffer.view(shape, strides, offset), requires_grad=False)
+
+    # -- ops ---------------------------------------------------------------------------------------------
+    def matmul(self, other: "Tensor", track_grad: bool = True) -> "Tensor":
+        """Tensor.matmul -> Matmul.forward (tensor.mojo:4141-4159, matmul.mojo:202-241)."""
+        a, b = self.shape(), other.shape()
+        if len(a) < 2 or len(b) < 2:
+            panic("Matmul: rank-1 operands (dot / mv / vm) are not on this path; reshape to rank 2")
+        if a[-1] != b[-2]:
+            panic("Matmul: incompatible shapes", a, b)
+        two_d = len(a) == 2 and len(b) == 2
+        ndb = self.buffer.matmul_2d(other.buffer) if two_d else self.buffer.matmul_nd(other.buffer)
+        out = Tensor(ndb)
+        if track_grad and (self.requires_grad or other.requires_grad):
+            out.requires_grad = True
+            out.ancestry = Ancestry(BACKWARD_MATMUL_2D if two_d else BACKWARD_MATMUL_ND, [self, other])
+        return out
+
+    def __matmul__(self, other):
+        return self.matmul(other)
+
+    def add_bias(self, bias: "Tensor", track_grad: bool = True) -> "Tensor":
+        """Adder.forward with differing shapes => BACKWARD_ADD_BROADCAST (addition.mojo:71-112)."""
+        out = Tensor(self.buffer.add_bias(bias.buffer))
+        if track_grad and (self.requires_grad or bias.requires_grad):
+            out.requires_grad = True
+            out.ancestry = Ancestry(BACKWARD_ADD_BROADCAST, [self, bias])
+        return out
+
+    def relu(self, track_grad: bool = True) -> "Tensor":
+        """ReLU.forward: output and a float 0/1 mask kept for backward (relu.mojo:50-95)."""
+        x = self.buffer.contiguous()
+        out, mask = NDBuffer.empty(x.shape), NDBuffer.empty(x.shape)
+        handle().relu_fwd(x.data_ptr(), out.data_ptr(), mask.data_ptr(), x.numels())
+        t = Tensor(out)
+        if track_grad and self.requires_grad:
+            t.requires_grad = True
+            t.ancestry = Ancestry(BACKWARD_RELU, [self], arg=mask)
+        return t
+
+    def sigmoid(self, track_grad: bool = True) -> "Tensor":
+        """Sigmoid.forward; the output is kept for backward (sigmoid.mojo:32-53)."""
+        x = self.buffer.contiguous()
+        out = NDBuffer.empty(x.shape)
+        handle().sigmoid_fwd(x.data_ptr(), out.data_ptr(), x.numels())
+        t = Tensor(out)
+        if track_grad and self.requires_grad:
+            t.requires_grad = True
+            t.ancestry = Ancestry(BACKWARD_SIGMOID, [self], arg=out)
+        return t
+
+    def sum(self) -> "Tensor":
+        """Scalar sum of all elements (used by the reference's matmul gradient tests as the loss)."""
+        x = self.buffer.contiguous()
+        out = NDBuffer.empty(())
+        handle().colsum(x.data_ptr(), x.numels(), 1, 1, out.data_ptr())
+        t = Tensor(out)
+        if self.requires_grad:
+            t.requires_grad = True
+            t.ancestry = Ancestry(BACKWARD_SUM, [self])
+        return t
+
+    # -- autograd ------------------------------------------------------------------------------------------
+    def zero_grad(self):
+        if self.gradbox is not None:
+            self.gradbox.fill(0.0)
+
+    def seed_grad(self, value: float):
+        self.gradbox = NDBuffer.empty(self.shape())
+        self.gradbox.fill(value)
+
+    def update_grad(self, incoming: NDBuffer):
+        """Ancestor.update_grad with AddTensor: gradbox += incoming (ancestry.mojo:72-105)."""
+        if self.gradbox is None:
+            self.gradbox = NDBuffer.zeros(self.shape())
+        if tuple(incoming.shape) != tuple(self.shape()):
+            incoming = incoming.reshape(self.shape())
+        self.gradbox.inplace_add(incoming)
+
+    def backward(self, start_grad=1.0, retain_graph: bool = False):
+        """Tensor.backward (tensor.mojo:3132-3247)."""
+        if not self.requires_grad:
+            return
+        if isinstance(start_grad, Tensor):
+            self.gradbox = NDBuffer.zeros(self.shape())
+            self.gradbox.inplace_add(start_grad.buffer.reshape(self.shape()))
+        else:
+            self.seed_grad(float(start_grad))
+        # DFS: collect nodes, count fan-in (number of children that will send a gradient)
+        fan_in: dict[int, int] = {}
+        nodes: dict[int, Tensor] = {self._id: self}
+        stack = [self]
+        seen = {self._id}
+        while stack:
+            node = stack.pop()
+            if node.ancestry is None:
+                continue
+            for par in node.ancestry.parents:
+                if not par.requires_grad:
+                    continue
+                fan_in[par._id] = fan_in.get(par._id, 0) + 1
+                if par._id not in seen:
+                    seen.add(par._id)
+                    nodes[par._id] = par
+                    stack.append(par)
+        ready = deque([self])
+        while ready:
+            node = ready.popleft()
+            if node.ancestry is None:
+                continue
+            touched = Backward.invoke(node, retain_graph)
+            for par in touched:
+                fan_in[par._id] -= 1
+                if fan_in[par._id] == 0:
+                    ready.append(par)
+
+
+class Backward:
+    """Backward.invoke: if/elif dispatch on the integer tag (backpropagation.mojo:278-519)."""
+
+    @staticmethod
+    def invoke(output: Tensor, retain_graph: bool):
+        code = output.ancestry.op_code
+        if code == BACKWARD_MATMUL_2D or code == BACKWARD_MATMUL_ND:
+            return Backward.matmul(output, retain_graph)
+        elif code == BACKWARD_ADD_BROADCAST:
+            return Backward.add_broadcast(output, retain_graph)
+        elif code == BACKWARD_RELU:
+            return Backward.relu(output, retain_graph)
+        elif code == BACKWARD_SIGMOID:
+            return Backward.sigmoid(output, retain_graph)
+        elif code == BACKWARD_SUM:
+            return Backward.sum(output, retain_graph)
+        elif code in (BACKWARD_CE_CLASS_INDICES_INT64, BACKWARD_CE_CLASS_INDICES_INT32):
+            from .crossentropy import ce_class_indices_backward
+
+            return ce_class_indices_backward(output, retain_graph)
+        panic("Backward.invoke: unknown op code", code)
+
+    @staticmethod
+    def matmul(output: Tensor, retain_graph: bool):
+        """Matmul2dBackward / MatmulNdBackward (matmul.mojo:24-54,101-137): dA = dC.B^T, dB = A^T.dC on
+        transposed stride views, each only if that parent requires grad; batched results are summed back
+        over broadcast batch dims; `+=` into the parent's gradbox."""
+        grad_out = output.gradbox
+        A, B = output.ancestry.parents
+        touched = []
+        if A.requires_grad:
+            ndb = grad_out.matmul_nd(B.buffer.transpose((-1, -2)))
+            A.update_grad(ndb.sum_leading(A.shape()))
+            touched.append(A)
+        if B.requires_grad:
+            ndb = A.buffer.transpose((-1, -2)).matmul_nd(grad_out)
+            B.update_grad(ndb.sum_leading(B.shape()))
+            touched.append(B)
+        if not retain_graph:
+            grad_out.fill(0.0)
+        return touched
+
+    @staticmethod
+    def add_broadcast(output: Tensor, retain_graph: bool):
+        """BroadcastBackward[augment=False] (broadcast.mojo:17-88): the left parent gets the upstream
+        unchanged, the bias gets the upstream summed over the broadcast axes."""
+        grad_out = output.gradbox
+        left, bias = output.ancestry.parents
+        touched = []
+        if left.requires_grad:
+            left.update_grad(grad_out)
+            touched.append(left)
+        if bias.requires_grad:
+            bias.update_grad(grad_out.sum_leading(bias.shape()))
+            touched.append(bias)
+        if not retain_graph:
+            grad_out.fill(0.0)
+        return touched
+
+    @staticmethod
+    def relu(output: Tensor, retain_graph: bool):
+        """ReLUBackward: grad * mask (relu.mojo:19-46)."""
+        (parent,) = output.ancestry.parents
+        mask = output.ancestry.arg
+        g = output.gradbox
+        dx = NDBuffer.empty(g.shape)
+        handle().relu_bwd(g.data_ptr(), mask.data_ptr(), dx.data_ptr(), g.numels())
+        parent.update_grad(dx)
+        if not retain_graph:
+            g.fill(0.0)
+        return [parent]
+
+    @staticmethod
+    def sigmoid(output: Tensor, retain_graph: bool):
+        """SigmoidBackward: g * y * (1 - y) (sigmoid.mojo:9-29)."""
+        (parent,) = output.ancestry.parents
+        y = output.ancestry.arg
+        g = output.gradbox
+        dx = NDBuffer.empty(g.shape)
+        handle().sigmoid_bwd(g.data_ptr(), y.data_ptr(), dx.data_ptr(), g.numels())
+        parent.update_grad(dx)
+        if not retain_graph:
+            g.fill(0.0)
+        return [parent]
+
+    @staticmethod
+    def sum(output: Tensor, retain_graph: bool):
+        (parent,) = output.ancestry.parents
+        g = float(output.gradbox.numpy().reshape(-1)[0])
+        inc = NDBuffer.empty(parent.shape())
+        inc.fill(g)
+        parent.update_grad(inc)
+        return [parent]
