@@ -172,6 +172,93 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------------
+# MLP training legs (secondary figures on the same JSON line)
+# ---------------------------------------------------------------------------------------------------
+def measure_mlps(h, rank, world, local_rank, timed, args):
+    """wide_mlp: 4096-4096-4096-4096-1000, global batch 8192 split by rows over the ranks (strong scaling),
+    one NCCL sum all-reduce of the flat gradient bucket per step, SGD momentum 0.9.
+    mnist_mlp (1 GPU only): 784-128-32-10, batch 64, the step replayed as a CUDA graph (latency-bound:
+    samples/s and us/step, no roofline claim)."""
+    import numpy as np
+    import torch
+
+    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_broadcast_bytes
+    from tenmo_b200.trainer import MLPTrainer
+
+    out = {}
+    rng = np.random.default_rng(4321)  # same stream on every rank: identical replicas
+
+    def uniform_init(dims, limit_fn):
+        return ([rng.uniform(-1, 1, (dims[i], dims[i + 1])).astype(np.float32) * np.float32(limit_fn(dims[i], dims[i + 1]))
+                 for i in range(len(dims) - 1)], [np.zeros(d, np.float32) for d in dims[1:]])
+
+    # ---- wide MLP, data parallel ----
+    dims, gb = [4096, 4096, 4096, 4096, 1000], 8192
+    Ws, bs = uniform_init(dims, lambda i, o: np.sqrt(6.0 / i))  # "Kaiming-uniform": U(+-sqrt(6/in))
+    lo, hi = shard_rows(gb, rank, world)
+    uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(torch.device("cuda", local_rank)))
+    tr = MLPTrainer(Ws, bs, batch=hi - lo, lr=0.01, momentum=0.9, algo="3xtf32", handle=h, rank=rank, world=world,
+                    unique_id=uid, device=local_rank)
+    gen = torch.Generator(device="cpu").manual_seed(777)
+    Xg = torch.randn(gb, dims[0], generator=gen)
+    yg = torch.randint(0, dims[-1], (gb,), generator=gen)
+    Xh, yh = Xg[lo:hi].contiguous().pin_memory(), yg[lo:hi].contiguous().pin_memory()
+    tr.load_batch(Xh, yh)
+    for _ in range(3):
+        tr.step()
+    ms = timed(tr.step, args.mlp_steps)
+
+    def e2e_step():
+        tr.load_batch(Xh, yh)   # H2D of this rank's rows from pinned memory
+        tr.step()
+        tr.loss.cpu()            # D2H read of the step's loss
+
+    e2e_step()
+    ms_e2e = timed(e2e_step, args.mlp_steps)
+    flops = sum(2.0 * gb * dims[l] * dims[l + 1] * (3 if l > 0 else 2) for l in range(4))
+    out["wide_mlp"] = {
+        "metric": "mlp_train_samples_per_s", "value": gb * args.mlp_steps / (ms * 1e-3), "unit": "samples/s",
+        "ms_per_step": ms / args.mlp_steps, "tflops": flops * args.mlp_steps / (ms * 1e-3) / 1e12, "scaling": "strong",
+        "global_batch": gb, "per_rank_batch": hi - lo, "allreduce_bytes_per_step": 0 if world == 1 else tr.numel * 4,
+        "e2e_value": gb * args.mlp_steps / (ms_e2e * 1e-3), "steps": args.mlp_steps,
+        "config": "4096-4096-4096-4096-1000 Linear+ReLU, softmax-CE, fp32 (3xTF32 GEMMs), N(0,1) inputs, U(+-sqrt(6/in)) weights",
+    }
+    if world > 1:
+        h.dp_finalize()
+    del tr
+    torch.cuda.empty_cache()
+
+    # ---- MNIST-shaped MLP, one GPU ----
+    if world == 1:
+        dims = [784, 128, 32, 10]
+        Ws, bs = uniform_init(dims, lambda i, o: np.sqrt(6.0 / (i + o)))  # Xavier-uniform (net.mojo:87-116)
+        tr = MLPTrainer(Ws, bs, batch=64, lr=0.01, momentum=0.9, algo="simt", handle=h, device=local_rank)
+        pool = torch.rand(938 * 64, 784, generator=gen).cuda()   # one epoch of synthetic pixels in [0,1)
+        labels = torch.randint(0, 10, (938 * 64,), generator=gen).cuda()
+        tr.load_batch(pool[:64], labels[:64])
+        tr.capture()
+        k = [0]
+
+        def epoch_step():
+            i = k[0] % 938
+            tr.load_batch(pool[i * 64:(i + 1) * 64], labels[i * 64:(i + 1) * 64])
+            tr.replay()
+            k[0] += 1
+
+        for _ in range(20):
+            epoch_step()
+        ms = timed(epoch_step, 938)
+        out["mnist_mlp"] = {
+            "metric": "mlp_train_samples_per_s", "value": 938 * 64 / (ms * 1e-3), "unit": "samples/s",
+            "us_per_step": ms / 938 * 1e3, "steps": 938, "batch": 64, "final_loss": tr.loss_value(),
+            "config": "784-128-32-10 Linear+ReLU, softmax-CE, SGD lr 0.01 momentum 0.9, strict-fp32 GEMMs, one epoch "
+                      "(938 steps) of synthetic U[0,1) pixels, step replayed as a CUDA graph; latency-bound",
+        }
+        h.set_stream(torch.cuda.current_stream(local_rank).cuda_stream)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------
 def run_gpu_arm(args):
@@ -265,6 +352,11 @@ def run_gpu_arm(args):
     ms_e2e = timed(step_e2e, args.steps)
     h.check_device_status()
 
+    # release the GEMM buffers before the MLP legs
+    del A, B, dC, C, dA, dB, host_in, host_out
+    torch.cuda.empty_cache()
+    mlp = None if args.no_mlp else measure_mlps(h, rank, world, local_rank, timed, args)
+
     flop_step = 6.0 * M * N * K
     value = flop_step * world * args.steps / (ms_dev * 1e-3) / 1e12
     e2e_value = flop_step * world * args.steps / (ms_e2e * 1e-3) / 1e12
@@ -298,6 +390,8 @@ def run_gpu_arm(args):
                          "unit": UNIT, "frac": (achieved / peak) if achieved else None, "traffic": None,
                          "launches_timed": n_kernel, "avg_launch_ms": kernel_ms / max(n_kernel, 1), "peak_note": peak_note},
         }
+        if mlp:
+            out.update(mlp)
         if world == 1 and not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline(args.cpu_budget)
         print(json.dumps(out), flush=True)
@@ -317,6 +411,8 @@ def main():
     ap.add_argument("--ref-size", type=int, default=2048, help="CPU sample size for --impl reference")
     ap.add_argument("--cpu-budget", type=float, default=20.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-mlp", action="store_true", help="skip the MLP training legs")
+    ap.add_argument("--mlp-steps", type=int, default=20)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

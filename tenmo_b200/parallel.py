@@ -1,0 +1,57 @@
+"""Host-side logic of batch-sharded data-parallel training (one process per GPU).
+
+The reference has no distributed layer (its README lists it as future work), so there is nothing to
+mirror here; this is the plumbing around ``tenmo_dp_*``: which rows a rank owns, how the NCCL unique id
+travels from rank 0 to the others, and the gradient-averaging rule.  Everything in this module runs
+without a GPU (the collective is passed in), so it is tested with gloo ranks on CPU.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def shard_rows(global_batch: int, rank: int, world: int) -> tuple[int, int]:
+    """[begin, end) of the consecutive rows rank ``rank`` owns.  The global batch must divide evenly:
+    with equal shards the mean of the per-rank mean losses is the global mean, and a sum all-reduce
+    scaled by 1/world is the global-batch gradient."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} for world {world}")
+    if global_batch % world != 0:
+        raise ValueError(f"global batch {global_batch} does not split evenly over {world} ranks")
+    per = global_batch // world
+    return rank * per, (rank + 1) * per
+
+
+def exchange_unique_id(get_unique_id, rank: int, world: int, broadcast_bytes) -> bytes | None:
+    """Rank 0 draws the 128-byte NCCL id (``get_unique_id()``), everyone receives it through
+    ``broadcast_bytes(buf: bytearray, src=0)`` -- any out-of-band channel (a torch.distributed gloo / nccl
+    broadcast, a file, a TCP store).  Returns None when world == 1."""
+    if world == 1:
+        return None
+    buf = bytearray(128)
+    if rank == 0:
+        uid = get_unique_id()
+        if len(uid) != 128:
+            raise ValueError("unique id must be 128 bytes")
+        buf[:] = uid
+    broadcast_bytes(buf, 0)
+    return bytes(buf)
+
+
+def torch_broadcast_bytes(device=None):
+    """A ``broadcast_bytes`` built on the default torch.distributed process group."""
+    import torch
+    import torch.distributed as dist
+
+    def bcast(buf: bytearray, src: int):
+        t = torch.tensor(list(buf), dtype=torch.uint8, device=device)
+        dist.broadcast(t, src)
+        buf[:] = bytes(t.cpu().tolist())
+
+    return bcast
+
+
+def averaged_gradients(local_grads: np.ndarray, allreduce_sum, world: int) -> np.ndarray:
+    """sum over ranks, then 1/world: what the fused SGD kernel applies through ``grad_scale``."""
+    total = allreduce_sum(np.ascontiguousarray(local_grads, np.float32))
+    return total * np.float32(1.0 / world)

@@ -25,7 +25,10 @@ BACKWARD_MATMUL_2D = 4
 BACKWARD_SIGMOID = 7
 BACKWARD_CE_CLASS_INDICES_INT32 = 9
 BACKWARD_SUM = 16
+BACKWARD_MATRIX_VECTOR_MUL = 20
+BACKWARD_VECTOR_MATMUL = 21
 BACKWARD_ADD_BROADCAST = 23
+BACKWARD_DOT = 30
 BACKWARD_CE_CLASS_INDICES_INT64 = 66
 
 _handles: dict[int, TenmoCuda] = {}
@@ -128,6 +131,13 @@ class NDBuffer:
 
     def view(self, shape, strides, offset=0) -> "NDBuffer":
         return NDBuffer(self.storage, shape, strides, self.offset + offset)
+
+    def unsqueeze(self, axis: int) -> "NDBuffer":
+        """Insert a size-1 dim as a view (its stride is never used)."""
+        sh, st = list(self.shape), list(self.strides)
+        sh.insert(axis, 1)
+        st.insert(axis, 1)
+        return NDBuffer(self.storage, sh, st, self.offset)
 
     def reshape(self, shape) -> "NDBuffer":
         if not self.is_contiguous():
@@ -278,11 +288,14 @@ class Tensor:
         return Tensor(self.buffer.view(shape, strides, offset), requires_grad=False)
 
     # -- ops ---------------------------------------------------------------------------------------------
-    def matmul(self, other: "Tensor", track_grad: bool = True) -> "Tensor":
-        """Tensor.matmul -> Matmul.forward (tensor.mojo:4141-4159, matmul.mojo:202-241)."""
+    def matmul(self, other: "Tensor", track_grad: bool = True, mode: str = "mm") -> "Tensor":
+        """Tensor.matmul -> Matmul.forward (tensor.mojo:4141-4159, matmul.mojo:202-241).  ``mode`` mirrors the
+        reference's compile-time ``mode`` parameter: "mm" classifies by rank, "mv" / "vm" / "dot" force it."""
         a, b = self.shape(), other.shape()
-        if len(a) < 2 or len(b) < 2:
-            panic("Matmul: rank-1 operands (dot / mv / vm) are not on this path; reshape to rank 2")
+        if mode != "mm":
+            return self._matmul_rank1(other, track_grad, mode)
+        if len(a) <= 1 or len(b) <= 1:  # classify_matmul (matmul.mojo:258-272): dot / vm / mv
+            return self._matmul_rank1(other, track_grad)
         if a[-1] != b[-2]:
             panic("Matmul: incompatible shapes", a, b)
         two_d = len(a) == 2 and len(b) == 2
@@ -291,6 +304,33 @@ class Tensor:
         if track_grad and (self.requires_grad or other.requires_grad):
             out.requires_grad = True
             out.ancestry = Ancestry(BACKWARD_MATMUL_2D if two_d else BACKWARD_MATMUL_ND, [self, other])
+        return out
+
+    def _matmul_rank1(self, other: "Tensor", track_grad: bool, kind: str | None = None) -> "Tensor":
+        """dot, vector @ matrix and matrix @ vector (dotproduct.mojo, vectormatrix.mojo:210-375,
+        matrixvector.mojo:205-402) as GEMMs with a unit dimension: the vector becomes a (1,k) row or a (k,1)
+        column view, batch dims broadcast as usual, and the unit dim is dropped from the result."""
+        a, b = self.shape(), other.shape()
+        if len(a) == 0 or len(b) == 0:
+            panic("Matmul: scalar operands")
+        if kind is None:
+            kind = "dot" if (len(a) == 1 and len(b) == 1) else ("vm" if len(a) == 1 else "mv")
+        if kind == "dot":
+            code, la, lb, drop = BACKWARD_DOT, self.buffer.unsqueeze(0), other.buffer.unsqueeze(1), (-1, -2)
+        elif kind == "vm":  # v[..., k] @ M[..., k, n] -> [..., n]
+            code, la, lb, drop = BACKWARD_VECTOR_MATMUL, self.buffer.unsqueeze(len(a) - 1), other.buffer, (-2,)
+        else:  # M[..., m, k] @ v[..., k] -> [..., m]
+            code, la, lb, drop = BACKWARD_MATRIX_VECTOR_MUL, self.buffer, other.buffer.unsqueeze(len(b)), (-1,)
+        if la.shape[-1] != lb.shape[-2]:
+            panic("Matmul: incompatible shapes", a, b)
+        full = la.matmul_nd(lb)
+        shape = list(full.shape)
+        for d in sorted((ax % len(shape) for ax in drop), reverse=True):
+            del shape[d]
+        out = Tensor(full.reshape(tuple(shape)))
+        if track_grad and (self.requires_grad or other.requires_grad):
+            out.requires_grad = True
+            out.ancestry = Ancestry(code, [self, other], arg=dict(la=la, lb=lb, full_shape=full.shape))
         return out
 
     def __matmul__(self, other):
@@ -408,6 +448,8 @@ class Backward:
             return Backward.sigmoid(output, retain_graph)
         elif code == BACKWARD_SUM:
             return Backward.sum(output, retain_graph)
+        elif code in (BACKWARD_MATRIX_VECTOR_MUL, BACKWARD_VECTOR_MATMUL, BACKWARD_DOT):
+            return Backward.matmul_rank1(output, retain_graph)
         elif code in (BACKWARD_CE_CLASS_INDICES_INT64, BACKWARD_CE_CLASS_INDICES_INT32):
             from .crossentropy import ce_class_indices_backward
 
@@ -432,6 +474,28 @@ class Backward:
             touched.append(B)
         if not retain_graph:
             grad_out.fill(0.0)
+        return touched
+
+    @staticmethod
+    def matmul_rank1(output: Tensor, retain_graph: bool):
+        """MatrixVectorMulNdBackward / VectorMatmulNdBackward / dot backward (matrixvector.mojo:15-201,
+        vectormatrix.mojo:14-206): the outer-product and gemv gradients are the two backward GEMMs of the
+        unit-dimension matmul, summed over broadcast batch dims back to each parent's shape."""
+        arg = output.ancestry.arg
+        la, lb = arg["la"], arg["lb"]
+        A, B = output.ancestry.parents
+        g = output.gradbox.reshape(arg["full_shape"])
+        touched = []
+        if A.requires_grad:
+            ndb = g.matmul_nd(lb.transpose((-1, -2)))
+            A.update_grad(ndb.sum_leading(la.shape).reshape(A.shape()))
+            touched.append(A)
+        if B.requires_grad:
+            ndb = la.transpose((-1, -2)).matmul_nd(g)
+            B.update_grad(ndb.sum_leading(lb.shape).reshape(B.shape()))
+            touched.append(B)
+        if not retain_graph:
+            output.gradbox.fill(0.0)
         return touched
 
     @staticmethod

@@ -1,0 +1,198 @@
+"""A whole Linear/ReLU/softmax-CE/SGD training step as one pre-planned sequence of C-ABI calls.
+
+This is the call sequence tenmo's host makes for ``Sequential(Linear, ReLU, ..., Linear)`` +
+``CrossEntropyLoss`` + ``SGD`` (net.mojo:1085-1092, crossentropy.mojo:1360-1391, tensor.mojo:3154-3247,
+optim.mojo:405-543) with the host round trips taken out so that it can be replayed as a CUDA graph:
+
+  forward   per layer ONE GEMM with the bias add, ReLU and the 0/1 mask in its epilogue
+  loss      fused cross-entropy forward + backward, loss and valid count stay on the device
+  backward  per layer dW = X^T . dY (db rides along as the column sum of dY) and dX = dY . W^T on
+            transposed stride views, then the ReLU mask multiply
+  exchange  (data parallel) one NCCL sum all-reduce of the flat gradient bucket
+  update    ONE SGD-momentum launch over the flat parameter / gradient / velocity buffers,
+            1/world folded into it
+
+All parameters live in one flat buffer (weights and biases back to back), and so do gradients and
+velocities, which is what makes the single all-reduce and the single optimizer launch possible.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import lib as _lib
+from .lib import TenmoCuda, make_mat
+from .parallel import shard_rows
+
+
+class MLPTrainer:
+    def __init__(self, weights, biases, batch: int, lr: float = 0.01, momentum: float = 0.9, weight_decay: float = 0.0,
+                 algo: str = "auto", handle: TenmoCuda | None = None, rank: int = 0, world: int = 1,
+                 unique_id: bytes | None = None, device: int | None = None):
+        self.dev = torch.cuda.current_device() if device is None else device
+        self.h = handle or TenmoCuda(self.dev).require()
+        self.algo = {"auto": _lib.ALGO_AUTO, "simt": _lib.ALGO_SIMT_FP32, "3xtf32": _lib.ALGO_TC_3XTF32}[algo]
+        self.rank, self.world = rank, world
+        self.lr, self.momentum, self.wd = float(lr), float(momentum), float(weight_decay)
+        self.batch = int(batch)
+        self.dims = [int(weights[0].shape[0])] + [int(w.shape[1]) for w in weights]
+        self.L = len(weights)
+        f32 = dict(dtype=torch.float32, device=f"cuda:{self.dev}")
+        # flat parameter / gradient / velocity buffers; every slice starts on a 16-byte boundary
+        sizes, offs, off = [], [], 0
+        for l in range(self.L):
+            for n in (self.dims[l] * self.dims[l + 1], self.dims[l + 1]):
+                offs.append(off)
+                sizes.append(n)
+                off += (n + 3) // 4 * 4
+        self.numel = off
+        self.P = torch.zeros(off, **f32)
+        self.G = torch.zeros(off, **f32)
+        self.V = torch.zeros(off, **f32)
+        self.W = [self.P[offs[2 * l]:offs[2 * l] + sizes[2 * l]].view(self.dims[l], self.dims[l + 1]) for l in range(self.L)]
+        self.b = [self.P[offs[2 * l + 1]:offs[2 * l + 1] + sizes[2 * l + 1]] for l in range(self.L)]
+        self.dW = [self.G[offs[2 * l]:offs[2 * l] + sizes[2 * l]].view(self.dims[l], self.dims[l + 1]) for l in range(self.L)]
+        self.db = [self.G[offs[2 * l + 1]:offs[2 * l + 1] + sizes[2 * l + 1]] for l in range(self.L)]
+        for l in range(self.L):
+            self.W[l].copy_(torch.from_numpy(np.ascontiguousarray(weights[l], np.float32)))
+            self.b[l].copy_(torch.from_numpy(np.ascontiguousarray(biases[l], np.float32)))
+        B = self.batch
+        self.X = torch.zeros(B, self.dims[0], **f32)
+        self.y = torch.zeros(B, dtype=torch.int64, device=f"cuda:{self.dev}")
+        self.act = [self.X] + [torch.empty(B, d, **f32) for d in self.dims[1:]]
+        self.mask = [torch.empty(B, d, **f32) for d in self.dims[1:-1]]
+        self.gout = [torch.empty(B, d, **f32) for d in self.dims[1:]]     # dL/d(pre-activation) of layer l
+        self.gact = [torch.empty(B, d, **f32) for d in self.dims[1:-1]]   # dL/d(activation) before the mask
+        self.softmax = torch.empty(B, self.dims[-1], **f32)
+        self.loss = torch.zeros(1, **f32)
+        self.valid = torch.zeros(1, dtype=torch.int32, device=f"cuda:{self.dev}")
+        self.correct = torch.zeros(1, dtype=torch.int64, device=f"cuda:{self.dev}")
+        self.graph = None
+        self._stream = None
+        if world > 1:
+            self.h.dp_init(rank, world, unique_id)
+        torch.cuda.synchronize(self.dev)
+
+    # ------------------------------------------------------------------------------------------------
+    def _m(self, t: torch.Tensor, transpose: bool = False):
+        r, c = t.shape
+        if transpose:
+            return make_mat(t.data_ptr(), (c, r), (1, c))
+        return make_mat(t.data_ptr(), (r, c), (c, 1))
+
+    def _enqueue(self, update: bool = True):
+        """Queue one step on the context's current stream (no host synchronisation anywhere)."""
+        h, L, B = self.h, self.L, self.batch
+        for l in range(L):  # forward
+            last = l == L - 1
+            h.gemm(B, self.dims[l + 1], self.dims[l], self._m(self.act[l]), self._m(self.W[l]), self.act[l + 1].data_ptr(),
+                   algo=self.algo, bias=self.b[l].data_ptr(), act=_lib.ACT_NONE if last else _lib.ACT_RELU,
+                   aux=0 if last else self.mask[l].data_ptr())
+        C = self.dims[-1]
+        h.ce_fwd(self.act[L].data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
+                 self.loss.data_ptr(), self.valid.data_ptr())
+        h.ce_bwd(self.softmax.data_ptr(), self.y.data_ptr(), True, B, C, -100, 0.0, 0, 0, self.valid.data_ptr(),
+                 self.gout[L - 1].data_ptr())
+        for l in range(L - 1, -1, -1):  # backward
+            g = self.gout[l]
+            # dW = X^T . dY, db = column sum of dY (same call)
+            h.gemm(self.dims[l], self.dims[l + 1], B, self._m(self.act[l], transpose=True), self._m(g),
+                   self.dW[l].data_ptr(), algo=self.algo, colsum=self.db[l].data_ptr())
+            if l > 0:  # the network input needs no gradient (matmul.mojo:34)
+                h.gemm(B, self.dims[l], self.dims[l + 1], self._m(g), self._m(self.W[l], transpose=True),
+                       self.gact[l - 1].data_ptr(), algo=self.algo)
+                h.relu_bwd(self.gact[l - 1].data_ptr(), self.mask[l - 1].data_ptr(), self.gout[l - 1].data_ptr(),
+                           B * self.dims[l])
+        if not update:
+            return
+        if self.world > 1:
+            h.dp_allreduce_sum(self.G.data_ptr(), self.numel)
+        h.sgd_step([self.P.data_ptr()], [self.G.data_ptr()], [self.V.data_ptr()], [self.numel], self.lr, self.momentum,
+                   self.wd, 1.0 / self.world)
+
+    # ------------------------------------------------------------------------------------------------
+    def load_batch(self, X, y):
+        """Copy a (batch, in) fp32 array and (batch,) int64 labels into the step's static input buffers
+        (host arrays / pinned tensors are copied asynchronously on the current stream)."""
+        if not torch.is_tensor(X):
+            X = torch.from_numpy(np.ascontiguousarray(X, np.float32))
+        if not torch.is_tensor(y):
+            y = torch.from_numpy(np.ascontiguousarray(y, np.int64))
+        self.X.copy_(X, non_blocking=True)
+        self.y.copy_(y, non_blocking=True)
+
+    def step(self, X=None, y=None, update: bool = True):
+        """One training step, eagerly enqueued.  Returns nothing; read ``loss`` / ``logits()`` afterwards."""
+        self.h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
+        if X is not None:
+            self.load_batch(X, y)
+        self._enqueue(update)
+
+    def capture(self):
+        """Record the step once into a CUDA graph; ``replay()`` then costs one launch per step."""
+        side = torch.cuda.Stream(self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(side):
+            self.h.set_stream(side.cuda_stream)
+            snap = (self.P.clone(), self.V.clone())
+            for _ in range(2):  # warm up: grow the workspace and load every kernel before capture
+                self._enqueue(True)
+            side.synchronize()
+            self.P.copy_(snap[0])
+            self.V.copy_(snap[1])
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                self._enqueue(True)
+        torch.cuda.current_stream(self.dev).wait_stream(side)
+        self.P.copy_(snap[0])  # the capture itself does not run, but keep the state explicit
+        self.V.copy_(snap[1])
+        self.h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
+
+    def replay(self):
+        self.graph.replay()
+
+    # ------------------------------------------------------------------------------------------------
+    def logits(self) -> np.ndarray:
+        return self.act[self.L].detach().cpu().numpy()
+
+    def loss_value(self) -> float:
+        return float(self.loss.item())
+
+    def accuracy(self) -> int:
+        self.h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
+        C = self.dims[-1]
+        return self.h.accuracy(self.act[self.L].data_ptr(), C, self.y.data_ptr(), True, self.batch, C, self.correct.data_ptr())
+
+    def weights(self):
+        return [w.detach().cpu().numpy() for w in self.W]
+
+    def biases(self):
+        return [b.detach().cpu().numpy() for b in self.b]
+
+    def flops_per_step(self) -> float:
+        """Algorithmic flop of one step on this rank: forward + dW for every layer, dX for layers 2..L."""
+        f = 0.0
+        for l in range(self.L):
+            mnk = self.batch * self.dims[l] * self.dims[l + 1]
+            f += 2.0 * mnk * (3 if l > 0 else 2)
+        return f
+
+    def state_dict(self) -> dict:
+        """Parameters under the reference's checkpoint names ("<idx>.weight"/"<idx>.bias" with the module
+        index of Sequential(Linear, ReLU, ...), numpy_interop.mojo:166-196) plus the SGD velocities."""
+        out = {}
+        for l in range(self.L):
+            out[f"{2 * l}.weight"] = self.W[l].detach().cpu().numpy()
+            out[f"{2 * l}.bias"] = self.b[l].detach().cpu().numpy()
+        out["__velocity__"] = self.V.detach().cpu().numpy()
+        return out
+
+    def load_state_dict(self, sd: dict):
+        for l in range(self.L):
+            self.W[l].copy_(torch.from_numpy(np.ascontiguousarray(sd[f"{2 * l}.weight"], np.float32)))
+            self.b[l].copy_(torch.from_numpy(np.ascontiguousarray(sd[f"{2 * l}.bias"], np.float32)))
+        if "__velocity__" in sd:
+            self.V.copy_(torch.from_numpy(np.ascontiguousarray(sd["__velocity__"], np.float32)))
+
+
+__all__ = ["MLPTrainer", "shard_rows"]

@@ -1,0 +1,89 @@
+"""Data-parallel training over NCCL: two ranks on two GPUs equal one rank on the global batch.
+
+Runs as child processes, one per GPU (skipped with fewer than two GPUs).  NVLS is switched off and every
+rank leaves only between steps, as this pool asks of multi-process GPU tests.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _problem():
+    rng = np.random.default_rng(31)
+    dims = [256, 192, 128, 10]
+    Ws = [rng.uniform(-1, 1, (dims[i], dims[i + 1])).astype(np.float32) * np.float32(np.sqrt(6.0 / dims[i])) for i in range(3)]
+    bs = [np.zeros(d, np.float32) for d in dims[1:]]
+    X = rng.standard_normal((4, 128, 256)).astype(np.float32)  # 4 steps of a 128-row global batch
+    y = rng.integers(0, 10, (4, 128))
+    return Ws, bs, X, y
+
+
+def _worker(rank, world, port, out_dir):
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    import torch.distributed as dist
+
+    from tenmo_b200 import TenmoCuda
+    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_broadcast_bytes
+    from tenmo_b200.trainer import MLPTrainer
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        h = TenmoCuda(rank).require()
+        uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes())
+        Ws, bs, X, y = _problem()
+        lo, hi = shard_rows(128, rank, world)
+        tr = MLPTrainer(Ws, bs, batch=hi - lo, lr=0.05, momentum=0.9, algo="simt", handle=h, rank=rank, world=world,
+                        unique_id=uid, device=rank)
+        losses = []
+        for s in range(4):
+            tr.step(X[s, lo:hi], y[s, lo:hi])
+            losses.append(tr.loss_value())
+        torch.cuda.synchronize()
+        h.check_device_status()
+        np.save(os.path.join(out_dir, f"w{rank}.npy"), np.concatenate([w.reshape(-1) for w in tr.weights() + tr.biases()]))
+        np.save(os.path.join(out_dir, f"l{rank}.npy"), np.array(losses))
+        dist.barrier()  # leave only between steps, with nothing in flight
+        h.dp_finalize()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_equal_one_rank_on_the_global_batch(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    from tenmo_b200.trainer import MLPTrainer
+
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    Ws, bs, X, y = _problem()
+    single = MLPTrainer(Ws, bs, batch=128, lr=0.05, momentum=0.9, algo="simt")
+    losses = []
+    for s in range(4):
+        single.step(X[s], y[s])
+        losses.append(single.loss_value())
+    ref = np.concatenate([w.reshape(-1) for w in single.weights() + single.biases()])
+    w0, w1 = np.load(tmp_path / "w0.npy"), np.load(tmp_path / "w1.npy")
+    assert np.array_equal(w0, w1), "replicas diverged"
+    # summation order differs (two half-batch sums added by NCCL vs one full-batch chain): 1e-5 relative
+    assert np.max(np.abs(w0 - ref)) <= 1e-5 * np.max(np.abs(ref))
+    l0, l1 = np.load(tmp_path / "l0.npy"), np.load(tmp_path / "l1.npy")
+    assert np.allclose((l0 + l1) / 2, losses, rtol=1e-5, atol=1e-6)  # mean of rank means == global mean
