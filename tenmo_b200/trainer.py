@@ -82,8 +82,14 @@ class MLPTrainer:
 
     def _enqueue(self, update: bool = True):
         """Queue one step on the context's current stream (no host synchronisation anywhere)."""
+        self._forward()
+        self._backward()
+        if update:
+            self._update()
+
+    def _forward(self):
         h, L, B = self.h, self.L, self.batch
-        for l in range(L):  # forward
+        for l in range(L):
             last = l == L - 1
             h.gemm(B, self.dims[l + 1], self.dims[l], self._m(self.act[l]), self._m(self.W[l]), self.act[l + 1].data_ptr(),
                    algo=self.algo, bias=self.b[l].data_ptr(), act=_lib.ACT_NONE if last else _lib.ACT_RELU,
@@ -91,9 +97,13 @@ class MLPTrainer:
         C = self.dims[-1]
         h.ce_fwd(self.act[L].data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
                  self.loss.data_ptr(), self.valid.data_ptr())
+
+    def _backward(self):
+        h, L, B = self.h, self.L, self.batch
+        C = self.dims[-1]
         h.ce_bwd(self.softmax.data_ptr(), self.y.data_ptr(), True, B, C, -100, 0.0, 0, 0, self.valid.data_ptr(),
                  self.gout[L - 1].data_ptr())
-        for l in range(L - 1, -1, -1):  # backward
+        for l in range(L - 1, -1, -1):
             g = self.gout[l]
             # dW = X^T . dY, db = column sum of dY (same call)
             h.gemm(self.dims[l], self.dims[l + 1], B, self._m(self.act[l], transpose=True), self._m(g),
@@ -103,8 +113,9 @@ class MLPTrainer:
                        self.gact[l - 1].data_ptr(), algo=self.algo)
                 h.relu_bwd(self.gact[l - 1].data_ptr(), self.mask[l - 1].data_ptr(), self.gout[l - 1].data_ptr(),
                            B * self.dims[l])
-        if not update:
-            return
+
+    def _update(self):
+        h = self.h
         if self.world > 1:
             h.dp_allreduce_sum(self.G.data_ptr(), self.numel)
         h.sgd_step([self.P.data_ptr()], [self.G.data_ptr()], [self.V.data_ptr()], [self.numel], self.lr, self.momentum,

@@ -76,20 +76,31 @@ def test_wide_mlp_tensor_core_step_matches_oracle(oracle):
     scale = np.max(np.abs(r_logits))
     assert np.max(np.abs(tr.logits() - r_logits)) <= 1e-4 * scale
     assert abs(tr.loss_value() - r_loss) <= 1e-4
-    # Gradients: ReLU is discontinuous, so a pre-activation that the two paths place on opposite sides of
-    # zero (|z| below the 3xTF32 error, about a dozen of the 1.5 M hidden units here) flips one mask entry
-    # and moves the gradient entries it feeds by one term of their sum.  The last layer's gradients do not
-    # pass through a mask and are held to 1e-4 of the largest entry; the layers below are held to 1e-3 in
-    # the Frobenius norm.  The GEMMs themselves are held to 1e-4 per element in test_gpu_gemm_tc.py.
+    # Gradients.  ReLU is discontinuous: a pre-activation the two paths place on opposite sides of zero (one
+    # or two of the 1.5 M hidden units here) flips a mask entry, and ONE flip moves a weight-gradient column
+    # by a whole sample's contribution (~1e-3 of the gradient's norm).  That is a property of comparing any
+    # two roundings of the forward pass, not of the backward kernels, so the backward pass is checked with
+    # the oracle's masks forced in (teacher forcing), which leaves only smooth error propagation: the
+    # relative error of d(loss)/d(logits) equals the absolute logit error (~1e-4 here), and the backward
+    # GEMMs add their own 3xTF32 rounding.  Bar: 5e-4 of the largest entry, per gradient tensor.
+    h = X
+    masks = []
+    for l in range(3):
+        out, m = oracle.relu_fwd(oracle.add_bias(oracle.matmul(h, Ws[l], threads=4), bs[l]))
+        masks.append(m)
+        h = out
+    flips = 0
+    for l in range(3):
+        flips += int(np.sum(tr.mask[l].cpu().numpy() != masks[l]))
+        tr.mask[l].copy_(torch.from_numpy(masks[l]))
+    assert flips <= 16, f"{flips} ReLU masks differ from the oracle's"
+    tr._backward()
+    torch.cuda.synchronize()
     for l in range(4):
         g, rg = tr.dW[l].cpu().numpy(), ref.dW[l]
         gb, rgb = tr.db[l].cpu().numpy(), ref.db[l]
-        if l == 3:
-            assert np.max(np.abs(g - rg)) <= 1e-4 * np.max(np.abs(rg)), f"dW[{l}]"
-            assert np.max(np.abs(gb - rgb)) <= 1e-4 * np.max(np.abs(rgb)), f"db[{l}]"
-        else:
-            assert np.linalg.norm(g - rg) <= 1e-3 * np.linalg.norm(rg), f"dW[{l}]"
-            assert np.linalg.norm(gb - rgb) <= 1e-3 * np.linalg.norm(rgb), f"db[{l}]"
+        assert np.max(np.abs(g - rg)) <= 5e-4 * np.max(np.abs(rg)), f"dW[{l}]"
+        assert np.max(np.abs(gb - rgb)) <= 5e-4 * np.max(np.abs(rgb)), f"db[{l}]"
     # near-ties aside, predictions agree; count disagreements instead of demanding zero on a 3xTF32 path
     assert np.mean(np.argmax(tr.logits(), 1) == np.argmax(r_logits, 1)) >= 0.999
     tr.h.check_device_status()
