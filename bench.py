@@ -400,6 +400,75 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------------
+# HBM-bound kernels of the path against the bandwidth roofline
+# ---------------------------------------------------------------------------------------------------
+def run_kernel_rooflines(args):
+    """One JSON line per kernel: algorithmic bytes per launch / CUDA-event time, against the measured copy
+    bandwidth.  Shapes are the wide-MLP ones (per-rank batch 8192).  Every kernel cycles through enough
+    distinct buffers that the working set exceeds the 126 MB L2."""
+    import torch
+
+    from tenmo_b200 import TenmoCuda
+
+    torch.cuda.set_device(0)
+    h = TenmoCuda(0).require()
+    stream = torch.cuda.current_stream()
+    h.set_stream(stream.cuda_stream)
+    peaks = load_peaks()
+    f32 = dict(dtype=torch.float32, device="cuda")
+
+    def report(name, alg_bytes, fn, iters=40, note=""):
+        for i in range(5):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(iters):
+            fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        gbs = alg_bytes / (ms * 1e-3) / 1e9
+        print(json.dumps({"kernel": name, "avg_launch_ms": ms, "roofline": {
+            "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+            "traffic": None, "peak_note": f"{peaks['source']} copy bandwidth"}, "algorithmic_bytes": alg_bytes,
+            "note": note}), flush=True)
+
+    M, N, C = 8192, 4096, 1000
+    R = 4  # rotating buffers: 4 x 134 MB
+    xs = [torch.randn(M, N, **f32) for _ in range(R)]
+    out = torch.empty(N, **f32)
+    report("colsum_split_kernel", 4.0 * M * N + 4.0 * N,
+           lambda i: h.colsum(xs[i % R].data_ptr(), M, N, N, out.data_ptr()), note=f"bias gradient of a ({M},{N}) activation gradient")
+    ys = [torch.empty(M, N, **f32) for _ in range(2)]
+    report("ew_kernel<relu_bwd>", 12.0 * M * N,
+           lambda i: h.relu_bwd(xs[i % R].data_ptr(), xs[(i + 1) % R].data_ptr(), ys[i % 2].data_ptr(), M * N),
+           note="dx = g * mask")
+    report("add_bias_kernel", 8.0 * M * N + 4.0 * N,
+           lambda i: h.add_bias(xs[i % R].data_ptr(), out.data_ptr(), ys[i % 2].data_ptr(), M, N), note="un-fused bias add")
+    del ys
+    # SGD over the wide MLP's 54.4 M parameters (218 MB each of p, g, v)
+    n = 54440936
+    p, g, v = (torch.randn(n, **f32) * 0.01 for _ in range(3))
+    report("sgd_kernel", 20.0 * n, lambda i: h.sgd_step([p.data_ptr()], [g.data_ptr()], [v.data_ptr()], [n], 0.01, 0.9, 0.0, 1.0),
+           note="momentum 0.9, one flat tensor of 54.4 M parameters")
+    del p, g, v, xs
+    # cross-entropy at (8192, 1000): 32 MB per matrix, so rotate 8 logits / softmax pairs
+    R = 8
+    logits = [torch.randn(M, C, **f32) for _ in range(R)]
+    sm = [torch.empty(M, C, **f32) for _ in range(R)]
+    labels = torch.randint(0, C, (M,), device="cuda")
+    loss, valid = torch.zeros(1, **f32), torch.zeros(1, dtype=torch.int32, device="cuda")
+    report("ce_fwd_kernel", 8.0 * M * C + 8.0 * M,
+           lambda i: h.ce_fwd(logits[i % R].data_ptr(), C, labels.data_ptr(), True, M, C, -100, 0.0, 0, sm[i % R].data_ptr(),
+                              loss.data_ptr(), valid.data_ptr()), note="softmax kept for backward, loss finished on the device")
+    report("ce_bwd_kernel", 8.0 * M * C + 8.0 * M,
+           lambda i: h.ce_bwd(sm[i % R].data_ptr(), labels.data_ptr(), True, M, C, -100, 0.0, 0, 0, valid.data_ptr(),
+                              logits[i % R].data_ptr()))
+    h.check_device_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -413,9 +482,13 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-mlp", action="store_true", help="skip the MLP training legs")
     ap.add_argument("--mlp-steps", type=int, default=20)
+    ap.add_argument("--kernels", action="store_true",
+                    help="time the bandwidth-bound kernels of the path against the HBM roofline (one JSON line each)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.kernels:
+        run_kernel_rooflines(args)
     else:
         run_gpu_arm(args)
 

@@ -28,7 +28,7 @@ from .parallel import shard_rows
 class MLPTrainer:
     def __init__(self, weights, biases, batch: int, lr: float = 0.01, momentum: float = 0.9, weight_decay: float = 0.0,
                  algo: str = "auto", handle: TenmoCuda | None = None, rank: int = 0, world: int = 1,
-                 unique_id: bytes | None = None, device: int | None = None):
+                 unique_id: bytes | None = None, device: int | None = None, overlap: bool = True):
         self.dev = torch.cuda.current_device() if device is None else device
         self.h = handle or TenmoCuda(self.dev).require()
         self.algo = {"auto": _lib.ALGO_AUTO, "simt": _lib.ALGO_SIMT_FP32, "3xtf32": _lib.ALGO_TC_3XTF32}[algo]
@@ -69,6 +69,11 @@ class MLPTrainer:
         self.correct = torch.zeros(1, dtype=torch.int64, device=f"cuda:{self.dev}")
         self.graph = None
         self._stream = None
+        # [start, count) of each layer's weight + bias inside the flat buffers
+        self.layer_span = [(offs[2 * l], offs[2 * l + 1] + (sizes[2 * l + 1] + 3) // 4 * 4 - offs[2 * l])
+                           for l in range(self.L)]
+        self.overlap = overlap and world > 1
+        self._side = torch.cuda.Stream(self.dev) if self.overlap else None
         if world > 1:
             self.h.dp_init(rank, world, unique_id)
         torch.cuda.synchronize(self.dev)
@@ -83,9 +88,12 @@ class MLPTrainer:
     def _enqueue(self, update: bool = True):
         """Queue one step on the context's current stream (no host synchronisation anywhere)."""
         self._forward()
-        self._backward()
-        if update:
-            self._update()
+        if update and self.overlap:
+            self._backward(exchange=True)  # per-layer all-reduce + SGD on the side stream, under the backward GEMMs
+        else:
+            self._backward()
+            if update:
+                self._update()
 
     def _forward(self):
         h, L, B = self.h, self.L, self.batch
@@ -98,7 +106,22 @@ class MLPTrainer:
         h.ce_fwd(self.act[L].data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
                  self.loss.data_ptr(), self.valid.data_ptr())
 
-    def _backward(self):
+    def _exchange_layer(self, l: int):
+        """Side stream: wait for layer l's gradients (and for the dX GEMM that still reads W[l]), sum them over
+        the ranks, apply SGD to that layer's slice.  The main stream goes on with layer l-1 meanwhile."""
+        main = torch.cuda.current_stream(self.dev)
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self._side.wait_event(ev)
+        start, count = self.layer_span[l]
+        h = self.h
+        h.set_stream(self._side.cuda_stream)
+        h.dp_allreduce_sum(self.G.data_ptr() + 4 * start, count)
+        h.sgd_step([self.P.data_ptr() + 4 * start], [self.G.data_ptr() + 4 * start], [self.V.data_ptr() + 4 * start], [count],
+                   self.lr, self.momentum, self.wd, 1.0 / self.world)
+        h.set_stream(main.cuda_stream)
+
+    def _backward(self, exchange: bool = False):
         h, L, B = self.h, self.L, self.batch
         C = self.dims[-1]
         h.ce_bwd(self.softmax.data_ptr(), self.y.data_ptr(), True, B, C, -100, 0.0, 0, 0, self.valid.data_ptr(),
@@ -113,6 +136,10 @@ class MLPTrainer:
                        self.gact[l - 1].data_ptr(), algo=self.algo)
                 h.relu_bwd(self.gact[l - 1].data_ptr(), self.mask[l - 1].data_ptr(), self.gout[l - 1].data_ptr(),
                            B * self.dims[l])
+            if exchange:
+                self._exchange_layer(l)
+        if exchange:  # the next step's forward reads the updated parameters
+            torch.cuda.current_stream(self.dev).wait_stream(self._side)
 
     def _update(self):
         h = self.h
