@@ -50,6 +50,10 @@ const char* tenmo_cuda_version(void);
  * stream).  A new context runs on a stream of its own; TENMO_STREAM_OWN selects that one again. */
 #define TENMO_STREAM_OWN ((void*)(intptr_t)-1)
 int tenmo_cuda_set_stream(tenmo_ctx* ctx, void* cuda_stream);
+/* The persistent tensor-core GEMM launches one CTA per SM.  While a collective runs beside it on another
+ * stream (data-parallel gradient exchange) its CTAs need SMs of their own: leave `n` SMs out of the GEMM
+ * grid (0 restores the full grid).  No counterpart in the reference (single stream, no collectives). */
+int tenmo_cuda_reserve_sms(tenmo_ctx* ctx, int n);
 /* DeviceContext.synchronize (the `sync=True` argument of every launcher, matmul_kernel.mojo:277). */
 int tenmo_cuda_synchronize(tenmo_ctx* ctx);
 int tenmo_cuda_device_info(tenmo_ctx* ctx, int* sm_count, int* cc_major, int* cc_minor, int* sm_clock_khz);

@@ -40,6 +40,8 @@ struct tenmo_ctx {
     // tcgen05 GEMM state (tensor-map encoder entry point, opt-in smem set)
     void* encode_tiled = nullptr;
     bool tc_ready = false;
+    unsigned int tile_counter_next = 0;
+    int reserve_sms = 0;  // persistent GEMM kernels launch sm_count - reserve_sms CTAs (tenmo_cuda_reserve_sms)
     // optional device timing of the GEMM kernels (tenmo_cuda_profile_begin/end)
     bool prof_on = false;
     cudaEvent_t* prof_ev = nullptr;  // pairs: [2*i] before, [2*i+1] after

@@ -34,6 +34,8 @@ constexpr int TC_THREADS = 192;
 constexpr int BM = 128;
 constexpr int BK = 32;                       // fp32 elements per k-block = one 128-byte swizzle row
 constexpr int UMMA_K = 8;                    // tf32 k per instruction
+constexpr int SQ = 4;                        // depth of the tile-id ring between the scheduler and its consumers
+constexpr int TILE_COUNTERS = 32;            // ring of global tile counters, one per GEMM launch in flight
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 template <int BN>
@@ -58,6 +60,7 @@ struct TcParams {
     int act;
     int c_vec;
     uint32_t* status;
+    unsigned int* tile_counter;  // zero at launch; hands out tiles gridDim.x, gridDim.x + 1, ...
 };
 
 // ---------------------------------------------------------------------------------------------------
@@ -181,12 +184,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 128B swizzle wants 1024-byte alignment
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + Cfg::STAGES * Cfg::STAGE;
-    // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem ptr, abort flag
+    // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], sched_full[SQ],
+    // sched_empty[SQ]; then the tile-id ring, the tmem pointer and the abort flag
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::STAGES + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::STAGES + 2 + a); };
-    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + Cfg::STAGES * Cfg::STAGE + 8 * (2 * Cfg::STAGES + 4));
+    auto sfull_bar = [&](int q) { return bar_base + 8u * (2 * Cfg::STAGES + 4 + q); };
+    auto sempty_bar = [&](int q) { return bar_base + 8u * (2 * Cfg::STAGES + 4 + SQ + q); };
+    volatile int* sched_tiles =
+        reinterpret_cast<volatile int*>(smem_gen + Cfg::STAGES * Cfg::STAGE + 8 * (2 * Cfg::STAGES + 4 + 2 * SQ));
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(const_cast<int*>(sched_tiles) + SQ);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -196,6 +204,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        for (int q = 0; q < SQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 5); }  // MMA thread + 4 epilogue warps
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -217,11 +226,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t phase = 0;
             uint32_t armed = 0;  // stages whose full barrier was armed at least once
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            // Tile scheduler: the first tile of a CTA is its block index, every further one comes from a
+            // global counter, so a CTA that starts late (its SM was busy with another stream's kernel) or runs
+            // slow simply takes fewer tiles.  Tile ids travel to the MMA and epilogue warps through a small
+            // shared-memory ring; -1 ends the stream.
+            int sq = 0;
+            uint32_t sphase = 0;
+            int64_t tile = blockIdx.x;
+            while (ok) {
+                if (!mbar_wait(sempty_bar(sq), sphase ^ 1u, abort_flag)) { ok = false; break; }
+                sched_tiles[sq] = tile < num_tiles ? (int)tile : -1;
+                mbar_arrive(sfull_bar(sq));
+                if (++sq == SQ) { sq = 0; sphase ^= 1u; }
+                if (tile >= num_tiles) break;
                 int64_t batch; int tm, tn;
                 tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
                 const int m0 = tm * BM, n0 = tn * BN;
                 const int ba = p.a_batched ? (int)batch : 0, bb = p.b_batched ? (int)batch : 0;
+                tile = (int64_t)gridDim.x + (int64_t)atomicAdd(p.tile_counter, 1u);  // fetched early: latency hides under the loads
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t sa = smem_base + stage * Cfg::STAGE;
@@ -286,7 +308,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t acc_phase[2] = {0, 0};
             int acc = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int sq = 0;
+            uint32_t sphase = 0;
+            while (ok) {
+                if (!mbar_wait(sfull_bar(sq), sphase, abort_flag)) { ok = false; break; }
+                const int tile = sched_tiles[sq];
+                mbar_arrive(sempty_bar(sq));
+                if (++sq == SQ) { sq = 0; sphase ^= 1u; }
+                if (tile < 0) break;
                 if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -320,10 +349,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t acc_phase[2] = {0, 0};
         int acc = 0;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int sq = 0;
+        uint32_t sphase = 0;
+        // Lane 0 does the waiting and the warp follows its verdict, so the warp never diverges around the
+        // warp-collective tcgen05.ld below, not even when a wait is abandoned.
+        auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool {
+            int got = 1;
+            if (lane == 0) got = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+            return __shfl_sync(0xffffffffu, got, 0) != 0;
+        };
+        while (ok) {
+            if (!warp_wait(sfull_bar(sq), sphase)) { ok = false; break; }
+            int tile = 0;
+            if (lane == 0) {
+                tile = sched_tiles[sq];
+                mbar_arrive(sempty_bar(sq));
+            }
+            tile = __shfl_sync(0xffffffffu, tile, 0);
+            if (++sq == SQ) { sq = 0; sphase ^= 1u; }
+            if (tile < 0) break;
             int64_t batch; int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
-            if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag)) { ok = false; break; }
+            if (!warp_wait(tfull_bar(acc), acc_phase[acc])) { ok = false; break; }
             tcgen05_fence_after();
             const int64_t m = (int64_t)tm * BM + quarter * 32 + lane;
             const int64_t n_base = (int64_t)tn * BN;
@@ -378,7 +425,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     tcgen05_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, TENMO_DEV_TIMEOUT);
+    if (threadIdx.x == 0) {
+        if (*abort_flag) atomicOr(p.status, TENMO_DEV_TIMEOUT);
+        // every CTA has finished drawing tiles once it is here; the last one re-arms the counter pair
+        if (atomicAdd(p.tile_counter + 1, 1u) == gridDim.x - 1) {
+            p.tile_counter[0] = 0;
+            p.tile_counter[1] = 0;
+            __threadfence();
+        }
+    }
     if (warp == 1) {
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
@@ -614,7 +669,13 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
                (!p.aux || (reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0);
     tp.status = ctx->dev_status;
     const int64_t tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.total_batch;
-    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    int ctas = ctx->sm_count - ctx->reserve_sms;  // SMs left free for a collective running beside the GEMM
+    if (ctas < 1) ctas = 1;
+    if (tiles > 0x7fffffffLL) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_tc: %lld tiles is out of range", (long long)tiles);
+    const int grid = (int)(tiles < ctas ? tiles : ctas);
+    // a tile counter pair for this launch (dev_status words 64..127: [next tile, CTAs finished] x 32).  Both words
+    // are zero between launches: the last CTA to leave clears them, so no memset sits in front of the kernel.
+    tp.tile_counter = reinterpret_cast<unsigned int*>(ctx->dev_status) + 64 + 2 * (ctx->tile_counter_next++ % TILE_COUNTERS);
     tenmo_prof_before(ctx);
     cudaError_t e = (bn == 256) ? launch_tc<256>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
                                 : launch_tc<128>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp);

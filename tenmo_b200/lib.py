@@ -23,7 +23,7 @@ DP_ID_BYTES = 128
 EXPORTS = [
     "tenmo_cuda_init", "tenmo_cuda_destroy", "tenmo_cuda_last_error", "tenmo_cuda_version", "tenmo_cuda_set_stream",
     "tenmo_cuda_synchronize", "tenmo_cuda_device_info", "tenmo_cuda_check_device_status", "tenmo_cuda_launch_count",
-    "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end",
+    "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end", "tenmo_cuda_reserve_sms",
     "tenmo_gemm_f32", "tenmo_gemm_last_algo", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
     "tenmo_colsum_f32_static", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
@@ -79,6 +79,7 @@ def _bind(lib):
         "tenmo_cuda_device_info": (I, [P, C.POINTER(I), C.POINTER(I), C.POINTER(I), C.POINTER(I)]),
         "tenmo_cuda_check_device_status": (I, [P]),
         "tenmo_cuda_launch_count": (I64, [P, I]),
+        "tenmo_cuda_reserve_sms": (I, [P, I]),
         "tenmo_cuda_profile_begin": (I, [P]),
         "tenmo_cuda_profile_end": (I, [P, C.POINTER(I64), C.POINTER(C.c_double)]),
         "tenmo_gemm_f32": (I, [P, I, I64, I64, I64, C.POINTER(Mat), C.POINTER(Mat), P, F, P, I, P, P]),
@@ -175,6 +176,10 @@ class TenmoCuda:
 
     def launch_count(self, reset: bool = False) -> int:
         return int(self.require()._lib.tenmo_cuda_launch_count(self._ctx, 1 if reset else 0))
+
+    def reserve_sms(self, n: int):
+        """Leave ``n`` SMs out of the persistent GEMM grid (for a collective running on another stream)."""
+        self._call("tenmo_cuda_reserve_sms", n)
 
     def profile_begin(self):
         self._call("tenmo_cuda_profile_begin")

@@ -28,7 +28,8 @@ from .parallel import shard_rows
 class MLPTrainer:
     def __init__(self, weights, biases, batch: int, lr: float = 0.01, momentum: float = 0.9, weight_decay: float = 0.0,
                  algo: str = "auto", handle: TenmoCuda | None = None, rank: int = 0, world: int = 1,
-                 unique_id: bytes | None = None, device: int | None = None, overlap: bool = True):
+                 unique_id: bytes | None = None, device: int | None = None, overlap: bool = True,
+                 reserve_sms: int = 0):
         self.dev = torch.cuda.current_device() if device is None else device
         self.h = handle or TenmoCuda(self.dev).require()
         self.algo = {"auto": _lib.ALGO_AUTO, "simt": _lib.ALGO_SIMT_FP32, "3xtf32": _lib.ALGO_TC_3XTF32}[algo]
@@ -74,6 +75,7 @@ class MLPTrainer:
                            for l in range(self.L)]
         self.overlap = overlap and world > 1
         self._side = torch.cuda.Stream(self.dev) if self.overlap else None
+        self.reserve_sms = int(reserve_sms) if self.overlap else 0
         if world > 1:
             self.h.dp_init(rank, world, unique_id)
         torch.cuda.synchronize(self.dev)
@@ -89,7 +91,11 @@ class MLPTrainer:
         """Queue one step on the context's current stream (no host synchronisation anywhere)."""
         self._forward()
         if update and self.overlap:
-            self._backward(exchange=True)  # per-layer all-reduce + SGD on the side stream, under the backward GEMMs
+            # per-layer all-reduce + SGD on the side stream, under the backward GEMMs, which leave a few SMs
+            # free for the collective's CTAs
+            self.h.reserve_sms(self.reserve_sms)
+            self._backward(exchange=True)
+            self.h.reserve_sms(0)
         else:
             self._backward()
             if update:
