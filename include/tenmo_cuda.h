@@ -108,6 +108,35 @@ enum { TENMO_ACT_NONE = 0, TENMO_ACT_RELU = 1, TENMO_ACT_SIGMOID = 2 };
 int tenmo_gemm_f32(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A,
                    const tenmo_mat* B, float* C, float beta, const float* bias, int act, float* aux,
                    float* colsum);
+/* The same GEMM with every option in one struct (zero-initialise it; NULL opts = all defaults), plus what a
+ * host that chains GEMMs can use to stop paying for the 3xTF32 operand split more than once per tensor:
+ *   a_lo, b_lo  lo planes of the operands' STORAGE as written by tenmo_split_lo_f32 or by an earlier call's
+ *               c_lo (a transposed view shares its storage's plane); NULL = split inside the call.
+ *               Ignored by the SIMT kernel.
+ *   c_lo        optional output: lo plane of the stored result, row-major, leading dimension N rounded up
+ *               to a multiple of 4, batches back to back -- ready to be the a_lo / b_lo of the next GEMM.
+ *   mul_mask    optional (total_batch, M, N) multiplier applied to act(A.B + bias) before beta / store: with
+ *               the ReLU mask of the layer below, dX = (dY . W^T) * mask is ReLUBackward (relu.mojo:19-46)
+ *               fused into Matmul2dBackward's dA GEMM (matmul.mojo:33-41).
+ * No counterpart in the reference, which runs each of these as a separate kernel. */
+typedef struct {
+    float beta;
+    const float* bias;
+    int act;
+    float* aux;
+    float* colsum;
+    const float* a_lo;
+    const float* b_lo;
+    float* c_lo;
+    const float* mul_mask;
+} tenmo_gemm_opts;
+int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A,
+                      const tenmo_mat* B, float* C, const tenmo_gemm_opts* opts);
+/* lo plane (x minus x truncated to TF32, rounded to TF32) of a (rows, cols) view X with one unit-stride axis,
+ * 16-byte aligned rows and batch dims that collapse to one stride.  Written in the order of X's storage:
+ * `outer` lines of `inner` floats, lines padded to a multiple of 4, batches back to back; `capacity` is the
+ * size of lo_out in floats and must cover that. */
+int tenmo_split_lo_f32(tenmo_ctx* ctx, const tenmo_mat* X, int64_t rows, int64_t cols, float* lo_out, int64_t capacity);
 /* Which kernel the last tenmo_gemm_f32 call on this context ran: TENMO_ALGO_SIMT_FP32 or _TC_3XTF32. */
 int tenmo_gemm_last_algo(tenmo_ctx* ctx);
 

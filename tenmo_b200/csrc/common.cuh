@@ -87,6 +87,16 @@ static inline int tenmo_stream_grid(const tenmo_ctx* ctx, int64_t work_items, in
     return (int)(want < cap ? want : cap);
 }
 
+// lo plane of the 3xTF32 split: x = hi + lo with hi = x truncated to TF32 (what the tensor core reads from
+// an fp32 word) and lo rounded to TF32.
+__device__ __forceinline__ float tenmo_tf32_lo(float x) {
+    const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+    const float d = x - hi;
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(d));
+    return __uint_as_float(r);
+}
+
 __device__ __forceinline__ float tenmo_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

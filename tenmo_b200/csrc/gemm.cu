@@ -1,11 +1,11 @@
-// tenmo_gemm_f32: argument validation, batch broadcasting and kernel selection.
+// tenmo_gemm_f32 / tenmo_gemm_f32_ex: argument validation, batch broadcasting and kernel selection.
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 
 namespace {
 
 int build_batch(tenmo_ctx* ctx, const tenmo_mat* A, const tenmo_mat* B, TenmoBatch* out, int64_t* total) {
-    const int ra = A->batch_rank, rb = B->batch_rank;
+    const int ra = A->batch_rank, rb = B ? B->batch_rank : 0;
     if (ra < 0 || rb < 0 || ra > TENMO_MAX_BATCH_RANK || rb > TENMO_MAX_BATCH_RANK)
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: batch rank out of range (A %d, B %d, max %d)", ra, rb,
                                TENMO_MAX_BATCH_RANK);
@@ -15,14 +15,14 @@ int build_batch(tenmo_ctx* ctx, const tenmo_mat* A, const tenmo_mat* B, TenmoBat
     for (int d = 0; d < r; ++d) {
         const int ad = d - (r - ra), bd = d - (r - rb);
         const int64_t sa = ad >= 0 ? A->batch_shape[ad] : 1;
-        const int64_t sb = bd >= 0 ? B->batch_shape[bd] : 1;
+        const int64_t sb = (B && bd >= 0) ? B->batch_shape[bd] : 1;
         if (sa < 0 || sb < 0 || (sa != sb && sa != 1 && sb != 1))
             return tenmo_set_error(ctx, TENMO_ERR_INVALID,
                                    "gemm: batch shapes not broadcastable at dim %d (%lld vs %lld)", d, (long long)sa,
                                    (long long)sb);
         out->shape[d] = sa > sb ? sa : sb;
         out->a_stride[d] = (ad >= 0 && sa > 1) ? A->batch_stride[ad] : 0;
-        out->b_stride[d] = (bd >= 0 && sb > 1) ? B->batch_stride[bd] : 0;
+        out->b_stride[d] = (B && bd >= 0 && sb > 1) ? B->batch_stride[bd] : 0;
         t *= out->shape[d];
     }
     for (int d = r; d < TENMO_MAX_BATCH_RANK; ++d) {
@@ -39,23 +39,26 @@ extern "C" {
 
 int tenmo_gemm_last_algo(tenmo_ctx* ctx) { return ctx ? ctx->last_gemm_algo : -1; }
 
-int tenmo_gemm_f32(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A, const tenmo_mat* B,
-                   float* C, float beta, const float* bias, int act, float* aux, float* colsum) {
+int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A, const tenmo_mat* B,
+                      float* C, const tenmo_gemm_opts* o) {
     TENMO_CHECK_CTX(ctx);
+    tenmo_gemm_opts none;
+    memset(&none, 0, sizeof(none));
+    if (!o) o = &none;
     if (!A || !B) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: NULL operand descriptor");
     if (M < 0 || N < 0 || K < 0)
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: negative dimension (M=%lld N=%lld K=%lld)", (long long)M,
                                (long long)N, (long long)K);
     if (algo < TENMO_ALGO_AUTO || algo > TENMO_ALGO_TC_3XTF32)
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: unknown algo %d", algo);
-    if (act < TENMO_ACT_NONE || act > TENMO_ACT_SIGMOID)
-        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: unknown activation %d", act);
-    if (beta != 0.f && beta != 1.f) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: beta must be 0 or 1");
+    if (o->act < TENMO_ACT_NONE || o->act > TENMO_ACT_SIGMOID)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: unknown activation %d", o->act);
+    if (o->beta != 0.f && o->beta != 1.f) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: beta must be 0 or 1");
     TenmoGemmParams p;
     memset(&p, 0, sizeof(p));
     int st = build_batch(ctx, A, B, &p.batch, &p.total_batch);
     if (st != TENMO_OK) return st;
-    if (colsum && p.batch.rank != 0)
+    if (o->colsum && p.batch.rank != 0)
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: colsum output is defined for 2-D operands only");
     if (M == 0 || N == 0 || p.total_batch == 0) return TENMO_OK;  // empty output: nothing to do
     if (!C) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: C is NULL");
@@ -66,7 +69,9 @@ int tenmo_gemm_f32(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, co
     p.M = M; p.N = N; p.K = K;
     p.a_rs = A->row_stride; p.a_cs = A->col_stride;
     p.b_rs = B->row_stride; p.b_cs = B->col_stride;
-    p.beta = beta; p.bias = bias; p.act = act; p.aux = aux;
+    p.beta = o->beta; p.bias = o->bias; p.act = o->act; p.aux = o->aux;
+    p.a_lo = o->a_lo; p.b_lo = o->b_lo; p.c_lo = o->c_lo; p.mul_mask = o->mul_mask;
+    p.ld_clo = (N + 3) / 4 * 4;
 
     TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     int chosen = TENMO_ALGO_SIMT_FP32;
@@ -81,13 +86,39 @@ int tenmo_gemm_f32(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, co
     else st = tenmo_gemm_simt_launch(ctx, p);
     if (st != TENMO_OK) return st;
     ctx->last_gemm_algo = chosen;
-    if (colsum) {
+    if (o->colsum) {
         // column sums of the right operand: db when this call is dW = X^T . dY
         if (B->col_stride != 1)
             return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm: colsum needs a unit column stride on B");
-        st = tenmo_colsum_f32(ctx, p.B, K, N, B->row_stride, colsum, beta);
+        st = tenmo_colsum_f32(ctx, p.B, K, N, B->row_stride, o->colsum, o->beta);
     }
     return st;
+}
+
+int tenmo_gemm_f32(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A, const tenmo_mat* B,
+                   float* C, float beta, const float* bias, int act, float* aux, float* colsum) {
+    tenmo_gemm_opts o;
+    memset(&o, 0, sizeof(o));
+    o.beta = beta; o.bias = bias; o.act = act; o.aux = aux; o.colsum = colsum;
+    return tenmo_gemm_f32_ex(ctx, algo, M, N, K, A, B, C, &o);
+}
+
+int tenmo_split_lo_f32(tenmo_ctx* ctx, const tenmo_mat* X, int64_t rows, int64_t cols, float* lo_out, int64_t capacity) {
+    TENMO_CHECK_CTX(ctx);
+    if (!X || !X->ptr || !lo_out) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "split_lo: NULL pointer");
+    if (rows <= 0 || cols <= 0) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "split_lo: empty matrix");
+    TenmoBatch batch;
+    int64_t total = 1;
+    int st = build_batch(ctx, X, nullptr, &batch, &total);
+    if (st != TENMO_OK) return st;
+    const int64_t inner = (X->col_stride == 1 || cols == 1) ? cols : rows, outer = inner == cols ? rows : cols;
+    const int64_t need = total * outer * ((inner + 3) / 4 * 4);
+    if (capacity < need)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "split_lo: output holds %lld floats, %lld needed", (long long)capacity,
+                               (long long)need);
+    TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return tenmo_split_lo_launch(ctx, X->ptr + X->offset, rows, cols, X->row_stride, X->col_stride, batch, batch.a_stride, total,
+                                 lo_out, nullptr);
 }
 
 }  // extern "C"

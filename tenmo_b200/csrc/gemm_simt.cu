@@ -209,7 +209,8 @@ __global__ void __launch_bounds__(THREADS) gemm_simt_kernel(const TenmoGemmParam
                 v[q] = apply_act(x, p.act);
             }
             float* dst = C + m * p.N + n;
-            if (CW == 4 && p.c_vec && n + 3 < p.N) {
+            const bool extended = p.mul_mask != nullptr || p.c_lo != nullptr;
+            if (CW == 4 && p.c_vec && n + 3 < p.N && !extended) {
                 float4 o = make_float4(v[0], v[1], v[2], v[3]);
                 if (p.beta != 0.f) {
                     const float4 old = *reinterpret_cast<const float4*>(dst);
@@ -222,9 +223,11 @@ __global__ void __launch_bounds__(THREADS) gemm_simt_kernel(const TenmoGemmParam
                 for (int q = 0; q < CW; ++q) {
                     if (n + q < p.N) {
                         float o = v[q];
+                        if (p.mul_mask) o *= __ldg(p.mul_mask + (batch * p.M + m) * p.N + n + q);
                         if (p.beta != 0.f) o += dst[q];
                         dst[q] = o;
                         if (AUX) AUX[m * p.N + n + q] = mk[q];
+                        if (p.c_lo) p.c_lo[(batch * p.M + m) * p.ld_clo + n + q] = tenmo_tf32_lo(o);
                     }
                 }
             }

@@ -26,6 +26,12 @@ struct TenmoGemmParams {
     const float* bias;
     int act;
     float* aux;
+    // extended options (tenmo_gemm_f32_ex)
+    const float* a_lo;      // precomputed lo planes of the operands' storage (tensor-core kernel only), or NULL
+    const float* b_lo;
+    float* c_lo;            // optional: lo plane of the stored result, row-major with leading dimension ld_clo
+    int64_t ld_clo;
+    const float* mul_mask;  // optional (total_batch, M, N): result is multiplied by it before beta / store
     int tiles_m, tiles_n;
     int64_t total_batch;
     TenmoBatch batch;

@@ -43,7 +43,7 @@ struct TcCfg {
     static constexpr int A_TILE = BM * BK * 4;   // bytes of one plane of A per stage
     static constexpr int B_TILE = BN * BK * 4;
     static constexpr int STAGE = 2 * A_TILE + 2 * B_TILE;
-    static constexpr int STAGES = (BN == 256) ? 2 : 3;
+    static constexpr int STAGES = (BN == 256) ? 2 : (BN == 128 ? 3 : 4);
     static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static constexpr int TMEM_COLS = 2 * BN;     // two accumulators
 };
@@ -52,6 +52,9 @@ struct TcParams {
     float* C;
     float* aux;
     const float* bias;
+    const float* mul_mask;  // optional elementwise multiplier of the result (fused ReLU backward)
+    float* c_lo;            // optional lo plane of the stored result
+    int64_t ld_clo;
     int64_t M, N, K;
     int64_t total_batch;
     int tiles_m, tiles_n;
@@ -376,6 +379,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int64_t n_base = (int64_t)tn * BN;
             float* crow = p.C + (batch * p.M + m) * p.N;
             float* auxrow = p.aux ? p.aux + (batch * p.M + m) * p.N : nullptr;
+            const float* maskrow = p.mul_mask ? p.mul_mask + (batch * p.M + m) * p.N : nullptr;
+            float* clorow = p.c_lo ? p.c_lo + (batch * p.M + m) * p.ld_clo : nullptr;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
@@ -398,18 +403,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                         if (p.c_vec && n + 3 < p.N) {
                             float4 o = make_float4(v[0], v[1], v[2], v[3]);
+                            if (maskrow) {
+                                const float4 mm = __ldg(reinterpret_cast<const float4*>(maskrow + n));
+                                o.x *= mm.x; o.y *= mm.y; o.z *= mm.z; o.w *= mm.w;
+                            }
                             if (p.beta != 0.f) {
                                 const float4 old = *reinterpret_cast<const float4*>(crow + n);
                                 o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                             }
                             *reinterpret_cast<float4*>(crow + n) = o;
                             if (auxrow) *reinterpret_cast<float4*>(auxrow + n) = make_float4(mk[0], mk[1], mk[2], mk[3]);
+                            if (clorow)
+                                *reinterpret_cast<float4*>(clorow + n) = make_float4(tenmo_tf32_lo(o.x), tenmo_tf32_lo(o.y),
+                                                                                     tenmo_tf32_lo(o.z), tenmo_tf32_lo(o.w));
                         } else {
 #pragma unroll
                             for (int e = 0; e < 4; ++e)
                                 if (n + e < p.N) {
-                                    crow[n + e] = p.beta != 0.f ? crow[n + e] + v[e] : v[e];
+                                    float o = v[e];
+                                    if (maskrow) o *= __ldg(maskrow + n + e);
+                                    if (p.beta != 0.f) o += crow[n + e];
+                                    crow[n + e] = o;
                                     if (auxrow) auxrow[n + e] = mk[e];
+                                    if (clorow) clorow[n + e] = tenmo_tf32_lo(o);
                                 }
                         }
                     }
@@ -444,13 +460,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ---------------------------------------------------------------------------------------------------
 // lo-plane split:  lo = tf32_rna(x - trunc_tf32(x)), written compactly (rows x inner, ld = ld_lo)
 // ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float tf32_lo(float x) {
-    const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-    const float d = x - hi;
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(d));
-    return __uint_as_float(r);
-}
+__device__ __forceinline__ float tf32_lo(float x) { return tenmo_tf32_lo(x); }
 
 __global__ void __launch_bounds__(256)
 split_lo_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t rows, int64_t inner, int64_t ld_src,
@@ -618,6 +628,23 @@ bool tenmo_gemm_tc_profitable(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     return flop >= 2.0e9 && p.M >= 128 && p.N >= 64 && p.K >= 64;
 }
 
+int tenmo_split_lo_launch(tenmo_ctx* ctx, const float* base, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
+                          const TenmoBatch& batch, const int64_t* bstrides, int64_t total_batch, float* out,
+                          int64_t* floats_written) {
+    OperandPlan o;
+    char why[160];
+    if (!plan_operand(rows, cols, rs, cs, false, base, batch, bstrides, total_batch, &o, "X", why, sizeof(why)))
+        return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "split_lo: %s", why);
+    if (reinterpret_cast<uintptr_t>(out) & 15u) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "split_lo: output is not 16-byte aligned");
+    const int64_t work = o.batches * o.outer * (o.ld_lo / 4);
+    const int grid = tenmo_stream_grid(ctx, work, 256 * 4, 8);
+    split_lo_kernel<<<grid, 256, 0, ctx->stream>>>(base, out, o.outer, o.inner, o.ld, o.ld_lo, o.batches,
+                                                   o.batched ? o.batch_stride : 0, o.bstride_lo);
+    TENMO_LAUNCH_CHECK(ctx, "split_lo_kernel");
+    if (floats_written) *floats_written = o.bstride_lo * o.batches;
+    return TENMO_OK;
+}
+
 int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     int st = tc_init(ctx);
     if (st != TENMO_OK) return st;
@@ -625,14 +652,19 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     char why[160];
     if (!make_plan(p, &a, &b, why, sizeof(why))) return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm_tc: %s", why);
 
-    // workspace: [A_lo | B_lo]
-    const size_t a_lo_bytes = ((size_t)a.bstride_lo * a.batches * 4 + 1023) & ~(size_t)1023;
-    const size_t b_lo_bytes = ((size_t)b.bstride_lo * b.batches * 4 + 1023) & ~(size_t)1023;
+    // lo planes: taken from the caller when supplied (same storage geometry: outer x inner rounded up to 4,
+    // batches back to back), else split here into the workspace [A_lo | B_lo]
+    const size_t a_lo_bytes = p.a_lo ? 0 : (((size_t)a.bstride_lo * a.batches * 4 + 1023) & ~(size_t)1023);
+    const size_t b_lo_bytes = p.b_lo ? 0 : (((size_t)b.bstride_lo * b.batches * 4 + 1023) & ~(size_t)1023);
     void* ws = nullptr;
-    st = tenmo_workspace(ctx, a_lo_bytes + b_lo_bytes, &ws);
-    if (st != TENMO_OK) return st;
-    float* a_lo = static_cast<float*>(ws);
-    float* b_lo = reinterpret_cast<float*>(static_cast<char*>(ws) + a_lo_bytes);
+    if (a_lo_bytes + b_lo_bytes > 0) {
+        st = tenmo_workspace(ctx, a_lo_bytes + b_lo_bytes, &ws);
+        if (st != TENMO_OK) return st;
+    }
+    const float* a_lo = p.a_lo ? p.a_lo : static_cast<float*>(ws);
+    const float* b_lo = p.b_lo ? p.b_lo : reinterpret_cast<float*>(static_cast<char*>(ws) + a_lo_bytes);
+    if ((p.a_lo && (reinterpret_cast<uintptr_t>(p.a_lo) & 15u)) || (p.b_lo && (reinterpret_cast<uintptr_t>(p.b_lo) & 15u)))
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_tc: a supplied lo plane is not 16-byte aligned");
 
     auto split = [&](const float* src, float* dst, const OperandPlan& o) -> int {
         const int64_t work = o.batches * o.outer * (o.ld_lo / 4);
@@ -642,13 +674,20 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
         TENMO_LAUNCH_CHECK(ctx, "split_lo_kernel");
         return TENMO_OK;
     };
-    if ((st = split(p.A, a_lo, a)) != TENMO_OK) return st;
-    if ((st = split(p.B, b_lo, b)) != TENMO_OK) return st;
+    if (!p.a_lo && (st = split(p.A, const_cast<float*>(a_lo), a)) != TENMO_OK) return st;
+    if (!p.b_lo && (st = split(p.B, const_cast<float*>(b_lo), b)) != TENMO_OK) return st;
 
-    const char* env_bn = getenv("TENMO_TC_BN");
+    // Tile width: 128 x 256 unless that leaves most SMs without a tile, then 128 x 128, then 128 x 64
+    // (e.g. the 1000-class output layer at batch 1024: 32 tiles -> 64 -> 128).
+    int ctas = ctx->sm_count - ctx->reserve_sms;  // SMs left free for a collective running beside the GEMM
+    if (ctas < 1) ctas = 1;
+    auto tiles_for = [&](int w) { return ((p.M + BM - 1) / BM) * ((p.N + w - 1) / w) * p.total_batch; };
     int bn = 256;
-    if (env_bn && atoi(env_bn) == 128) bn = 128;
-    if (p.N <= 128) bn = 128;
+    if (tiles_for(256) * 4 < (int64_t)ctas * 3) bn = tiles_for(128) * 4 < (int64_t)ctas * 3 ? 64 : 128;
+    if (p.N <= 64) bn = 64;
+    else if (p.N <= 128 && bn > 128) bn = 128;
+    const char* env_bn = getenv("TENMO_TC_BN");
+    if (env_bn && (atoi(env_bn) == 64 || atoi(env_bn) == 128 || atoi(env_bn) == 256)) bn = atoi(env_bn);
 
     CUtensorMap ma, mal, mb, mbl;
     const int a_box = a.mn_major ? 32 : BM;
@@ -660,25 +699,27 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
 
     TcParams tp;
     tp.C = p.C; tp.aux = p.aux; tp.bias = p.bias;
+    tp.mul_mask = p.mul_mask; tp.c_lo = p.c_lo; tp.ld_clo = p.ld_clo;
     tp.M = p.M; tp.N = p.N; tp.K = p.K; tp.total_batch = p.total_batch;
     tp.tiles_m = (int)((p.M + BM - 1) / BM);
     tp.tiles_n = (int)((p.N + bn - 1) / bn);
     tp.a_batched = a.batched; tp.b_batched = b.batched;
     tp.beta = p.beta; tp.act = p.act;
     tp.c_vec = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) &&
-               (!p.aux || (reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0);
+               (!p.aux || (reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0) &&
+               (!p.mul_mask || (reinterpret_cast<uintptr_t>(p.mul_mask) & 15u) == 0) &&
+               (!p.c_lo || ((reinterpret_cast<uintptr_t>(p.c_lo) & 15u) == 0 && p.ld_clo % 4 == 0));
     tp.status = ctx->dev_status;
     const int64_t tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.total_batch;
-    int ctas = ctx->sm_count - ctx->reserve_sms;  // SMs left free for a collective running beside the GEMM
-    if (ctas < 1) ctas = 1;
     if (tiles > 0x7fffffffLL) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_tc: %lld tiles is out of range", (long long)tiles);
     const int grid = (int)(tiles < ctas ? tiles : ctas);
     // a tile counter pair for this launch (dev_status words 64..127: [next tile, CTAs finished] x 32).  Both words
     // are zero between launches: the last CTA to leave clears them, so no memset sits in front of the kernel.
     tp.tile_counter = reinterpret_cast<unsigned int*>(ctx->dev_status) + 64 + 2 * (ctx->tile_counter_next++ % TILE_COUNTERS);
     tenmo_prof_before(ctx);
-    cudaError_t e = (bn == 256) ? launch_tc<256>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
-                                : launch_tc<128>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp);
+    cudaError_t e = (bn == 256)   ? launch_tc<256>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
+                    : (bn == 128) ? launch_tc<128>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
+                                  : launch_tc<64>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp);
     tenmo_prof_after(ctx);
     ctx->launches++;
     if (e != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_tc_kernel failed: %s", cudaGetErrorString(e));

@@ -24,7 +24,7 @@ EXPORTS = [
     "tenmo_cuda_init", "tenmo_cuda_destroy", "tenmo_cuda_last_error", "tenmo_cuda_version", "tenmo_cuda_set_stream",
     "tenmo_cuda_synchronize", "tenmo_cuda_device_info", "tenmo_cuda_check_device_status", "tenmo_cuda_launch_count",
     "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end", "tenmo_cuda_reserve_sms",
-    "tenmo_gemm_f32", "tenmo_gemm_last_algo", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
+    "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
     "tenmo_colsum_f32_static", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
     "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
@@ -48,6 +48,22 @@ class Mat(C.Structure):
         ("batch_rank", C.c_int32),
         ("batch_shape", C.c_int64 * MAX_BATCH_RANK),
         ("batch_stride", C.c_int64 * MAX_BATCH_RANK),
+    ]
+
+
+class GemmOpts(C.Structure):
+    """``tenmo_gemm_opts``."""
+
+    _fields_ = [
+        ("beta", C.c_float),
+        ("bias", C.c_void_p),
+        ("act", C.c_int),
+        ("aux", C.c_void_p),
+        ("colsum", C.c_void_p),
+        ("a_lo", C.c_void_p),
+        ("b_lo", C.c_void_p),
+        ("c_lo", C.c_void_p),
+        ("mul_mask", C.c_void_p),
     ]
 
 
@@ -83,6 +99,8 @@ def _bind(lib):
         "tenmo_cuda_profile_begin": (I, [P]),
         "tenmo_cuda_profile_end": (I, [P, C.POINTER(I64), C.POINTER(C.c_double)]),
         "tenmo_gemm_f32": (I, [P, I, I64, I64, I64, C.POINTER(Mat), C.POINTER(Mat), P, F, P, I, P, P]),
+        "tenmo_gemm_f32_ex": (I, [P, I, I64, I64, I64, C.POINTER(Mat), C.POINTER(Mat), P, C.POINTER(GemmOpts)]),
+        "tenmo_split_lo_f32": (I, [P, C.POINTER(Mat), I64, I64, P, I64]),
         "tenmo_gemm_last_algo": (I, [P]),
         "tenmo_add_bias_f32": (I, [P, P, P, P, I64, I64]),
         "tenmo_add_inplace_f32": (I, [P, P, P, I64]),
@@ -194,6 +212,16 @@ class TenmoCuda:
     def gemm(self, M, N, K, A: Mat, B: Mat, c_ptr, *, algo=ALGO_AUTO, beta=0.0, bias=0, act=ACT_NONE, aux=0, colsum=0):
         self._call("tenmo_gemm_f32", algo, M, N, K, C.byref(A), C.byref(B), c_ptr, beta, bias or None, act,
                    aux or None, colsum or None)
+
+    def gemm_ex(self, M, N, K, A: Mat, B: Mat, c_ptr, *, algo=ALGO_AUTO, beta=0.0, bias=0, act=ACT_NONE, aux=0, colsum=0,
+                a_lo=0, b_lo=0, c_lo=0, mul_mask=0):
+        """tenmo_gemm_f32_ex: the GEMM with precomputed / produced lo planes and a fused mask multiply."""
+        o = GemmOpts(beta, bias or None, act, aux or None, colsum or None, a_lo or None, b_lo or None, c_lo or None,
+                     mul_mask or None)
+        self._call("tenmo_gemm_f32_ex", algo, M, N, K, C.byref(A), C.byref(B), c_ptr, C.byref(o))
+
+    def split_lo(self, X: Mat, rows, cols, lo_out, capacity):
+        self._call("tenmo_split_lo_f32", C.byref(X), rows, cols, lo_out, capacity)
 
     def gemm_last_algo(self) -> int:
         return int(self.require()._lib.tenmo_gemm_last_algo(self._ctx))

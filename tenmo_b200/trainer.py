@@ -63,7 +63,14 @@ class MLPTrainer:
         self.act = [self.X] + [torch.empty(B, d, **f32) for d in self.dims[1:]]
         self.mask = [torch.empty(B, d, **f32) for d in self.dims[1:-1]]
         self.gout = [torch.empty(B, d, **f32) for d in self.dims[1:]]     # dL/d(pre-activation) of layer l
-        self.gact = [torch.empty(B, d, **f32) for d in self.dims[1:-1]]   # dL/d(activation) before the mask
+        # 3xTF32 lo planes, each produced once per tensor per step: weights after the update, activations and
+        # gradients by the epilogue of the GEMM that writes them (only the tensor-core path uses them)
+        self.fused_lo = self.algo == _lib.ALGO_TC_3XTF32
+        r4 = lambda n: (n + 3) // 4 * 4
+        if self.fused_lo:
+            self.W_lo = [torch.empty(self.dims[l] * r4(self.dims[l + 1]), **f32) for l in range(self.L)]
+            self.act_lo = [torch.empty(B * r4(d), **f32) for d in self.dims[:-1]]
+            self.gout_lo = [torch.empty(B * r4(d), **f32) for d in self.dims[1:]]
         self.softmax = torch.empty(B, self.dims[-1], **f32)
         self.loss = torch.zeros(1, **f32)
         self.valid = torch.zeros(1, dtype=torch.int32, device=f"cuda:{self.dev}")
@@ -78,6 +85,10 @@ class MLPTrainer:
         self.reserve_sms = int(reserve_sms) if self.overlap else 0
         if world > 1:
             self.h.dp_init(rank, world, unique_id)
+        if self.fused_lo:
+            self.h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
+            for l in range(self.L):
+                self._split_weight(l)
         torch.cuda.synchronize(self.dev)
 
     # ------------------------------------------------------------------------------------------------
@@ -101,13 +112,22 @@ class MLPTrainer:
             if update:
                 self._update()
 
+    def _split_weight(self, l: int):
+        w = self.W[l]
+        self.h.split_lo(self._m(w), w.shape[0], w.shape[1], self.W_lo[l].data_ptr(), self.W_lo[l].numel())
+
     def _forward(self):
         h, L, B = self.h, self.L, self.batch
+        lo = self.fused_lo
+        if lo:  # the input's lo plane: the only activation no GEMM epilogue produces
+            h.split_lo(self._m(self.X), B, self.dims[0], self.act_lo[0].data_ptr(), self.act_lo[0].numel())
         for l in range(L):
             last = l == L - 1
-            h.gemm(B, self.dims[l + 1], self.dims[l], self._m(self.act[l]), self._m(self.W[l]), self.act[l + 1].data_ptr(),
-                   algo=self.algo, bias=self.b[l].data_ptr(), act=_lib.ACT_NONE if last else _lib.ACT_RELU,
-                   aux=0 if last else self.mask[l].data_ptr())
+            h.gemm_ex(B, self.dims[l + 1], self.dims[l], self._m(self.act[l]), self._m(self.W[l]), self.act[l + 1].data_ptr(),
+                      algo=self.algo, bias=self.b[l].data_ptr(), act=_lib.ACT_NONE if last else _lib.ACT_RELU,
+                      aux=0 if last else self.mask[l].data_ptr(),
+                      a_lo=self.act_lo[l].data_ptr() if lo else 0, b_lo=self.W_lo[l].data_ptr() if lo else 0,
+                      c_lo=self.act_lo[l + 1].data_ptr() if (lo and not last) else 0)
         C = self.dims[-1]
         h.ce_fwd(self.act[L].data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
                  self.loss.data_ptr(), self.valid.data_ptr())
@@ -125,6 +145,8 @@ class MLPTrainer:
         h.dp_allreduce_sum(self.G.data_ptr() + 4 * start, count)
         h.sgd_step([self.P.data_ptr() + 4 * start], [self.G.data_ptr() + 4 * start], [self.V.data_ptr() + 4 * start], [count],
                    self.lr, self.momentum, self.wd, 1.0 / self.world)
+        if self.fused_lo:
+            self._split_weight(l)
         h.set_stream(main.cuda_stream)
 
     def _backward(self, exchange: bool = False):
@@ -132,16 +154,23 @@ class MLPTrainer:
         C = self.dims[-1]
         h.ce_bwd(self.softmax.data_ptr(), self.y.data_ptr(), True, B, C, -100, 0.0, 0, 0, self.valid.data_ptr(),
                  self.gout[L - 1].data_ptr())
+        lo = self.fused_lo
+        if lo:
+            h.split_lo(self._m(self.gout[L - 1]), B, C, self.gout_lo[L - 1].data_ptr(), self.gout_lo[L - 1].numel())
         for l in range(L - 1, -1, -1):
             g = self.gout[l]
+            g_lo = self.gout_lo[l].data_ptr() if lo else 0
             # dW = X^T . dY, db = column sum of dY (same call)
-            h.gemm(self.dims[l], self.dims[l + 1], B, self._m(self.act[l], transpose=True), self._m(g),
-                   self.dW[l].data_ptr(), algo=self.algo, colsum=self.db[l].data_ptr())
+            h.gemm_ex(self.dims[l], self.dims[l + 1], B, self._m(self.act[l], transpose=True), self._m(g),
+                      self.dW[l].data_ptr(), algo=self.algo, colsum=self.db[l].data_ptr(),
+                      a_lo=self.act_lo[l].data_ptr() if lo else 0, b_lo=g_lo)
             if l > 0:  # the network input needs no gradient (matmul.mojo:34)
-                h.gemm(B, self.dims[l], self.dims[l + 1], self._m(g), self._m(self.W[l], transpose=True),
-                       self.gact[l - 1].data_ptr(), algo=self.algo)
-                h.relu_bwd(self.gact[l - 1].data_ptr(), self.mask[l - 1].data_ptr(), self.gout[l - 1].data_ptr(),
-                           B * self.dims[l])
+                # dX = (dY . W^T) * mask: the ReLU backward rides in the epilogue, and so does the lo plane of
+                # the result, which is the next layer's dY
+                h.gemm_ex(B, self.dims[l], self.dims[l + 1], self._m(g), self._m(self.W[l], transpose=True),
+                          self.gout[l - 1].data_ptr(), algo=self.algo, mul_mask=self.mask[l - 1].data_ptr(),
+                          a_lo=g_lo, b_lo=self.W_lo[l].data_ptr() if lo else 0,
+                          c_lo=self.gout_lo[l - 1].data_ptr() if lo else 0)
             if exchange:
                 self._exchange_layer(l)
         if exchange:  # the next step's forward reads the updated parameters
@@ -153,6 +182,9 @@ class MLPTrainer:
             h.dp_allreduce_sum(self.G.data_ptr(), self.numel)
         h.sgd_step([self.P.data_ptr()], [self.G.data_ptr()], [self.V.data_ptr()], [self.numel], self.lr, self.momentum,
                    self.wd, 1.0 / self.world)
+        if self.fused_lo:
+            for l in range(self.L):
+                self._split_weight(l)
 
     # ------------------------------------------------------------------------------------------------
     def load_batch(self, X, y):
@@ -184,6 +216,7 @@ class MLPTrainer:
             side.synchronize()
             self.P.copy_(snap[0])
             self.V.copy_(snap[1])
+            self._refresh_weight_lo()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=side):
                 self._enqueue(True)
@@ -191,6 +224,13 @@ class MLPTrainer:
         self.P.copy_(snap[0])  # the capture itself does not run, but keep the state explicit
         self.V.copy_(snap[1])
         self.h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
+        self._refresh_weight_lo()
+
+    def _refresh_weight_lo(self):
+        """The weights changed behind the step's back (restore, checkpoint load): redo their lo planes."""
+        if self.fused_lo:
+            for l in range(self.L):
+                self._split_weight(l)
 
     def replay(self):
         self.graph.replay()
@@ -237,6 +277,8 @@ class MLPTrainer:
             self.b[l].copy_(torch.from_numpy(np.ascontiguousarray(sd[f"{2 * l}.bias"], np.float32)))
         if "__velocity__" in sd:
             self.V.copy_(torch.from_numpy(np.ascontiguousarray(sd["__velocity__"], np.float32)))
+        self.h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
+        self._refresh_weight_lo()
 
 
 __all__ = ["MLPTrainer", "shard_rows"]

@@ -38,7 +38,8 @@ def layouts(oracle, A, B, layout):
 
 
 SHAPES = [(128, 32, 256), (128, 64, 128), (256, 128, 512), (384, 96, 640), (200, 100, 300), (1000, 260, 132),
-          (129, 36, 260), (512, 784, 128), (2048, 512, 1024), (640, 2052, 388)]
+          (129, 36, 260), (512, 784, 128), (2048, 512, 1024), (640, 2052, 388),
+          (2048, 96, 2048), (1024, 160, 1000)]  # 128 x 256 tiles; the 1000-class layer on 128 x 64 tiles
 
 
 @pytest.mark.parametrize("mkn", SHAPES, ids=str)
@@ -122,6 +123,56 @@ def test_tc_refuses_what_it_cannot_take_and_auto_falls_back(g, oracle):
     C, _, _ = g.gpu_matmul(oracle.View.of(A), oracle.View.of(B), algo=-1)
     assert g.handle().gemm_last_algo() == 1
     assert rel_err(C, A.astype(np.float64) @ B.astype(np.float64), np.abs(A), np.abs(B)) <= TOL
+
+
+@pytest.mark.parametrize("algo", [0, 1], ids=["simt", "3xtf32"])
+def test_gemm_ex_lo_planes_and_mask(g, oracle, algo):
+    """tenmo_gemm_f32_ex: supplied lo planes give the same bits as the in-call split, c_lo is the lo plane of
+    what was stored, mul_mask multiplies the result (fused ReLU backward)."""
+    from tenmo_b200 import make_mat
+
+    h = g.handle()
+    M, K, N = 256, 192, 320
+    rng = np.random.default_rng(12)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32)
+    mask = (rng.random((M, N)) < 0.5).astype(np.float32)
+    Ad, Bd, Md = g.dev(A), g.dev(B), g.dev(mask)
+    mA, mB = make_mat(Ad.data_ptr(), (M, K), (K, 1)), make_mat(Bd.data_ptr(), (K, N), (N, 1))
+    a_lo, b_lo = g.empty(M * K), g.empty(K * N)
+    h.split_lo(mA, M, K, a_lo.data_ptr(), M * K)
+    h.split_lo(mB, K, N, b_lo.data_ptr(), K * N)
+    # lo = x - trunc_tf32(x), rounded to tf32: exact check on the host
+    hi = (A.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    lo_ref = A - hi
+    got_lo = g.host(a_lo).reshape(M, K)
+    assert np.max(np.abs(got_lo - lo_ref)) <= 2.0 ** -11 * np.max(np.abs(lo_ref)) and not (got_lo.view(np.uint32) & 0x1FFF).any()
+    C0, C1, c_lo = g.empty(M, N), g.empty(M, N), g.empty(M * N)
+    h.gemm_ex(M, N, K, mA, mB, C0.data_ptr(), algo=algo, mul_mask=Md.data_ptr())
+    h.gemm_ex(M, N, K, mA, mB, C1.data_ptr(), algo=algo, mul_mask=Md.data_ptr(), a_lo=a_lo.data_ptr(), b_lo=b_lo.data_ptr(),
+              c_lo=c_lo.data_ptr())
+    torch.cuda.synchronize()
+    c0, c1 = g.host(C0), g.host(C1)
+    assert np.array_equal(c0, c1)
+    ref = oracle.matmul(A, B, threads=4) * mask
+    if algo == 0:
+        assert np.array_equal(c1, ref)
+    else:
+        assert rel_err(c1, ref.astype(np.float64), np.abs(A), np.abs(B)) <= TOL
+    assert not c1[mask == 0].any()
+    want_lo = g.empty(M * N)
+    h.split_lo(make_mat(C1.data_ptr(), (M, N), (N, 1)), M, N, want_lo.data_ptr(), M * N)
+    assert np.array_equal(g.host(c_lo), g.host(want_lo))
+    # the transposed view of a matrix shares its storage's lo plane (what the backward GEMMs rely on)
+    Ct = g.empty(K, N)
+    G = g.dev(rng.standard_normal((M, N), np.float32))
+    g_lo = g.empty(M * N)
+    mG = make_mat(G.data_ptr(), (M, N), (N, 1))
+    h.split_lo(mG, M, N, g_lo.data_ptr(), M * N)
+    h.gemm_ex(K, N, M, make_mat(Ad.data_ptr(), (K, M), (1, K)), mG, Ct.data_ptr(), algo=algo, a_lo=a_lo.data_ptr(),
+              b_lo=g_lo.data_ptr())
+    torch.cuda.synchronize()
+    want = A.T.astype(np.float64) @ g.host(G).astype(np.float64)
+    assert rel_err(g.host(Ct), want, np.abs(A.T), np.abs(g.host(G))) <= TOL
 
 
 def test_tc_run_to_run_identical(g, oracle):
