@@ -96,7 +96,7 @@ __device__ __forceinline__ int frag_index(int t, int i) {
 }
 
 template <int BM, int BN, int BK, int TM, int TN, bool A_INNER_K, bool B_INNER_K>
-__global__ void __launch_bounds__(THREADS) gemm_simt_kernel(const TenmoGemmParams p) {
+__global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(const TenmoGemmParams p) {
     static_assert((BM / TM) * (BN / TN) == THREADS, "thread tile must cover the CTA tile");
     using LoaderA = TileLoader<BM, BK, A_INNER_K>;
     using LoaderB = TileLoader<BN, BK, B_INNER_K>;

@@ -32,7 +32,11 @@ namespace {
 
 constexpr int TC_THREADS = 192;
 constexpr int BM = 128;
-constexpr int BK = 32;                       // fp32 elements per k-block = one 128-byte swizzle row
+#ifndef TENMO_TC_BK
+#define TENMO_TC_BK 32
+#endif
+constexpr int BK = TENMO_TC_BK;  // fp32 elements per k-block: 32 = one 128-byte swizzle row, 16 = one 64-byte row
+static_assert(BK == 32 || BK == 16, "BK must be 16 or 32");
 constexpr int UMMA_K = 8;                    // tf32 k per instruction
 constexpr int SQ = 4;                        // depth of the tile-id ring between the scheduler and its consumers
 constexpr int TILE_COUNTERS = 32;            // ring of global tile counters, one per GEMM launch in flight
@@ -43,7 +47,7 @@ struct TcCfg {
     static constexpr int A_TILE = BM * BK * 4;   // bytes of one plane of A per stage
     static constexpr int B_TILE = BN * BK * 4;
     static constexpr int STAGE = 2 * A_TILE + 2 * B_TILE;
-    static constexpr int STAGES = (BN == 256) ? 2 : (BN == 128 ? 3 : 4);
+    static constexpr int STAGES = ((BN == 256) ? 2 : (BN == 128 ? 3 : 4)) * (32 / BK);
     static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static constexpr int TMEM_COLS = 2 * BN;     // two accumulators
 };
@@ -261,8 +265,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     } else {
 #pragma unroll
                         for (int j = 0; j < BM / 32; ++j) {
-                            tma_load_3d(sa + j * 4096, &map_a, bar, m0 + 32 * j, k0, ba);
-                            tma_load_3d(sal + j * 4096, &map_a_lo, bar, m0 + 32 * j, k0, ba);
+                            tma_load_3d(sa + j * (BK * 128), &map_a, bar, m0 + 32 * j, k0, ba);
+                            tma_load_3d(sal + j * (BK * 128), &map_a_lo, bar, m0 + 32 * j, k0, ba);
                         }
                     }
                     if (!B_MN) {
@@ -271,8 +275,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 32; ++j) {
-                            tma_load_3d(sb + j * 4096, &map_b, bar, n0 + 32 * j, k0, bb);
-                            tma_load_3d(sbl + j * 4096, &map_b_lo, bar, n0 + 32 * j, k0, bb);
+                            tma_load_3d(sb + j * (BK * 128), &map_b, bar, n0 + 32 * j, k0, bb);
+                            tma_load_3d(sbl + j * (BK * 128), &map_b_lo, bar, n0 + 32 * j, k0, bb);
                         }
                     }
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
@@ -303,9 +307,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // K-major: rows of 128 B, 8-row groups 1024 B apart (SBO), k-step = 32 B inside the swizzle row.
             // MN-major: a tile is [32-wide mn chunk][k row of 128 B]; chunks are 4096 B apart (LBO), the
             // swizzle pattern repeats every 4 k rows = 512 B (SBO), one k-step of 8 rows = 1024 B.
-            constexpr uint32_t A_LBO = A_MN ? 4096u : 16u, A_SBO = A_MN ? 512u : 1024u, A_KSTEP = A_MN ? 1024u : 32u;
-            constexpr uint32_t B_LBO = B_MN ? 4096u : 16u, B_SBO = B_MN ? 512u : 1024u, B_KSTEP = B_MN ? 1024u : 32u;
-            constexpr uint32_t A_LT = A_MN ? 1u : 2u, B_LT = B_MN ? 1u : 2u;
+            // With BK = 16 a K-major row is 64 B (64-byte swizzle, 8-row groups 512 B apart) and an MN-major chunk
+            // holds 16 k rows (2048 B).
+            constexpr uint32_t K_SBO = 8u * BK * 4u, K_LT = BK == 32 ? 2u : 4u, MN_LBO = BK * 128u;
+            constexpr uint32_t A_LBO = A_MN ? MN_LBO : 16u, A_SBO = A_MN ? 512u : K_SBO, A_KSTEP = A_MN ? 1024u : 32u;
+            constexpr uint32_t B_LBO = B_MN ? MN_LBO : 16u, B_SBO = B_MN ? 512u : K_SBO, B_KSTEP = B_MN ? 1024u : 32u;
+            constexpr uint32_t A_LT = A_MN ? 1u : K_LT, B_LT = B_MN ? 1u : K_LT;
             int stage = 0;
             uint32_t phase = 0;
             uint32_t acc_phase[2] = {0, 0};
@@ -571,11 +578,11 @@ int encode_map(tenmo_ctx* ctx, CUtensorMap* map, const float* base, const Operan
     cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)bs * 4};
     if (o.batches == 1) strides[1] = (cuuint64_t)ld * 4 * (cuuint64_t)o.outer;  // unused, but must be a legal stride
     if (strides[1] % 16 != 0) strides[1] = (strides[1] + 15) / 16 * 16;
-    cuuint32_t box[3] = {32u, (cuuint32_t)box_outer, 1u};
+    cuuint32_t box[3] = {o.mn_major ? 32u : (cuuint32_t)BK, (cuuint32_t)box_outer, 1u};
     cuuint32_t estr[3] = {1u, 1u, 1u};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    o.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    o.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : (BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B),
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -690,8 +697,8 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     if (env_bn && (atoi(env_bn) == 64 || atoi(env_bn) == 128 || atoi(env_bn) == 256)) bn = atoi(env_bn);
 
     CUtensorMap ma, mal, mb, mbl;
-    const int a_box = a.mn_major ? 32 : BM;
-    const int b_box = b.mn_major ? 32 : bn;
+    const int a_box = a.mn_major ? BK : BM;
+    const int b_box = b.mn_major ? BK : bn;
     if ((st = encode_map(ctx, &ma, p.A, a, false, a_box)) != TENMO_OK) return st;
     if ((st = encode_map(ctx, &mal, a_lo, a, true, a_box)) != TENMO_OK) return st;
     if ((st = encode_map(ctx, &mb, p.B, b, false, b_box)) != TENMO_OK) return st;
