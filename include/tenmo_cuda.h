@@ -180,6 +180,13 @@ int tenmo_colsum_f32(tenmo_ctx* ctx, const float* x, int64_t M, int64_t N, int64
 int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int64_t ldx, float* out, float beta,
                             void* cuda_stream);
 
+/* ---- softmax over the last axis (the step between the two GEMMs of an attention block) --------------
+ * Forward y = exp(x - max) / sum (SoftmaxNdBuffer.softmax, softmax.mojo:30-48); x has leading dimension ldx,
+ * y is contiguous (M, C).  Backward dx = y * (g - sum_c(g * y)) (+= when beta == 1)
+ * (SoftmaxBackwardDelegate, softmax.mojo:206-213). */
+int tenmo_softmax_fwd_f32(tenmo_ctx* ctx, const float* x, int64_t ldx, float* y, int64_t M, int64_t C);
+int tenmo_softmax_bwd_f32(tenmo_ctx* ctx, const float* y, const float* g, float* dx, float beta, int64_t M, int64_t C);
+
 /* ---- softmax cross-entropy, class-index targets ---------------------------------------------------
  * reduction: 0 mean, 1 sum, 2 none (shared/__init__.mojo:4-40).
  * Forward (crossentropy.mojo:285-432, kernels/crossentropy_fused_kernel.mojo:39-160): per row max,

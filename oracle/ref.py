@@ -206,6 +206,20 @@ def sigmoid_bwd(g, y) -> np.ndarray:
     return dx
 
 
+def softmax_fwd(x) -> np.ndarray:
+    """SoftmaxNdBuffer.softmax over the last axis (softmax.mojo:30-48): exp(x - max) / sum, in fp32."""
+    x = _f32(x)
+    e = np.exp(x - x.max(axis=-1, keepdims=True), dtype=np.float32)
+    return (e / e.sum(axis=-1, keepdims=True, dtype=np.float32)).astype(np.float32)
+
+
+def softmax_bwd(g, y) -> np.ndarray:
+    """SoftmaxBackwardDelegate (softmax.mojo:206-213): y * (g - sum(g * y))."""
+    g, y = _f32(g), _f32(y)
+    gy = (g * y).sum(axis=-1, keepdims=True, dtype=np.float32)
+    return (y * (g - gy)).astype(np.float32)
+
+
 def colsum(x) -> np.ndarray:
     x = _f32(x)
     out = np.empty(x.shape[1], np.float32)

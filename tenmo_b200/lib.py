@@ -26,7 +26,7 @@ EXPORTS = [
     "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end", "tenmo_cuda_reserve_sms",
     "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
-    "tenmo_colsum_f32_static", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
+    "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
     "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
 ]
 
@@ -111,6 +111,8 @@ def _bind(lib):
         "tenmo_sigmoid_bwd_f32": (I, [P, P, P, P, F, I64]),
         "tenmo_colsum_f32": (I, [P, P, I64, I64, I64, P, F]),
         "tenmo_colsum_f32_static": (I, [P, I64, I64, I64, P, F, P]),
+        "tenmo_softmax_fwd_f32": (I, [P, P, I64, P, I64, I64]),
+        "tenmo_softmax_bwd_f32": (I, [P, P, P, P, F, I64, I64]),
         "tenmo_ce_fwd_f32": (I, [P, P, I64, P, I, I64, I64, I64, F, I, P, P, P]),
         "tenmo_ce_bwd_f32": (I, [P, P, P, I, I64, I64, I64, F, I, P, P, P, F]),
         "tenmo_sgd_step_f32": (I, [P, I, P, P, P, P, F, F, F, F]),
@@ -258,6 +260,12 @@ class TenmoCuda:
         st = self._lib.tenmo_colsum_f32_static(x, M, N, ldx, out, beta, C.c_void_p(stream))
         if st != 0:
             raise TenmoError(st, self._lib.tenmo_cuda_last_error(None).decode())
+
+    def softmax_fwd(self, x, ldx, y, M, Cn):
+        self._call("tenmo_softmax_fwd_f32", x, ldx, y, M, Cn)
+
+    def softmax_bwd(self, y, g, dx, M, Cn, beta=0.0):
+        self._call("tenmo_softmax_bwd_f32", y, g, dx, beta, M, Cn)
 
     def ce_fwd(self, logits, ld, labels, label_is_i64, M, Cn, ignore_index, label_smoothing, reduction, softmax,
                loss, valid_count):

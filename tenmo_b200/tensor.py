@@ -22,7 +22,9 @@ from .lib import TenmoCuda, make_mat
 BACKWARD_RELU = 2
 BACKWARD_MATMUL_ND = 3
 BACKWARD_MATMUL_2D = 4
+BACKWARD_TRANSPOSE = 5
 BACKWARD_SIGMOID = 7
+BACKWARD_SOFTMAX = 8
 BACKWARD_CE_CLASS_INDICES_INT32 = 9
 BACKWARD_SUM = 16
 BACKWARD_MATRIX_VECTOR_MUL = 20
@@ -282,7 +284,12 @@ class Tensor:
 
     # -- views -------------------------------------------------------------------------------------------
     def transpose(self, axes=(-1, -2)) -> "Tensor":
-        return Tensor(self.buffer.transpose(axes), requires_grad=False)
+        """A stride view; the gradient flows back through the same permutation (BACKWARD_TRANSPOSE)."""
+        out = Tensor(self.buffer.transpose(axes), requires_grad=False)
+        if self.requires_grad:
+            out.requires_grad = True
+            out.ancestry = Ancestry(BACKWARD_TRANSPOSE, [self], arg=tuple(axes))
+        return out
 
     def view(self, shape, strides, offset=0) -> "Tensor":
         return Tensor(self.buffer.view(shape, strides, offset), requires_grad=False)
@@ -364,6 +371,19 @@ class Tensor:
         if track_grad and self.requires_grad:
             t.requires_grad = True
             t.ancestry = Ancestry(BACKWARD_SIGMOID, [self], arg=out)
+        return t
+
+    def softmax(self, track_grad: bool = True) -> "Tensor":
+        """Softmax over the last axis (Softmax.forward, softmax.mojo:222-305); the output is kept for backward."""
+        x = self.buffer.contiguous()
+        C = x.shape[-1]
+        M = x.numels() // C
+        out = NDBuffer.empty(x.shape)
+        handle().softmax_fwd(x.data_ptr(), C, out.data_ptr(), M, C)
+        t = Tensor(out)
+        if track_grad and self.requires_grad:
+            t.requires_grad = True
+            t.ancestry = Ancestry(BACKWARD_SOFTMAX, [self], arg=out)
         return t
 
     def sum(self) -> "Tensor":
@@ -448,6 +468,10 @@ class Backward:
             return Backward.sigmoid(output, retain_graph)
         elif code == BACKWARD_SUM:
             return Backward.sum(output, retain_graph)
+        elif code == BACKWARD_TRANSPOSE:
+            return Backward.transpose(output, retain_graph)
+        elif code == BACKWARD_SOFTMAX:
+            return Backward.softmax(output, retain_graph)
         elif code in (BACKWARD_MATRIX_VECTOR_MUL, BACKWARD_VECTOR_MATMUL, BACKWARD_DOT):
             return Backward.matmul_rank1(output, retain_graph)
         elif code in (BACKWARD_CE_CLASS_INDICES_INT64, BACKWARD_CE_CLASS_INDICES_INT32):
@@ -539,6 +563,30 @@ class Backward:
         parent.update_grad(dx)
         if not retain_graph:
             g.fill(0.0)
+        return [parent]
+
+    @staticmethod
+    def softmax(output: Tensor, retain_graph: bool):
+        """SoftmaxBackwardDelegate (softmax.mojo:206-213): y * (g - sum(g * y)) in one kernel."""
+        (parent,) = output.ancestry.parents
+        y = output.ancestry.arg
+        g = output.gradbox
+        C = y.shape[-1]
+        dx = NDBuffer.empty(y.shape)
+        handle().softmax_bwd(y.data_ptr(), g.data_ptr(), dx.data_ptr(), y.numels() // C, C)
+        parent.update_grad(dx)
+        if not retain_graph:
+            g.fill(0.0)
+        return [parent]
+
+    @staticmethod
+    def transpose(output: Tensor, retain_graph: bool):
+        """The upstream gradient, permuted back, is added to the parent (a host-side layout step next to the
+        path: the strided copy is torch's, not a kernel of this library)."""
+        (parent,) = output.ancestry.parents
+        parent.update_grad(output.gradbox.transpose(output.ancestry.arg).contiguous())
+        if not retain_graph:
+            output.gradbox.fill(0.0)
         return [parent]
 
     @staticmethod
