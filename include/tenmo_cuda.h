@@ -129,6 +129,9 @@ typedef struct {
     const float* b_lo;
     float* c_lo;
     const float* mul_mask;
+    const float* bias_m; /* optional M floats added per ROW: the per-channel bias when a convolution runs as
+                            W(C_out, C_in*KH*KW) . patches^T.  The SIMT kernel starts its accumulators at it,
+                            as the reference's convolution does (cnn.mojo:435). */
 } tenmo_gemm_opts;
 int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A,
                       const tenmo_mat* B, float* C, const tenmo_gemm_opts* opts);
@@ -179,6 +182,29 @@ int tenmo_colsum_f32(tenmo_ctx* ctx, const float* x, int64_t M, int64_t N, int64
  *     launch, but two calls whose kernels overlap on the GPU (different streams) race on it. */
 int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int64_t ldx, float* out, float beta,
                             void* cuda_stream);
+
+/* ---- convolution as GEMM and max pooling, NCHW ---------------------------------------------------------
+ * The reference's Conv2d (cnn.mojo:290-950) pads the image (pad.mojo) and then convolves directly; here the
+ * padding is an argument (pad = 0 reproduces the pre-padded contract) and the arithmetic is a GEMM between
+ * the kernel tensor viewed as (C_out, C_in*KH*KW) and the patch matrix these helpers produce / consume.
+ *   im2col   patches[(n,oy,ox), (c,ky,kx)] = x[n, c, oy*stride - pad + ky*dilation, ox*stride - pad + kx*dilation],
+ *            zero outside the image; patches is (N*Ho*Wo, C*KH*KW) row-major (the patch extraction of
+ *            compute_kernel_gradient, cnn.mojo:716-778).
+ *   col2im   adjoint of im2col: dx (N,C,H,W) (+)= gather of dpatches (compute_input_gradient, cnn.mojo:812-950).
+ *   channel_sum   out[c] (+)= sum over n and the S trailing elements of g viewed as (N, C, S)
+ *            (compute_bias_gradient, cnn.mojo:664-714).
+ *   maxpool2d fwd  k x k window, first maximum wins (strict >), argmax = y*W + x inside the (n,c) plane or -1
+ *            (pooling.mojo:301-402); bwd  dx = 0 then dx[argmax] += g (pooling.mojo:25-107). */
+int tenmo_conv_out_size(int64_t in, int k, int stride, int dilation, int pad, int64_t* out);
+int tenmo_im2col_f32(tenmo_ctx* ctx, const float* x, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW,
+                     int stride, int dilation, int pad, float* patches);
+int tenmo_col2im_f32(tenmo_ctx* ctx, const float* dpatches, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW,
+                     int stride, int dilation, int pad, float* dx, float beta);
+int tenmo_channel_sum_f32(tenmo_ctx* ctx, const float* g, int64_t N, int64_t C, int64_t S, float* out, float beta);
+int tenmo_maxpool2d_fwd_f32(tenmo_ctx* ctx, const float* x, int64_t N, int64_t C, int64_t H, int64_t W, int k, int stride,
+                            int pad, float* out, int64_t* argmax);
+int tenmo_maxpool2d_bwd_f32(tenmo_ctx* ctx, const float* g, const int64_t* argmax, int64_t N, int64_t C, int64_t H,
+                            int64_t W, int64_t Ho, int64_t Wo, float* dx);
 
 /* ---- softmax over the last axis (the step between the two GEMMs of an attention block) --------------
  * Forward y = exp(x - max) / sum (SoftmaxNdBuffer.softmax, softmax.mojo:30-48); x has leading dimension ldx,

@@ -206,6 +206,71 @@ def sigmoid_bwd(g, y) -> np.ndarray:
     return dx
 
 
+def _conv_sig():
+    L = lib()
+    if not hasattr(L, "_conv_bound"):
+        P, I64, I = C.c_void_p, C.c_int64, C.c_int
+        L.tenmo_ref_conv2d_fwd.argtypes = [P, P, P, P, I64, I64, I64, I64, I64, I, I, I, I, I]
+        L.tenmo_ref_conv2d_fwd.restype = None
+        L.tenmo_ref_conv2d_bwd.argtypes = [P, P, P, P, P, P, I64, I64, I64, I64, I64, I, I, I, I]
+        L.tenmo_ref_conv2d_bwd.restype = None
+        L.tenmo_ref_maxpool2d_fwd.argtypes = [P, P, P, I64, I64, I64, I, I, I]
+        L.tenmo_ref_maxpool2d_fwd.restype = None
+        L.tenmo_ref_maxpool2d_bwd.argtypes = [P, P, P, I64, I64, I64, I64, I64]
+        L.tenmo_ref_maxpool2d_bwd.restype = None
+        L._conv_bound = True
+    return L
+
+
+def pad_nchw(x, pad: int) -> np.ndarray:
+    """Constant zero padding of the two spatial dims, what the reference's Conv2D applies before the fused
+    convolution (pad.mojo)."""
+    x = _f32(x)
+    return np.ascontiguousarray(np.pad(x, ((0, 0), (0, 0), (pad, pad), (pad, pad)))) if pad else x
+
+
+def conv2d_fwd(x, kernel, bias, stride=1, dilation=1, pad=0, contract=1) -> np.ndarray:
+    xp, kernel = pad_nchw(x, pad), _f32(kernel)
+    N, Cin, Hp, Wp = xp.shape
+    Cout, _, KH, KW = kernel.shape
+    Ho = (Hp - ((KH - 1) * dilation + 1)) // stride + 1
+    Wo = (Wp - ((KW - 1) * dilation + 1)) // stride + 1
+    out = np.empty((N, Cout, Ho, Wo), np.float32)
+    b = _f32(bias) if bias is not None else None
+    _conv_sig().tenmo_ref_conv2d_fwd(_ptr(xp), _ptr(kernel), _ptr(b) if b is not None else None, _ptr(out), N, Cin, Hp, Wp,
+                                     Cout, KH, KW, stride, dilation, contract)
+    return out
+
+
+def conv2d_bwd(grad, x, kernel, stride=1, dilation=1, pad=0):
+    """Returns (dx, d_kernel, d_bias); dx is cropped back to the unpadded image (the Pad op's backward)."""
+    xp, kernel, grad = pad_nchw(x, pad), _f32(kernel), _f32(grad)
+    N, Cin, Hp, Wp = xp.shape
+    Cout, _, KH, KW = kernel.shape
+    dxp, dk, db = np.empty_like(xp), np.empty_like(kernel), np.empty(Cout, np.float32)
+    _conv_sig().tenmo_ref_conv2d_bwd(_ptr(grad), _ptr(xp), _ptr(kernel), _ptr(dxp), _ptr(dk), _ptr(db), N, Cin, Hp, Wp, Cout,
+                                     KH, KW, stride, dilation)
+    dx = dxp[:, :, pad:Hp - pad, pad:Wp - pad] if pad else dxp
+    return np.ascontiguousarray(dx), dk, db
+
+
+def maxpool2d_fwd(x, k=2, stride=2, pad=0):
+    x = _f32(x)
+    N, Cn, H, W = x.shape
+    Ho, Wo = (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
+    out, arg = np.empty((N, Cn, Ho, Wo), np.float32), np.empty((N, Cn, Ho, Wo), np.int64)
+    _conv_sig().tenmo_ref_maxpool2d_fwd(_ptr(x), _ptr(out), _ptr(arg), N * Cn, H, W, k, stride, pad)
+    return out, arg
+
+
+def maxpool2d_bwd(g, argmax, in_shape) -> np.ndarray:
+    g, argmax = _f32(g), np.ascontiguousarray(argmax, dtype=np.int64)
+    N, Cn, H, W = in_shape
+    dx = np.empty(in_shape, np.float32)
+    _conv_sig().tenmo_ref_maxpool2d_bwd(_ptr(g), _ptr(argmax), _ptr(dx), N * Cn, H, W, g.shape[2], g.shape[3])
+    return dx
+
+
 def softmax_fwd(x) -> np.ndarray:
     """SoftmaxNdBuffer.softmax over the last axis (softmax.mojo:30-48): exp(x - max) / sum, in fp32."""
     x = _f32(x)

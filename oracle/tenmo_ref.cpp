@@ -479,4 +479,98 @@ float tenmo_ref_mlp_step(int L, const int64_t* dims, float** W, float** b, float
     return loss;
 }
 
+void tenmo_ref_conv2d_fwd(const float* img, const float* kernel, const float* bias, float* out, int64_t N, int64_t Cin,
+                          int64_t Hp, int64_t Wp, int64_t Cout, int KH, int KW, int stride, int dilation, int contract) {
+    const int64_t eh = (int64_t)(KH - 1) * dilation + 1, ew = (int64_t)(KW - 1) * dilation + 1;
+    const int64_t Ho = (Hp - eh) / stride + 1, Wo = (Wp - ew) / stride + 1;
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t oy = 0; oy < Ho; ++oy)
+            for (int64_t ox = 0; ox < Wo; ++ox)
+                for (int64_t co = 0; co < Cout; ++co) {
+                    float acc = bias ? bias[co] : 0.f;  // accumulator initialised with the bias (cnn.mojo:435)
+                    for (int64_t ci = 0; ci < Cin; ++ci)
+                        for (int ky = 0; ky < KH; ++ky)
+                            for (int kx = 0; kx < KW; ++kx) {
+                                const float v = img[((n * Cin + ci) * Hp + oy * stride + (int64_t)ky * dilation) * Wp +
+                                                    ox * stride + (int64_t)kx * dilation];
+                                const float w = kernel[((co * Cin + ci) * KH + ky) * KW + kx];
+                                acc = scalar_site(v, w, acc, contract != 0);
+                            }
+                    out[((n * Cout + co) * Ho + oy) * Wo + ox] = acc;
+                }
+}
+
+void tenmo_ref_conv2d_bwd(const float* grad, const float* img, const float* kernel, float* d_img, float* d_kernel,
+                          float* d_bias, int64_t N, int64_t Cin, int64_t Hp, int64_t Wp, int64_t Cout, int KH, int KW,
+                          int stride, int dilation) {
+    const int64_t eh = (int64_t)(KH - 1) * dilation + 1, ew = (int64_t)(KW - 1) * dilation + 1;
+    const int64_t Ho = (Hp - eh) / stride + 1, Wo = (Wp - ew) / stride + 1;
+    if (d_bias)  // cnn.mojo:664-714: per channel, over n then the spatial positions
+        for (int64_t co = 0; co < Cout; ++co) {
+            float acc = 0.f;
+            for (int64_t n = 0; n < N; ++n)
+                for (int64_t s = 0; s < Ho * Wo; ++s) acc += grad[(n * Cout + co) * Ho * Wo + s];
+            d_bias[co] = acc;
+        }
+    if (d_kernel)  // cnn.mojo:716-809: grad (C_out, N*Ho*Wo) . patches (N*Ho*Wo, C_in*KH*KW), patch index ascending
+        for (int64_t co = 0; co < Cout; ++co)
+            for (int64_t ci = 0; ci < Cin; ++ci)
+                for (int ky = 0; ky < KH; ++ky)
+                    for (int kx = 0; kx < KW; ++kx) {
+                        float acc = 0.f;
+                        for (int64_t n = 0; n < N; ++n)
+                            for (int64_t oy = 0; oy < Ho; ++oy)
+                                for (int64_t ox = 0; ox < Wo; ++ox)
+                                    acc = fma_chain(grad[((n * Cout + co) * Ho + oy) * Wo + ox],
+                                                    img[((n * Cin + ci) * Hp + oy * stride + (int64_t)ky * dilation) * Wp +
+                                                        ox * stride + (int64_t)kx * dilation],
+                                                    acc);
+                        d_kernel[((co * Cin + ci) * KH + ky) * KW + kx] = acc;
+                    }
+    if (d_img) {  // cnn.mojo:812-950: scatter of kernel-weighted output gradients
+        std::memset(d_img, 0, sizeof(float) * (size_t)(N * Cin * Hp * Wp));
+        for (int64_t n = 0; n < N; ++n)
+            for (int64_t co = 0; co < Cout; ++co)
+                for (int64_t oy = 0; oy < Ho; ++oy)
+                    for (int64_t ox = 0; ox < Wo; ++ox) {
+                        const float g = grad[((n * Cout + co) * Ho + oy) * Wo + ox];
+                        for (int64_t ci = 0; ci < Cin; ++ci)
+                            for (int ky = 0; ky < KH; ++ky)
+                                for (int kx = 0; kx < KW; ++kx)
+                                    d_img[((n * Cin + ci) * Hp + oy * stride + (int64_t)ky * dilation) * Wp + ox * stride +
+                                          (int64_t)kx * dilation] += g * kernel[((co * Cin + ci) * KH + ky) * KW + kx];
+                    }
+    }
+}
+
+void tenmo_ref_maxpool2d_fwd(const float* x, float* out, int64_t* argmax, int64_t NC, int64_t H, int64_t W, int k, int stride,
+                             int pad) {
+    const int64_t Ho = (H + 2 * pad - k) / stride + 1, Wo = (W + 2 * pad - k) / stride + 1;
+    for (int64_t nc = 0; nc < NC; ++nc)
+        for (int64_t oy = 0; oy < Ho; ++oy)
+            for (int64_t ox = 0; ox < Wo; ++ox) {
+                float best = -INFINITY;
+                int64_t idx = -1;
+                for (int ky = 0; ky < k; ++ky)
+                    for (int kx = 0; kx < k; ++kx) {
+                        const int64_t y = oy * stride - pad + ky, xx = ox * stride - pad + kx;
+                        if (y < 0 || y >= H || xx < 0 || xx >= W) continue;
+                        const float v = x[(nc * H + y) * W + xx];
+                        if (v > best) { best = v; idx = y * W + xx; }
+                    }
+                out[(nc * Ho + oy) * Wo + ox] = best;
+                argmax[(nc * Ho + oy) * Wo + ox] = idx;
+            }
+}
+
+void tenmo_ref_maxpool2d_bwd(const float* g, const int64_t* argmax, float* dx, int64_t NC, int64_t H, int64_t W, int64_t Ho,
+                             int64_t Wo) {
+    std::memset(dx, 0, sizeof(float) * (size_t)(NC * H * W));
+    for (int64_t nc = 0; nc < NC; ++nc)
+        for (int64_t i = 0; i < Ho * Wo; ++i) {
+            const int64_t idx = argmax[nc * Ho * Wo + i];
+            if (idx >= 0) dx[nc * H * W + idx] += g[nc * Ho * Wo + i];
+        }
+}
+
 }  // extern "C"

@@ -110,6 +110,21 @@ float tenmo_ref_mlp_step(int n_layers, const int64_t* dims, float** W, float** b
                          float lr, float momentum, float weight_decay, float grad_scale, int do_update,
                          float* logits_out, const tenmo_ref_opts* opts);
 
+/* Conv2d on a PRE-PADDED image, NCHW (cnn.mojo:404-507): per output, the accumulator starts at the bias and
+ * adds img * kernel over (c_in, ky, kx) ascending.  contract = 1 fuses each multiply-add. */
+void tenmo_ref_conv2d_fwd(const float* img, const float* kernel, const float* bias, float* out, int64_t N, int64_t Cin,
+                          int64_t Hp, int64_t Wp, int64_t Cout, int KH, int KW, int stride, int dilation, int contract);
+/* Gradients of the same op (cnn.mojo:664-950): db per-channel sum, dW = grad (C_out, N*Ho*Wo) . patches,
+ * dX scatter of kernel-weighted gradients.  Any of d_img / d_kernel / d_bias may be NULL. */
+void tenmo_ref_conv2d_bwd(const float* grad, const float* img, const float* kernel, float* d_img, float* d_kernel,
+                          float* d_bias, int64_t N, int64_t Cin, int64_t Hp, int64_t Wp, int64_t Cout, int KH, int KW,
+                          int stride, int dilation);
+/* MaxPool2d (pooling.mojo:301-402, 25-107): k x k window walked row by row, strict >, argmax = y*W + x or -1. */
+void tenmo_ref_maxpool2d_fwd(const float* x, float* out, int64_t* argmax, int64_t NC, int64_t H, int64_t W, int k, int stride,
+                             int pad);
+void tenmo_ref_maxpool2d_bwd(const float* g, const int64_t* argmax, float* dx, int64_t NC, int64_t H, int64_t W, int64_t Ho,
+                             int64_t Wo);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,188 @@
+"""Conv2d (as GEMM) and MaxPool2d over the C ABI, NCHW, plus the CIFAR-shaped CNN training step.
+
+The reference's Conv2D (tenmo/cnn.mojo:18-271, net.mojo) pads, then runs a direct convolution; its backward
+uses an explicit im2col + matmul for the kernel gradient and a scatter for the input gradient.  Here the
+same arithmetic is four calls per direction:
+
+  forward   patches = im2col(x);  out[n] = W(C_out, K) . patches[n]^T + bias  (one batched GEMM whose output
+            is NCHW as it stands, bias per row, ReLU and its mask in the epilogue)
+  backward  db = channel_sum(g);  dW = sum_n g[n] . patches[n]  (batched GEMM + sum over the batch);
+            dpatches[n] = g[n]^T . W  (batched GEMM);  dx = col2im(dpatches)
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import lib as _lib
+from .lib import TenmoCuda, make_mat
+
+
+def out_size(n: int, k: int, stride: int, dilation: int, pad: int) -> int:
+    return (n + 2 * pad - ((k - 1) * dilation + 1)) // stride + 1
+
+
+class Conv2d:
+    """One convolution layer with pre-planned buffers for a fixed batch."""
+
+    def __init__(self, h: TenmoCuda, N, Cin, H, W, Cout, k, stride=1, dilation=1, pad=0, relu=False, device=0,
+                 need_dx=True):
+        self.h, self.N, self.Cin, self.H, self.W, self.Cout, self.k = h, N, Cin, H, W, Cout, k
+        self.stride, self.dil, self.pad, self.relu, self.need_dx = stride, dilation, pad, relu, need_dx
+        self.Ho, self.Wo = out_size(H, k, stride, dilation, pad), out_size(W, k, stride, dilation, pad)
+        self.K = Cin * k * k
+        f32 = dict(dtype=torch.float32, device=f"cuda:{device}")
+        S = self.Ho * self.Wo
+        self.patches = torch.empty(N * S, self.K, **f32)
+        self.out = torch.empty(N, Cout, self.Ho, self.Wo, **f32)
+        self.mask = torch.empty(N, Cout, self.Ho, self.Wo, **f32) if relu else None
+        self.dW_full = torch.empty(N, Cout, self.K, **f32)
+        self.dpatches = torch.empty(N * S, self.K, **f32) if need_dx else None
+        self.dx = torch.empty(N, Cin, H, W, **f32) if need_dx else None
+
+    def forward(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+        h, N, S, K = self.h, self.N, self.Ho * self.Wo, self.K
+        h.im2col(x.data_ptr(), N, self.Cin, self.H, self.W, self.k, self.k, self.stride, self.dil, self.pad,
+                 self.patches.data_ptr())
+        mW = make_mat(weight.data_ptr(), (self.Cout, K), (K, 1))                 # broadcast over the batch
+        mPt = make_mat(self.patches.data_ptr(), (N, K, S), (S * K, 1, K))         # patches[n]^T as a stride view
+        h.gemm_ex(self.Cout, S, K, mW, mPt, self.out.data_ptr(), bias_m=bias.data_ptr(),
+                  act=_lib.ACT_RELU if self.relu else _lib.ACT_NONE, aux=self.mask.data_ptr() if self.relu else 0)
+        return self.out
+
+    def backward(self, g: torch.Tensor, weight: torch.Tensor, dW: torch.Tensor, db: torch.Tensor):
+        """g is dL/d(out) AFTER the activation; with relu=True it is multiplied by the mask first (in place)."""
+        h, N, S, K, Cout = self.h, self.N, self.Ho * self.Wo, self.K, self.Cout
+        if self.relu:
+            h.relu_bwd(g.data_ptr(), self.mask.data_ptr(), g.data_ptr(), g.numel())
+        h.channel_sum(g.data_ptr(), N, Cout, S, db.data_ptr())
+        mG = make_mat(g.data_ptr(), (N, Cout, S), (Cout * S, S, 1))
+        mP = make_mat(self.patches.data_ptr(), (N, S, K), (S * K, K, 1))
+        h.gemm_ex(Cout, K, S, mG, mP, self.dW_full.data_ptr())
+        h.colsum(self.dW_full.data_ptr(), N, Cout * K, Cout * K, dW.data_ptr())   # sum over the batch
+        if self.need_dx:
+            mGt = make_mat(g.data_ptr(), (N, S, Cout), (Cout * S, 1, S))
+            mW = make_mat(weight.data_ptr(), (Cout, K), (K, 1))
+            h.gemm_ex(S, K, Cout, mGt, mW, self.dpatches.data_ptr())
+            h.col2im(self.dpatches.data_ptr(), N, self.Cin, self.H, self.W, self.k, self.k, self.stride, self.dil, self.pad,
+                     self.dx.data_ptr())
+        return self.dx
+
+
+class MaxPool2d:
+    def __init__(self, h: TenmoCuda, N, C, H, W, k=2, stride=2, pad=0, device=0):
+        self.h, self.N, self.C, self.H, self.W, self.k, self.stride, self.pad = h, N, C, H, W, k, stride, pad
+        self.Ho, self.Wo = (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
+        dev = f"cuda:{device}"
+        self.out = torch.empty(N, C, self.Ho, self.Wo, dtype=torch.float32, device=dev)
+        self.argmax = torch.empty(N, C, self.Ho, self.Wo, dtype=torch.int64, device=dev)
+        self.dx = torch.empty(N, C, H, W, dtype=torch.float32, device=dev)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        self.h.maxpool2d_fwd(x.data_ptr(), self.N, self.C, self.H, self.W, self.k, self.stride, self.pad, self.out.data_ptr(),
+                             self.argmax.data_ptr())
+        return self.out
+
+    def backward(self, g: torch.Tensor) -> torch.Tensor:
+        self.h.maxpool2d_bwd(g.data_ptr(), self.argmax.data_ptr(), self.N, self.C, self.H, self.W, self.Ho, self.Wo,
+                             self.dx.data_ptr())
+        return self.dx
+
+
+class CNNTrainer:
+    """The CIFAR-shaped CNN of the reference's examples as one planned step: conv3x3(3->32, pad 1) + ReLU,
+    maxpool 2, conv3x3(32->64, pad 1) + ReLU, maxpool 2, flatten (NCHW order), Linear 4096->10, softmax
+    cross-entropy, SGD momentum.  Parameters, gradients and velocities live in flat buffers so that the
+    data-parallel exchange is one all-reduce and the update one launch."""
+
+    def __init__(self, params: dict, batch: int, hw: int = 32, lr: float = 0.01, momentum: float = 0.9,
+                 handle: TenmoCuda | None = None, rank: int = 0, world: int = 1, unique_id: bytes | None = None,
+                 device: int | None = None):
+        self.dev = torch.cuda.current_device() if device is None else device
+        self.h = handle or TenmoCuda(self.dev).require()
+        self.rank, self.world, self.lr, self.momentum, self.batch = rank, world, float(lr), float(momentum), int(batch)
+        f32 = dict(dtype=torch.float32, device=f"cuda:{self.dev}")
+        names = ["conv1.weight", "conv1.bias", "conv2.weight", "conv2.bias", "fc.weight", "fc.bias"]
+        shapes = [tuple(np.shape(params[n])) for n in names]
+        offs, off = [], 0
+        for s in shapes:
+            offs.append(off)
+            off += (int(np.prod(s)) + 3) // 4 * 4
+        self.numel = off
+        self.P, self.G, self.V = (torch.zeros(off, **f32) for _ in range(3))
+        view = lambda buf, i: buf[offs[i]:offs[i] + int(np.prod(shapes[i]))].view(*shapes[i])
+        self.p = {n: view(self.P, i) for i, n in enumerate(names)}
+        self.g = {n: view(self.G, i) for i, n in enumerate(names)}
+        for n in names:
+            self.p[n].copy_(torch.from_numpy(np.ascontiguousarray(params[n], np.float32)))
+        B, C1, C2 = self.batch, shapes[0][0], shapes[2][0]
+        h = self.h
+        self.conv1 = Conv2d(h, B, shapes[0][1], hw, hw, C1, shapes[0][2], pad=1, relu=True, device=self.dev, need_dx=False)
+        self.pool1 = MaxPool2d(h, B, C1, hw, hw, device=self.dev)
+        self.conv2 = Conv2d(h, B, C1, hw // 2, hw // 2, C2, shapes[2][2], pad=1, relu=True, device=self.dev)
+        self.pool2 = MaxPool2d(h, B, C2, hw // 2, hw // 2, device=self.dev)
+        self.feat = C2 * (hw // 4) * (hw // 4)
+        self.classes = shapes[4][1]
+        assert shapes[4][0] == self.feat, "fc.weight rows must equal the flattened feature count"
+        self.X = torch.zeros(B, shapes[0][1], hw, hw, **f32)
+        self.y = torch.zeros(B, dtype=torch.int64, device=f"cuda:{self.dev}")
+        self.logits = torch.empty(B, self.classes, **f32)
+        self.softmax = torch.empty(B, self.classes, **f32)
+        self.dlogits = torch.empty(B, self.classes, **f32)
+        self.dfeat = torch.empty(B, self.feat, **f32)
+        self.loss = torch.zeros(1, **f32)
+        self.valid = torch.zeros(1, dtype=torch.int32, device=f"cuda:{self.dev}")
+        self.correct = torch.zeros(1, dtype=torch.int64, device=f"cuda:{self.dev}")
+        if world > 1:
+            self.h.dp_init(rank, world, unique_id)
+        torch.cuda.synchronize(self.dev)
+
+    def load_batch(self, X, y):
+        if not torch.is_tensor(X):
+            X = torch.from_numpy(np.ascontiguousarray(X, np.float32))
+        if not torch.is_tensor(y):
+            y = torch.from_numpy(np.ascontiguousarray(y, np.int64))
+        self.X.copy_(X, non_blocking=True)
+        self.y.copy_(y, non_blocking=True)
+
+    def step(self, X=None, y=None, update: bool = True):
+        h, B, C = self.h, self.batch, self.classes
+        h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
+        if X is not None:
+            self.load_batch(X, y)
+        p, g = self.p, self.g
+        a1 = self.pool1.forward(self.conv1.forward(self.X, p["conv1.weight"], p["conv1.bias"]))
+        a2 = self.pool2.forward(self.conv2.forward(a1, p["conv2.weight"], p["conv2.bias"]))
+        flat = make_mat(a2.data_ptr(), (B, self.feat), (self.feat, 1))            # Flatten: NCHW order, a view
+        mWfc = make_mat(p["fc.weight"].data_ptr(), (self.feat, C), (C, 1))
+        h.gemm_ex(B, C, self.feat, flat, mWfc, self.logits.data_ptr(), bias=p["fc.bias"].data_ptr())
+        h.ce_fwd(self.logits.data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
+                 self.loss.data_ptr(), self.valid.data_ptr())
+        h.ce_bwd(self.softmax.data_ptr(), self.y.data_ptr(), True, B, C, -100, 0.0, 0, 0, self.valid.data_ptr(),
+                 self.dlogits.data_ptr())
+        mdl = make_mat(self.dlogits.data_ptr(), (B, C), (C, 1))
+        h.gemm_ex(self.feat, C, B, make_mat(a2.data_ptr(), (self.feat, B), (1, self.feat)), mdl, g["fc.weight"].data_ptr(),
+                  colsum=g["fc.bias"].data_ptr())
+        h.gemm_ex(B, self.feat, C, mdl, make_mat(p["fc.weight"].data_ptr(), (C, self.feat), (1, C)), self.dfeat.data_ptr())
+        d2 = self.pool2.backward(self.dfeat)                                       # (B, C2, 16, 16)
+        d1p = self.conv2.backward(d2, p["conv2.weight"], g["conv2.weight"], g["conv2.bias"])
+        d1 = self.pool1.backward(d1p)
+        self.conv1.backward(d1, p["conv1.weight"], g["conv1.weight"], g["conv1.bias"])
+        if update:
+            if self.world > 1:
+                h.dp_allreduce_sum(self.G.data_ptr(), self.numel)
+            h.sgd_step([self.P.data_ptr()], [self.G.data_ptr()], [self.V.data_ptr()], [self.numel], self.lr, self.momentum,
+                       0.0, 1.0 / self.world)
+
+    def loss_value(self) -> float:
+        return float(self.loss.item())
+
+    def accuracy(self) -> int:
+        return self.h.accuracy(self.logits.data_ptr(), self.classes, self.y.data_ptr(), True, self.batch, self.classes,
+                               self.correct.data_ptr())
+
+    def params(self) -> dict:
+        return {n: t.detach().cpu().numpy() for n, t in self.p.items()}
+
+    def grads(self) -> dict:
+        return {n: t.detach().cpu().numpy() for n, t in self.g.items()}

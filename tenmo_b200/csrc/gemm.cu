@@ -72,6 +72,7 @@ int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K,
     p.beta = o->beta; p.bias = o->bias; p.act = o->act; p.aux = o->aux;
     p.a_lo = o->a_lo; p.b_lo = o->b_lo; p.c_lo = o->c_lo; p.mul_mask = o->mul_mask;
     p.ld_clo = (N + 3) / 4 * 4;
+    p.bias_m = o->bias_m;
 
     TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     int chosen = TENMO_ALGO_SIMT_FP32;

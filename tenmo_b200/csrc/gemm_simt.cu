@@ -133,9 +133,16 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
 
     float acc[TM][TN];
 #pragma unroll
-    for (int i = 0; i < TM; ++i)
+    for (int i = 0; i < TM; ++i) {
+        // a per-row bias is the accumulator's starting value, as in the reference's convolution (cnn.mojo:435)
+        float init = 0.f;
+        if (p.bias_m) {
+            const int64_t m = m0 + frag_index<TM, BM>(ty, i);
+            if (m < p.M) init = __ldg(p.bias_m + m);
+        }
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < TN; ++j) acc[i][j] = init;
+    }
 
     LoaderA la;
     LoaderB lb;

@@ -32,6 +32,7 @@ struct TenmoGemmParams {
     float* c_lo;            // optional: lo plane of the stored result, row-major with leading dimension ld_clo
     int64_t ld_clo;
     const float* mul_mask;  // optional (total_batch, M, N): result is multiplied by it before beta / store
+    const float* bias_m;    // optional M floats: per-row bias (the per-channel bias of a convolution)
     int tiles_m, tiles_n;
     int64_t total_batch;
     TenmoBatch batch;

@@ -57,6 +57,7 @@ struct TcParams {
     float* aux;
     const float* bias;
     const float* mul_mask;  // optional elementwise multiplier of the result (fused ReLU backward)
+    const float* bias_m;    // optional per-row bias
     float* c_lo;            // optional lo plane of the stored result
     int64_t ld_clo;
     int64_t M, N, K;
@@ -388,6 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             float* auxrow = p.aux ? p.aux + (batch * p.M + m) * p.N : nullptr;
             const float* maskrow = p.mul_mask ? p.mul_mask + (batch * p.M + m) * p.N : nullptr;
             float* clorow = p.c_lo ? p.c_lo + (batch * p.M + m) * p.ld_clo : nullptr;
+            const float row_bias = (p.bias_m && m < p.M) ? __ldg(p.bias_m + m) : 0.f;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
@@ -403,7 +405,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         float v[4], mk[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            float x = __uint_as_float(r[q + e]);
+                            float x = __uint_as_float(r[q + e]) + row_bias;
                             if (p.bias && n + e < p.N) x += __ldg(p.bias + n + e);
                             mk[e] = x > 0.f ? 1.f : 0.f;
                             v[e] = act_apply(x, p.act);
@@ -706,7 +708,7 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
 
     TcParams tp;
     tp.C = p.C; tp.aux = p.aux; tp.bias = p.bias;
-    tp.mul_mask = p.mul_mask; tp.c_lo = p.c_lo; tp.ld_clo = p.ld_clo;
+    tp.mul_mask = p.mul_mask; tp.c_lo = p.c_lo; tp.ld_clo = p.ld_clo; tp.bias_m = p.bias_m;
     tp.M = p.M; tp.N = p.N; tp.K = p.K; tp.total_batch = p.total_batch;
     tp.tiles_m = (int)((p.M + BM - 1) / BM);
     tp.tiles_n = (int)((p.N + bn - 1) / bn);

@@ -26,6 +26,8 @@ EXPORTS = [
     "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end", "tenmo_cuda_reserve_sms",
     "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
+    "tenmo_conv_out_size", "tenmo_im2col_f32", "tenmo_col2im_f32", "tenmo_channel_sum_f32", "tenmo_maxpool2d_fwd_f32",
+    "tenmo_maxpool2d_bwd_f32",
     "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
     "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
 ]
@@ -64,6 +66,7 @@ class GemmOpts(C.Structure):
         ("b_lo", C.c_void_p),
         ("c_lo", C.c_void_p),
         ("mul_mask", C.c_void_p),
+        ("bias_m", C.c_void_p),
     ]
 
 
@@ -111,6 +114,12 @@ def _bind(lib):
         "tenmo_sigmoid_bwd_f32": (I, [P, P, P, P, F, I64]),
         "tenmo_colsum_f32": (I, [P, P, I64, I64, I64, P, F]),
         "tenmo_colsum_f32_static": (I, [P, I64, I64, I64, P, F, P]),
+        "tenmo_conv_out_size": (I, [I64, I, I, I, I, C.POINTER(I64)]),
+        "tenmo_im2col_f32": (I, [P, P, I64, I64, I64, I64, I, I, I, I, I, P]),
+        "tenmo_col2im_f32": (I, [P, P, I64, I64, I64, I64, I, I, I, I, I, P, F]),
+        "tenmo_channel_sum_f32": (I, [P, P, I64, I64, I64, P, F]),
+        "tenmo_maxpool2d_fwd_f32": (I, [P, P, I64, I64, I64, I64, I, I, I, P, P]),
+        "tenmo_maxpool2d_bwd_f32": (I, [P, P, P, I64, I64, I64, I64, I64, I64, P]),
         "tenmo_softmax_fwd_f32": (I, [P, P, I64, P, I64, I64]),
         "tenmo_softmax_bwd_f32": (I, [P, P, P, P, F, I64, I64]),
         "tenmo_ce_fwd_f32": (I, [P, P, I64, P, I, I64, I64, I64, F, I, P, P, P]),
@@ -216,10 +225,10 @@ class TenmoCuda:
                    aux or None, colsum or None)
 
     def gemm_ex(self, M, N, K, A: Mat, B: Mat, c_ptr, *, algo=ALGO_AUTO, beta=0.0, bias=0, act=ACT_NONE, aux=0, colsum=0,
-                a_lo=0, b_lo=0, c_lo=0, mul_mask=0):
+                a_lo=0, b_lo=0, c_lo=0, mul_mask=0, bias_m=0):
         """tenmo_gemm_f32_ex: the GEMM with precomputed / produced lo planes and a fused mask multiply."""
         o = GemmOpts(beta, bias or None, act, aux or None, colsum or None, a_lo or None, b_lo or None, c_lo or None,
-                     mul_mask or None)
+                     mul_mask or None, bias_m or None)
         self._call("tenmo_gemm_f32_ex", algo, M, N, K, C.byref(A), C.byref(B), c_ptr, C.byref(o))
 
     def split_lo(self, X: Mat, rows, cols, lo_out, capacity):
@@ -260,6 +269,21 @@ class TenmoCuda:
         st = self._lib.tenmo_colsum_f32_static(x, M, N, ldx, out, beta, C.c_void_p(stream))
         if st != 0:
             raise TenmoError(st, self._lib.tenmo_cuda_last_error(None).decode())
+
+    def im2col(self, x, N, Cn, H, W, KH, KW, stride, dilation, pad, patches):
+        self._call("tenmo_im2col_f32", x, N, Cn, H, W, KH, KW, stride, dilation, pad, patches)
+
+    def col2im(self, dpatches, N, Cn, H, W, KH, KW, stride, dilation, pad, dx, beta=0.0):
+        self._call("tenmo_col2im_f32", dpatches, N, Cn, H, W, KH, KW, stride, dilation, pad, dx, beta)
+
+    def channel_sum(self, g, N, Cn, S, out, beta=0.0):
+        self._call("tenmo_channel_sum_f32", g, N, Cn, S, out, beta)
+
+    def maxpool2d_fwd(self, x, N, Cn, H, W, k, stride, pad, out, argmax):
+        self._call("tenmo_maxpool2d_fwd_f32", x, N, Cn, H, W, k, stride, pad, out, argmax)
+
+    def maxpool2d_bwd(self, g, argmax, N, Cn, H, W, Ho, Wo, dx):
+        self._call("tenmo_maxpool2d_bwd_f32", g, argmax, N, Cn, H, W, Ho, Wo, dx)
 
     def softmax_fwd(self, x, ldx, y, M, Cn):
         self._call("tenmo_softmax_fwd_f32", x, ldx, y, M, Cn)
