@@ -42,6 +42,16 @@ def host_cores() -> int:
         return os.cpu_count() or 1
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from one-pass ncu captures of this file's own
+# workloads (profiles/gemm_tc_kernel_8192_dram_traffic.md, profiles/hbm_kernels_colsum_relu_bwd_dram_traffic.md).
+# A number taken under a profiler is never timed here; only the byte counts are carried over.
+NCU_TRAFFIC_BYTES = {
+    ("gemm_tc_kernel", 8192): 4.822e9,
+    ("colsum_split_kernel", 8192 * 4096): 134.6e6,
+    ("ew_kernel<relu_bwd>", 8192 * 4096): 370.8e6,
+}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -228,6 +238,35 @@ def measure_mlps(h, rank, world, local_rank, timed, args):
     del tr
     torch.cuda.empty_cache()
 
+    # ---- CIFAR-shaped CNN, data parallel (global batch 256) ----
+    from tenmo_b200.cnn import CNNTrainer
+
+    gbc = 256
+    lo, hi = shard_rows(gbc, rank, world)
+    he = lambda shape, fan_in: (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+    cp = {"conv1.weight": he((32, 3, 3, 3), 27), "conv1.bias": np.zeros(32, np.float32),
+          "conv2.weight": he((64, 32, 3, 3), 288), "conv2.bias": np.zeros(64, np.float32),
+          "fc.weight": he((4096, 10), 4096), "fc.bias": np.zeros(10, np.float32)}
+    uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(torch.device("cuda", local_rank)))
+    cnn = CNNTrainer(cp, batch=hi - lo, handle=h, rank=rank, world=world, unique_id=uid, device=local_rank)
+    Xc = torch.rand(gbc, 3, 32, 32, generator=gen)[lo:hi].contiguous().pin_memory()
+    yc = torch.randint(0, 10, (gbc,), generator=gen)[lo:hi].contiguous().pin_memory()
+    cnn.load_batch(Xc, yc)
+    for _ in range(3):
+        cnn.step()
+    ms = timed(cnn.step, args.mlp_steps)
+    out["cnn"] = {
+        "metric": "cnn_train_samples_per_s", "value": gbc * args.mlp_steps / (ms * 1e-3), "unit": "samples/s",
+        "ms_per_step": ms / args.mlp_steps, "scaling": "strong", "global_batch": gbc, "per_rank_batch": hi - lo,
+        "steps": args.mlp_steps,
+        "config": "(256,3,32,32) U[0,1): conv3x3 3->32 pad1, ReLU, maxpool2, conv3x3 32->64 pad1, ReLU, maxpool2, "
+                  "Linear 4096->10, softmax-CE, SGD momentum 0.9; convolutions as im2col + strict-fp32 GEMM",
+    }
+    if world > 1:
+        h.dp_finalize()
+    del cnn
+    torch.cuda.empty_cache()
+
     # ---- MNIST-shaped MLP, one GPU ----
     if world == 1:
         dims = [784, 128, 32, 10]
@@ -387,7 +426,8 @@ def run_gpu_arm(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor" if algo == 1 else "fp32", "kernel": kernel, "achieved": achieved, "peak": peak,
-                         "unit": UNIT, "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "unit": UNIT, "frac": (achieved / peak) if achieved else None,
+                         "traffic": NCU_TRAFFIC_BYTES.get((kernel, S)), "traffic_unit": "bytes per launch (ncu, dram read+write)",
                          "launches_timed": n_kernel, "avg_launch_ms": kernel_ms / max(n_kernel, 1), "peak_note": peak_note},
         }
         if mlp:
@@ -432,7 +472,8 @@ def run_kernel_rooflines(args):
         gbs = alg_bytes / (ms * 1e-3) / 1e9
         print(json.dumps({"kernel": name, "avg_launch_ms": ms, "roofline": {
             "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-            "traffic": None, "peak_note": f"{peaks['source']} copy bandwidth"}, "algorithmic_bytes": alg_bytes,
+            "traffic": NCU_TRAFFIC_BYTES.get((name, 8192 * 4096)), "peak_note": f"{peaks['source']} copy bandwidth"},
+            "algorithmic_bytes": alg_bytes,
             "note": note}), flush=True)
 
     M, N, C = 8192, 4096, 1000
