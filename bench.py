@@ -390,6 +390,7 @@ def run_gpu_arm(args):
         step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
     h.check_device_status()
+    last_kernel = h.gemm_last_kernel()  # which GEMM kernel the steps above launched
 
     # release the GEMM buffers before the MLP legs
     del A, B, dC, C, dA, dB, host_in, host_out
@@ -404,12 +405,12 @@ def run_gpu_arm(args):
         info = h.device_info()
         peak = 2.0 * 128 * info["sm_count"] * info["sm_clock_khz"] * 1e3 / 1e12
         peak_note = "strict-FP32 SIMT peak = 2 x 128 lanes x SMs x max SM clock"
-        kernel = "gemm_simt_kernel"
+        kernel = last_kernel or "gemm_simt_kernel"
     else:
         peak = peaks["bf16_sustained"] / 2.0 / 3.0
         peak_note = (f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']:.1f} TFLOP/s / 2 (TF32 rate) / 3 "
                      f"(three products per fp32 product); burst-based figure {peaks['bf16_burst'] / 6.0:.1f}")
-        kernel = "gemm_tc_kernel"
+        kernel = last_kernel or "gemm_tc_kernel"
     achieved = (2.0 * M * N * K) / ((kernel_ms / max(n_kernel, 1)) * 1e-3) / 1e12 if n_kernel else None
 
     out = None

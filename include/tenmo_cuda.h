@@ -142,6 +142,10 @@ int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K,
 int tenmo_split_lo_f32(tenmo_ctx* ctx, const tenmo_mat* X, int64_t rows, int64_t cols, float* lo_out, int64_t capacity);
 /* Which kernel the last tenmo_gemm_f32 call on this context ran: TENMO_ALGO_SIMT_FP32 or _TC_3XTF32. */
 int tenmo_gemm_last_algo(tenmo_ctx* ctx);
+/* Name of the kernel that call launched: "gemm_tc_kernel", "gemm_simt_tma_kernel" (strict fp32, TMA-staged tiles)
+ * or "gemm_simt_kernel" (strict fp32, register-staged: any strides); "" before the first call.  No reference
+ * counterpart; tests and benchmarks use it to state which path was measured. */
+const char* tenmo_gemm_last_kernel(tenmo_ctx* ctx);
 
 /* ---- elementwise neighbours of the GEMM (un-fused forms, for a host that calls op by op) ---------- */
 /* out[m,n] = x[m,n] + bias[n]; Adder.forward bias case (addition.mojo:71-112,

@@ -5,10 +5,13 @@
 // kept in registers (32 values per lane), so the algorithmic traffic of 4*M*C read + 4*M*C written is
 // also the real traffic.  Rows with few classes (C <= 32) are handled by one thread per row in
 // ascending class order, which reproduces the reference's sequential sum exactly.
-// The scalar loss is produced on the device: per-row losses go to a scratch row, and the last CTA to
-// finish (ticket counter) adds them in row order and divides by the valid count, so there is no host
-// read-back between forward and backward (the reference synchronises and reads two scalars back,
-// kernels/crossentropy_fused_kernel.mojo:359-375).
+// The scalar loss is produced on the device by the last CTA to finish (ticket counter): for a batch of
+// up to 256 rows it adds the per-row losses from a scratch row in ascending row order (the reference's
+// sequential sum), beyond that every CTA leaves one (sum, count) partial and the last CTA adds those in a
+// fixed order.  There is no host read-back between forward and backward (the reference synchronises and
+// reads two scalars back, kernels/crossentropy_fused_kernel.mojo:359-375).
+// Backward: one warp per row (label and scale read once per row, 16-byte accesses); rows of fewer than 32
+// classes use a flat element-per-thread form.
 // Roofline: HBM; forward 8*M*C + 8*M bytes, backward 8*M*C + 8*M bytes.
 #include "common.cuh"
 
@@ -30,28 +33,33 @@ struct CeFwdArgs {
     float* softmax;
     float* loss;          // 1 float (mean/sum) or M floats (none)
     int32_t* valid_count;
-    float* row_loss;      // scratch, M floats (mean/sum only)
+    float* row_loss;      // scratch, M floats (mean/sum with M <= CE_SEQ_ROWS only)
+    float* part_loss;     // scratch, one partial loss sum per CTA (M > CE_SEQ_ROWS)
+    int32_t* part_cnt;    // scratch, one counted-row total per CTA
+    int vec;              // rows may be read / written as float4 (C % 4 == 0, ld % 4 == 0, 16-byte aligned bases)
     unsigned int* ticket; // one counter, zero between calls
     uint32_t* status;
 };
+
+constexpr int CE_SEQ_ROWS = 256;  // up to here the mean is the reference's row-ascending sequential sum
 
 __device__ __forceinline__ int64_t load_label(const void* labels, int is_i64, int64_t row) {
     return is_i64 ? reinterpret_cast<const int64_t*>(labels)[row] : (int64_t) reinterpret_cast<const int32_t*>(labels)[row];
 }
 
-// loss of one row from its statistics (crossentropy.mojo:368-389)
-__device__ __forceinline__ float row_loss_from_stats(const CeFwdArgs& p, int64_t row, float mx, float sum_exp,
-                                                     float sum_logits, bool* valid) {
-    const int64_t t = load_label(p.labels, p.label_is_i64, row);
-    *valid = false;
+// loss of one row from its statistics (crossentropy.mojo:368-389); t = the row's label, logit_t = its logit
+// (read early by the caller so that the two dependent loads overlap the row's own traffic);
+// *counted = the row enters the mean's divisor
+__device__ __forceinline__ float row_loss_from_stats(const CeFwdArgs& p, int64_t t, float logit_t, float mx, float sum_exp,
+                                                     float sum_logits, int* counted) {
+    *counted = 0;
     if (t == p.ignore_index) return 0.f;
+    *counted = 1;
     if (t < 0 || t >= p.C) {
         atomicOr(p.status, TENMO_DEV_BAD_LABEL);
         return 0.f;
     }
-    *valid = true;
     const float lse = logf(fmaxf(sum_exp, 1e-7f));
-    const float logit_t = __ldg(p.logits + row * p.ld + t);
     float loss = -((logit_t - mx) - lse);
     if (p.ls > 0.f) {
         const float inv_c = 1.f / (float)p.C;
@@ -65,7 +73,7 @@ __device__ __forceinline__ float row_loss_from_stats(const CeFwdArgs& p, int64_t
 // sequential `scalar_loss += loss`), fixed-shape tree otherwise.
 __device__ void ce_finalize(const CeFwdArgs& p, float* red_smem) {
     const int tid = threadIdx.x;
-    if (p.M <= 256) {  // a serial walk costs ~100 ns per row: fine for a small batch, not beyond
+    if (p.M <= CE_SEQ_ROWS) {  // a serial walk costs ~100 ns per row: fine for a small batch, not beyond
         if (tid == 0) {
             float s = 0.f;
             int cnt = 0;
@@ -81,9 +89,10 @@ __device__ void ce_finalize(const CeFwdArgs& p, float* red_smem) {
     }
     float s = 0.f;
     int cnt = 0;
-    for (int64_t r = tid; r < p.M; r += CE_THREADS) {
-        if (p.reduction != 2) s += __ldcg(p.row_loss + r);
-        cnt += load_label(p.labels, p.label_is_i64, r) != p.ignore_index ? 1 : 0;
+    // per-CTA partials (each the sum of that CTA's rows in a fixed order), added in a fixed order
+    for (int b = tid; b < (int)gridDim.x; b += CE_THREADS) {
+        s += __ldcg(p.part_loss + b);
+        cnt += __ldcg(p.part_cnt + b);
     }
     s = tenmo_warp_sum(s);
 #pragma unroll
@@ -102,15 +111,20 @@ __device__ void ce_finalize(const CeFwdArgs& p, float* red_smem) {
 }
 
 template <bool SMALL_C>
-__global__ void __launch_bounds__(CE_THREADS) ce_fwd_kernel(const CeFwdArgs p) {
+__global__ void __launch_bounds__(CE_THREADS, SMALL_C ? 2 : 3) ce_fwd_kernel(const CeFwdArgs p) {
     __shared__ float red_smem[2 * CE_WARPS];
     __shared__ bool is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool partials = p.M > CE_SEQ_ROWS;
+    float part_loss = 0.f;  // this thread's rows, ascending
+    int part_cnt = 0;
     if (SMALL_C) {
         // one thread per row, classes in ascending order
         for (int64_t row = (int64_t)blockIdx.x * CE_THREADS + threadIdx.x; row < p.M;
              row += (int64_t)gridDim.x * CE_THREADS) {
             const float* x = p.logits + row * p.ld;
+            const int64_t t = load_label(p.labels, p.label_is_i64, row);
+            const float logit_t = (t >= 0 && t < p.C) ? __ldg(x + t) : 0.f;
             float v[32];
             float mx = -3.4028234663852886e38f;
 #pragma unroll
@@ -120,9 +134,11 @@ __global__ void __launch_bounds__(CE_THREADS) ce_fwd_kernel(const CeFwdArgs p) {
 #pragma unroll
             for (int c = 0; c < 32; ++c)
                 if (c < p.C) { sum_logits += v[c]; v[c] = expf(v[c] - mx); sum_exp += v[c]; }
-            bool valid;
-            const float loss = row_loss_from_stats(p, row, mx, sum_exp, sum_logits, &valid);
-            if (p.reduction == 2) p.loss[row] = loss; else p.row_loss[row] = loss;
+            int counted;
+            const float loss = row_loss_from_stats(p, t, logit_t, mx, sum_exp, sum_logits, &counted);
+            if (p.reduction == 2) p.loss[row] = loss; else if (!partials) p.row_loss[row] = loss;
+            part_loss += loss;
+            part_cnt += counted;
             if (p.softmax) {
                 const float inv = 1.f / sum_exp;
 #pragma unroll
@@ -132,11 +148,27 @@ __global__ void __launch_bounds__(CE_THREADS) ce_fwd_kernel(const CeFwdArgs p) {
         }
     } else {
         const bool cached = p.C <= 32 * CE_REG;
+        const bool vec = cached && p.vec;
         for (int64_t row = (int64_t)blockIdx.x * CE_WARPS + warp; row < p.M; row += (int64_t)gridDim.x * CE_WARPS) {
             const float* x = p.logits + row * p.ld;
+            // label first (same address in every lane: one broadcast load), its logit once the row's own loads are out:
+            // the two dependent loads then overlap the row traffic instead of trailing it
+            const int64_t t = load_label(p.labels, p.label_is_i64, row);
             float v[CE_REG];
             float mx = -3.4028234663852886e38f;
-            if (cached) {
+            if (vec) {
+                // lane owns classes 4*(lane + 32*i) .. +3: eight 16-byte loads in flight per lane
+                const float4* x4 = reinterpret_cast<const float4*>(x);
+#pragma unroll
+                for (int i = 0; i < CE_REG / 4; ++i) {
+                    const int c = (lane + 32 * i) * 4;
+                    float4 t = make_float4(mx, mx, mx, mx);
+                    if (c < p.C) t = __ldg(x4 + lane + 32 * i);
+                    v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+                }
+#pragma unroll
+                for (int i = 0; i < CE_REG; ++i) mx = fmaxf(mx, v[i]);
+            } else if (cached) {
 #pragma unroll
                 for (int i = 0; i < CE_REG; ++i) {
                     const int64_t c = lane + 32 * i;
@@ -147,8 +179,15 @@ __global__ void __launch_bounds__(CE_THREADS) ce_fwd_kernel(const CeFwdArgs p) {
                 for (int64_t c = lane; c < p.C; c += 32) mx = fmaxf(mx, __ldg(x + c));
             }
             mx = tenmo_warp_max(mx);
+            const float logit_t = (t >= 0 && t < p.C) ? __ldg(x + t) : 0.f;
             float sum_exp = 0.f, sum_logits = 0.f;
-            if (cached) {
+            if (vec) {
+#pragma unroll
+                for (int i = 0; i < CE_REG; ++i) {
+                    const int c = (lane + 32 * (i / 4)) * 4;
+                    if (c < p.C) { sum_logits += v[i]; v[i] = expf(v[i] - mx); sum_exp += v[i]; }
+                }
+            } else if (cached) {
 #pragma unroll
                 for (int i = 0; i < CE_REG; ++i) {
                     const int64_t c = lane + 32 * i;
@@ -163,15 +202,18 @@ __global__ void __launch_bounds__(CE_THREADS) ce_fwd_kernel(const CeFwdArgs p) {
             }
             sum_exp = tenmo_warp_sum(sum_exp);
             sum_logits = tenmo_warp_sum(sum_logits);
-            if (lane == 0) {
-                bool valid;
-                const float loss = row_loss_from_stats(p, row, mx, sum_exp, sum_logits, &valid);
-                if (p.reduction == 2) p.loss[row] = loss; else p.row_loss[row] = loss;
-            }
             if (p.softmax) {
                 const float inv = 1.f / sum_exp;
                 float* sm = p.softmax + row * p.C;
-                if (cached) {
+                if (vec) {
+                    float4* sm4 = reinterpret_cast<float4*>(sm);
+#pragma unroll
+                    for (int i = 0; i < CE_REG / 4; ++i) {
+                        const int c = (lane + 32 * i) * 4;
+                        if (c < p.C)
+                            sm4[lane + 32 * i] = make_float4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
+                    }
+                } else if (cached) {
 #pragma unroll
                     for (int i = 0; i < CE_REG; ++i) {
                         const int64_t c = lane + 32 * i;
@@ -181,6 +223,29 @@ __global__ void __launch_bounds__(CE_THREADS) ce_fwd_kernel(const CeFwdArgs p) {
                     for (int64_t c = lane; c < p.C; c += 32) sm[c] = expf(__ldg(x + c) - mx) * inv;
                 }
             }
+            if (lane == 0) {
+                int counted;
+                const float loss = row_loss_from_stats(p, t, logit_t, mx, sum_exp, sum_logits, &counted);
+                if (p.reduction == 2) p.loss[row] = loss; else if (!partials) p.row_loss[row] = loss;
+                part_loss += loss;
+                part_cnt += counted;
+            }
+        }
+    }
+    if (partials) {
+        // this CTA's partial: lanes, then warps, in a fixed order
+        part_loss = tenmo_warp_sum(part_loss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part_cnt += __shfl_xor_sync(0xffffffffu, part_cnt, o);
+        int* cnt_smem = reinterpret_cast<int*>(red_smem + CE_WARPS);
+        if (lane == 0) { red_smem[warp] = part_loss; cnt_smem[warp] = part_cnt; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.f;
+            int c = 0;
+            for (int w = 0; w < CE_WARPS; ++w) { t += red_smem[w]; c += cnt_smem[w]; }
+            p.part_loss[blockIdx.x] = t;
+            p.part_cnt[blockIdx.x] = c;
         }
     }
     __threadfence();
@@ -205,10 +270,68 @@ struct CeBwdArgs {
     const int32_t* valid_count;
     float* dlogits;
     float beta;
+    int vec;  // rows may be moved as float4
 };
 
-// dlogits = ((softmax - (1-ls)*onehot) - ls/C) * valid * (upstream / scale)   (crossentropy.mojo:742-766,473-481)
+// one element: ((softmax - (1-ls)*onehot) - ls/C) * valid * (upstream / scale)   (crossentropy.mojo:742-766,473-481)
+__device__ __forceinline__ float ce_bwd_value(const CeBwdArgs& p, float sm, bool hit, bool ignored, float ls_uniform, float m) {
+    const float onehot = hit ? 1.f : 0.f;
+    float g;
+    if (p.ls > 0.f) g = (sm - __fmul_rn(onehot, 1.f - p.ls)) - ls_uniform;
+    else g = sm - onehot;
+    g = g * (ignored ? 0.f : 1.f);
+    return __fmul_rn(g, m);
+}
+
+// One warp per row: the label and the row's scale are read once, the row moves as 16-byte accesses.
 __global__ void __launch_bounds__(CE_THREADS) ce_bwd_kernel(const CeBwdArgs p) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float scale_mul = 1.f;
+    if (p.reduction != 2) {
+        const float ug = p.upstream ? __ldg(p.upstream) : 1.f;
+        const int vc = p.valid_count ? *p.valid_count : 0;
+        const float scale = (p.reduction == 0 && vc > 0) ? (float)vc : 1.f;
+        scale_mul = ug / scale;
+    }
+    const float ls_uniform = p.ls / (float)p.C;
+    for (int64_t row = (int64_t)blockIdx.x * CE_WARPS + warp; row < p.M; row += (int64_t)gridDim.x * CE_WARPS) {
+        const int64_t t = load_label(p.labels, p.label_is_i64, row);
+        const bool ignored = t == p.ignore_index;
+        const int64_t hit = ignored ? -1 : t;
+        const float m = p.reduction == 2 ? (p.upstream ? __ldg(p.upstream + row) : 1.f) : scale_mul;
+        const float* sm = p.softmax + row * p.C;
+        float* dl = p.dlogits + row * p.C;
+        if (p.vec) {
+            const float4* sm4 = reinterpret_cast<const float4*>(sm);
+            float4* dl4 = reinterpret_cast<float4*>(dl);
+            const int n4 = (int)(p.C >> 2);
+#pragma unroll 4
+            for (int q = lane; q < n4; q += 32) {
+                const float4 s = __ldg(sm4 + q);
+                const int64_t c = (int64_t)q * 4;
+                float4 g;
+                g.x = ce_bwd_value(p, s.x, c == hit, ignored, ls_uniform, m);
+                g.y = ce_bwd_value(p, s.y, c + 1 == hit, ignored, ls_uniform, m);
+                g.z = ce_bwd_value(p, s.z, c + 2 == hit, ignored, ls_uniform, m);
+                g.w = ce_bwd_value(p, s.w, c + 3 == hit, ignored, ls_uniform, m);
+                if (p.beta != 0.f) {
+                    const float4 o = dl4[q];
+                    g.x += o.x; g.y += o.y; g.z += o.z; g.w += o.w;
+                }
+                dl4[q] = g;
+            }
+        } else {
+            for (int64_t c = lane; c < p.C; c += 32) {
+                const float g = ce_bwd_value(p, __ldg(sm + c), c == hit, ignored, ls_uniform, m);
+                dl[c] = p.beta != 0.f ? dl[c] + g : g;
+            }
+        }
+    }
+}
+
+// Flat form for rows of fewer than 32 classes (a warp per row would idle most lanes).
+// dlogits = ((softmax - (1-ls)*onehot) - ls/C) * valid * (upstream / scale)   (crossentropy.mojo:742-766,473-481)
+__global__ void __launch_bounds__(CE_THREADS) ce_bwd_flat_kernel(const CeBwdArgs p) {
     const int64_t total = p.M * p.C;
     float scale_mul = 1.f;
     if (p.reduction != 2) {
@@ -257,22 +380,26 @@ int tenmo_ce_fwd_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, con
     p.logits = logits; p.ld = ld_logits; p.labels = labels; p.label_is_i64 = label_is_i64;
     p.M = M; p.C = C; p.ignore_index = ignore_index; p.ls = label_smoothing; p.reduction = reduction;
     p.softmax = softmax_out; p.loss = loss_dev; p.valid_count = valid_count_dev;
+    const int grid = C <= 32 ? tenmo_stream_grid(ctx, M, CE_THREADS, 4) : tenmo_stream_grid(ctx, M, CE_WARPS, 8);
+    // scratch: per-row losses for the sequential mean of a small batch, one (sum, count) pair per CTA beyond it
     p.row_loss = nullptr;
-    if (reduction != 2) {
+    p.part_loss = nullptr;
+    p.part_cnt = nullptr;
+    {
+        const size_t rows = M <= CE_SEQ_ROWS ? (size_t)M : 0;
         void* ws = nullptr;
-        int st = tenmo_workspace(ctx, (size_t)M * sizeof(float), &ws);
+        int st = tenmo_workspace(ctx, (rows + 2 * (size_t)grid) * sizeof(float), &ws);
         if (st != TENMO_OK) return st;
         p.row_loss = static_cast<float*>(ws);
+        p.part_loss = p.row_loss + rows;
+        p.part_cnt = reinterpret_cast<int32_t*>(p.part_loss + grid);
     }
+    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+    p.vec = (C % 4 == 0) && (ld_logits % 4 == 0) && aligned16(logits) && (!softmax_out || aligned16(softmax_out));
     p.ticket = reinterpret_cast<unsigned int*>(ctx->dev_status + 8);
     p.status = ctx->dev_status;
-    if (C <= 32) {
-        const int grid = tenmo_stream_grid(ctx, M, CE_THREADS, 4);
-        ce_fwd_kernel<true><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
-    } else {
-        const int grid = tenmo_stream_grid(ctx, M, CE_WARPS, 8);
-        ce_fwd_kernel<false><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
-    }
+    if (C <= 32) ce_fwd_kernel<true><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
+    else ce_fwd_kernel<false><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
     TENMO_LAUNCH_CHECK(ctx, "ce_fwd_kernel");
     return TENMO_OK;
 }
@@ -288,10 +415,16 @@ int tenmo_ce_bwd_f32(tenmo_ctx* ctx, const float* softmax, const void* labels, i
     if (!softmax || !labels || !dlogits) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_bwd: NULL pointer");
     if (reduction == 0 && !valid_count_dev) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_bwd: mean reduction needs valid_count_dev");
     CeBwdArgs p{softmax, labels, label_is_i64, M, C, ignore_index, label_smoothing, reduction, upstream_dev,
-                valid_count_dev, dlogits, beta};
+                valid_count_dev, dlogits, beta, 0};
+    p.vec = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(softmax) | reinterpret_cast<uintptr_t>(dlogits)) & 15u) == 0;
     TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    const int grid = tenmo_stream_grid(ctx, M * C, CE_THREADS * 4, 8);
-    ce_bwd_kernel<<<grid, CE_THREADS, 0, ctx->stream>>>(p);
+    if (C < 32) {
+        const int grid = tenmo_stream_grid(ctx, M * C, CE_THREADS * 4, 8);
+        ce_bwd_flat_kernel<<<grid, CE_THREADS, 0, ctx->stream>>>(p);
+    } else {
+        const int grid = tenmo_stream_grid(ctx, M, CE_WARPS, 8);
+        ce_bwd_kernel<<<grid, CE_THREADS, 0, ctx->stream>>>(p);
+    }
     TENMO_LAUNCH_CHECK(ctx, "ce_bwd_kernel");
     return TENMO_OK;
 }

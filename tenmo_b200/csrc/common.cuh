@@ -25,6 +25,7 @@ struct tenmo_ctx {
     char err[512] = {0};
     int64_t launches = 0;
     int last_gemm_algo = -1;
+    const char* last_gemm_kernel = "";
     // workspace (grown on demand, never shrunk): lo planes for the 3xTF32 kernel, reduction partials
     void* ws = nullptr;
     size_t ws_bytes = 0;

@@ -38,6 +38,7 @@ int build_batch(tenmo_ctx* ctx, const tenmo_mat* A, const tenmo_mat* B, TenmoBat
 extern "C" {
 
 int tenmo_gemm_last_algo(tenmo_ctx* ctx) { return ctx ? ctx->last_gemm_algo : -1; }
+const char* tenmo_gemm_last_kernel(tenmo_ctx* ctx) { return ctx ? ctx->last_gemm_kernel : ""; }
 
 int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A, const tenmo_mat* B,
                       float* C, const tenmo_gemm_opts* o) {

@@ -5,6 +5,8 @@
 // current one is multiplied).  A thread owns a TM x TN register tile; for 8x8 it is split into four
 // 4x4 quadrants so that the shared-memory reads of a warp are conflict-free 16-byte accesses.
 // Roofline: FP32 pipe, 2*M*N*K flop against 2 * 128 lanes * SMs * clock.
+#include <cstdlib>
+
 #include "gemm_simt.cuh"
 
 namespace {
@@ -284,6 +286,10 @@ int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p_in) {
     else cfg = 32;
     if (cfg == 128 && (p.M <= 64 || p.N <= 64)) cfg = 64;
     if (cfg == 64 && (p.M <= 32 || p.N <= 32)) cfg = 32;
+    if (cfg == 128 && p.K >= 64) {
+        const char* env = getenv("TENMO_SIMT_TMA");  // "0" keeps the register-staged kernel (for comparisons)
+        if (!(env && env[0] == '0') && tenmo_gemm_simt_tma_supported(ctx, p)) return tenmo_gemm_simt_tma_launch(ctx, p);
+    }
     const int bm = cfg, bn = cfg;
     p.tiles_m = (int)((p.M + bm - 1) / bm);
     p.tiles_n = (int)((p.N + bn - 1) / bn);
@@ -297,6 +303,7 @@ int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p_in) {
     else e = launch_cfg<32, 32, 32, 2, 2>(p, a_inner_k, b_inner_k, grid, ctx->stream);
     tenmo_prof_after(ctx);
     ctx->launches++;
+    ctx->last_gemm_kernel = "gemm_simt_kernel";
     if (e != cudaSuccess)
         return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_simt_kernel failed: %s", cudaGetErrorString(e));
     return TENMO_OK;

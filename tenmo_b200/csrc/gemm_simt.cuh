@@ -38,4 +38,10 @@ struct TenmoGemmParams {
     TenmoBatch batch;
 };
 
+// Picks the tile shape; large problems whose operands can be described by tensor maps (a unit-stride axis,
+// 16-byte aligned base and leading stride, batch dims that collapse to one stride) go to the TMA-staged
+// kernel of gemm_simt_tma.cu, everything else to the register-staged kernels of gemm_simt.cu.  Both give the
+// same bits.
 int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p);
+bool tenmo_gemm_simt_tma_supported(tenmo_ctx* ctx, const TenmoGemmParams& p);
+int tenmo_gemm_simt_tma_launch(tenmo_ctx* ctx, const TenmoGemmParams& p);

@@ -1,0 +1,386 @@
+// Strict-FP32 SIMT GEMM with TMA-staged shared-memory tiles.
+//
+// Same arithmetic contract as gemm_simt.cu: every output element is one k-ascending fmaf chain, so the two
+// kernels give identical bits.  What differs is how the 128 x 128 x 16 tiles reach shared memory: one
+// elected thread issues two tiled bulk copies (cp.async.bulk.tensor, no multicast) per k-tile into a ring
+// of four 16 KB stages guarded by full / empty mbarriers, so the 256 threads spend their issue slots on
+// fmaf and on the 16-byte fragment reads only: no global loads, no address arithmetic, no transposing
+// stores and no block-wide barrier in the k loop.  The FP32 pipe issues one warp instruction per cycle per
+// scheduler, which is also the issue limit, so every instruction that is not an fmaf costs throughput.
+//
+// Shared-memory layouts (what the copy engine writes) and the fragment reads that go with them:
+//   unit stride along m / n ("MN-major", e.g. row-major B or a transposed view of A): box {128, 16} ->
+//       [k][128] rows of 512 B; per k a thread reads its 8 values as two float4 (columns tx*4.. and 64+tx*4..).
+//   unit stride along k ("K-major", e.g. row-major A): box {16, 128} -> [row][16] rows of 64 B, written with
+//       the 64-byte swizzle (16-byte chunk index ^= (row >> 1) & 3).  TMA cannot transpose 32-bit elements,
+//       so fragments are read as float4 ALONG k (four k steps of one row at once) and the 4 x 8 x 8 fmaf
+//       block is ordered so that each accumulator still sees k ascending.  For operand B the thread's
+//       columns are interleaved (n = tx + 16 j): 16 consecutive rows hit all banks through the swizzle.
+// Fragments are shared inside a warp by same-address shared-memory reads (a broadcast costs no extra
+// wavefront); a shuffle-based exchange would put one more instruction per value into the issue stream.
+// Every mbarrier wait is bounded (2 s); on expiry the kernel raises the context status word, waits for the
+// copies it has in flight and returns without storing.
+// Roofline: FP32 pipe, 2*M*N*K flop against 2 * 128 lanes * SMs * clock.
+#include <cstdlib>
+
+#include "gemm_tc.cuh"
+#include "tma_util.cuh"
+
+namespace {
+
+constexpr int ST_BM = 128, ST_BN = 128, ST_BK = 16;
+constexpr int ST_STAGES = 4;
+constexpr int ST_THREADS = 256;
+constexpr int ST_TILE = 128 * ST_BK * 4;  // bytes of one operand tile
+constexpr int ST_STAGE = 2 * ST_TILE;
+constexpr int ST_SMEM = ST_STAGES * ST_STAGE + 1024 /*alignment slack*/ + 128 /*barriers, abort flag*/;
+constexpr int ST_GROUP_M = 16;  // tile order: groups of 16 row tiles walked column by column (L2 reuse)
+
+struct StParams {
+    float* C;
+    float* aux;
+    const float* bias;
+    const float* bias_m;
+    const float* mul_mask;
+    float* c_lo;
+    int64_t ld_clo;
+    int64_t M, N, K;
+    int tiles_m, tiles_n;
+    int a_batched, b_batched;
+    float beta;
+    int act;
+    int c_vec;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ float st_act(float v, int act) {
+    if (act == TENMO_ACT_RELU) return v > 0.f ? v : 0.f;
+    if (act == TENMO_ACT_SIGMOID) return 1.f / (1.f + expf(-v));
+    return v;
+}
+
+__device__ __forceinline__ float4 lds128(const uint8_t* p) { return *reinterpret_cast<const float4*>(p); }
+
+// row / column of register index i in the quadrant split (two runs of four, 64 apart)
+__device__ __forceinline__ int quad_index(int t, int i) { return (i >> 2) * 64 + t * 4 + (i & 3); }
+
+// A_K / B_K: the operand's unit-stride axis is k.  J_OUTER only reorders the independent fmaf of one k step
+// (columns outer, rows inner) where both loop orders are legal.
+template <bool A_K, bool B_K, bool J_OUTER>
+__global__ void __launch_bounds__(ST_THREADS, 2)
+gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const StParams p) {
+    extern __shared__ uint8_t st_smem_raw[];
+    const uint32_t smem_base = (smem_u32(st_smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = st_smem_raw + (smem_base - smem_u32(st_smem_raw));
+    const uint32_t bar_base = smem_base + ST_STAGES * ST_STAGE;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (ST_STAGES + s); };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + ST_STAGES * ST_STAGE + 8 * 2 * ST_STAGES);
+
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int tx = tid & 15, ty = tid >> 4;
+
+    // tile decode
+    const int64_t per_batch = (int64_t)p.tiles_m * p.tiles_n;
+    const int64_t batch = (int64_t)blockIdx.x / per_batch;
+    int tile_m, tile_n;
+    {
+        const int t = (int)((int64_t)blockIdx.x % per_batch);
+        const int group = t / (ST_GROUP_M * p.tiles_n);
+        const int first_m = group * ST_GROUP_M;
+        const int rows = min(ST_GROUP_M, p.tiles_m - first_m);
+        const int in_group = t - group * ST_GROUP_M * p.tiles_n;
+        tile_m = first_m + in_group % rows;
+        tile_n = in_group / rows;
+    }
+    const int m0 = tile_m * ST_BM, n0 = tile_n * ST_BN;
+    const int ba = p.a_batched ? (int)batch : 0, bb = p.b_batched ? (int)batch : 0;
+    const int k_tiles = (int)((p.K + ST_BK - 1) / ST_BK);
+
+    auto issue = [&](int kt) {  // both operand tiles of k-tile kt into stage kt % ST_STAGES (one thread)
+        const int s = kt % ST_STAGES;
+        const uint32_t sa = smem_base + s * ST_STAGE, sb = sa + ST_TILE;
+        const uint32_t bar = full_bar(s);
+        mbar_expect_tx(bar, (uint32_t)ST_STAGE);
+        if (A_K) tma_load_3d(sa, &map_a, bar, kt * ST_BK, m0, ba);
+        else tma_load_3d(sa, &map_a, bar, m0, kt * ST_BK, ba);
+        if (B_K) tma_load_3d(sb, &map_b, bar, kt * ST_BK, n0, bb);
+        else tma_load_3d(sb, &map_b, bar, n0, kt * ST_BK, bb);
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < ST_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), ST_THREADS / 32); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    int issued = 0;  // thread 0 only
+    if (tid == 0) {
+        const int pre = k_tiles < ST_STAGES ? k_tiles : ST_STAGES;
+        for (; issued < pre; ++issued) issue(issued);
+    }
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        // a per-row bias is the accumulator's starting value, as in the reference's convolution (cnn.mojo:435)
+        float init = 0.f;
+        if (p.bias_m) {
+            const int64_t m = (int64_t)m0 + quad_index(ty, i);
+            if (m < p.M) init = __ldg(p.bias_m + m);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = init;
+    }
+
+    // per-thread constants of the fragment addresses
+    const int a_base = A_K ? ty * 256 : ty * 16;   // K-major: row ty*4 at 64 B per row; MN-major: column ty*4
+    const int b_base = B_K ? tx * 64 : tx * 16;    // K-major: row tx (rows tx + 16 j); MN-major: column tx*4
+    const int sa0 = (2 * ty) & 3, sa1 = (2 * ty + 1) & 3;  // swizzle term (row >> 1) & 3 of rows ty*4 + {0,1} / {2,3}
+    const int sb = (tx >> 1) & 3;                            // of rows tx + 16 j
+
+    int kt = 0;
+    for (; kt < k_tiles; ++kt) {
+        const int s = kt % ST_STAGES;
+        if (!mbar_wait(full_bar(s), (uint32_t)((kt / ST_STAGES) & 1), abort_flag)) break;
+        const uint8_t* As = smem_gen + s * ST_STAGE;
+        const uint8_t* Bs = As + ST_TILE;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+            if (k4 == 1 && tid == 0 && kt >= 1 && issued < k_tiles) {
+                // refill the stage k-tile kt-1 used, once all eight warps have released it
+                const int prev = kt - 1;
+                if (mbar_wait(empty_bar(prev % ST_STAGES), (uint32_t)((prev / ST_STAGES) & 1), abort_flag)) {
+                    issue(issued);
+                    ++issued;
+                }
+            }
+            if (A_K) {
+                float af[8][4];  // af[i][kk] = A[row i][4*k4 + kk]
+                const int x0 = (k4 ^ sa0) << 4, x1 = (k4 ^ sa1) << 4;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int off = (i >> 2) * 4096 + (i & 3) * 64 + (((i & 3) >> 1) ? x1 : x0);
+                    *reinterpret_cast<float4*>(&af[i][0]) = lds128(As + a_base + off);
+                }
+                if (!B_K) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        float b[8];
+                        *reinterpret_cast<float4*>(&b[0]) = lds128(Bs + (k4 * 4 + kk) * 512 + b_base);
+                        *reinterpret_cast<float4*>(&b[4]) = lds128(Bs + (k4 * 4 + kk) * 512 + b_base + 256);
+                        if (J_OUTER) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) acc[i][j] = fmaf(af[i][kk], b[j], acc[i][j]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(af[i][kk], b[j], acc[i][j]);
+                        }
+                    }
+                } else {
+                    const int xb = (k4 ^ sb) << 4;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float bf[4];  // bf[kk] = B[4*k4 + kk][column tx + 16 j]
+                        *reinterpret_cast<float4*>(&bf[0]) = lds128(Bs + b_base + j * 1024 + xb);
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc[i][j] = fmaf(af[i][kk], bf[kk], acc[i][j]);
+                    }
+                }
+            } else {
+                if (!B_K) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        float a[8], b[8];
+                        *reinterpret_cast<float4*>(&a[0]) = lds128(As + (k4 * 4 + kk) * 512 + a_base);
+                        *reinterpret_cast<float4*>(&a[4]) = lds128(As + (k4 * 4 + kk) * 512 + a_base + 256);
+                        *reinterpret_cast<float4*>(&b[0]) = lds128(Bs + (k4 * 4 + kk) * 512 + b_base);
+                        *reinterpret_cast<float4*>(&b[4]) = lds128(Bs + (k4 * 4 + kk) * 512 + b_base + 256);
+                        if (J_OUTER) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                        }
+                    }
+                } else {
+                    float am[4][8];  // am[kk][i] = A[row i][4*k4 + kk]
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        *reinterpret_cast<float4*>(&am[kk][0]) = lds128(As + (k4 * 4 + kk) * 512 + a_base);
+                        *reinterpret_cast<float4*>(&am[kk][4]) = lds128(As + (k4 * 4 + kk) * 512 + a_base + 256);
+                    }
+                    const int xb = (k4 ^ sb) << 4;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float bf[4];
+                        *reinterpret_cast<float4*>(&bf[0]) = lds128(Bs + b_base + j * 1024 + xb);
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc[i][j] = fmaf(am[kk][i], bf[kk], acc[i][j]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(s));
+    }
+
+    __syncthreads();  // every wait above is bounded, so all threads arrive here
+    if (*abort_flag) {
+        if (tid == 0) {
+            // copies still in flight target this CTA's shared memory: wait for them (bounded) before leaving
+            for (int t = kt; t < issued; ++t) {
+                const uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(full_bar(t % ST_STAGES), (uint32_t)((t / ST_STAGES) & 1)))
+                    if (globaltimer_ns() - t0 > TENMO_WAIT_LIMIT_NS) break;
+            }
+            atomicOr(p.status, TENMO_DEV_TIMEOUT);
+        }
+        return;
+    }
+
+    // Epilogue: bias, activation (+ mask), multiplier, accumulate, store.
+    float* C = p.C + batch * p.M * p.N;
+    float* AUX = p.aux ? p.aux + batch * p.M * p.N : nullptr;
+    const float* MASK = p.mul_mask ? p.mul_mask + batch * p.M * p.N : nullptr;
+    float* CLO = p.c_lo ? p.c_lo + batch * p.M * p.ld_clo : nullptr;
+    const bool extended = MASK != nullptr || CLO != nullptr;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int64_t m = (int64_t)m0 + quad_index(ty, i);
+        if (m >= p.M) continue;
+        if (!B_K && p.c_vec && !extended) {
+#pragma unroll
+            for (int jg = 0; jg < 2; ++jg) {
+                const int64_t n = (int64_t)n0 + jg * 64 + tx * 4;
+                if (n >= p.N) continue;  // N % 4 == 0 on this path, so n < N covers n + 3
+                float v[4], mk[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float x = acc[i][jg * 4 + q];
+                    if (p.bias) x += __ldg(p.bias + n + q);
+                    mk[q] = x > 0.f ? 1.f : 0.f;
+                    v[q] = st_act(x, p.act);
+                }
+                float* dst = C + m * p.N + n;
+                float4 o = make_float4(v[0], v[1], v[2], v[3]);
+                if (p.beta != 0.f) {
+                    const float4 old = *reinterpret_cast<const float4*>(dst);
+                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dst) = o;
+                if (AUX) *reinterpret_cast<float4*>(AUX + m * p.N + n) = make_float4(mk[0], mk[1], mk[2], mk[3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int64_t n = (int64_t)n0 + (B_K ? tx + 16 * j : quad_index(tx, j));
+                if (n >= p.N) continue;
+                float x = acc[i][j];
+                if (p.bias) x += __ldg(p.bias + n);
+                const float mk = x > 0.f ? 1.f : 0.f;
+                float o = st_act(x, p.act);
+                if (MASK) o *= __ldg(MASK + m * p.N + n);
+                float* dst = C + m * p.N + n;
+                if (p.beta != 0.f) o += *dst;
+                *dst = o;
+                if (AUX) AUX[m * p.N + n] = mk;
+                if (CLO) CLO[m * p.ld_clo + n] = tenmo_tf32_lo(o);
+            }
+        }
+    }
+}
+
+// K-major operand: box {16 k, 128 rows}, 64-byte swizzle; MN-major: box {128, 16 k}, no swizzle (the rows of
+// 512 B are read 16 bytes per lane, which is conflict-free as it lies).  Out-of-range elements read as zero.
+int st_encode_map(tenmo_ctx* ctx, CUtensorMap* map, const float* base, const TenmoOperandPlan& o) {
+    TenmoEncodeTiledFn fn = reinterpret_cast<TenmoEncodeTiledFn>(ctx->encode_tiled);
+    cuuint64_t dims[3] = {(cuuint64_t)o.inner, (cuuint64_t)o.outer, (cuuint64_t)o.batches};
+    cuuint64_t strides[2] = {(cuuint64_t)o.ld * 4, (cuuint64_t)(o.batched ? o.batch_stride : o.ld * o.outer) * 4};
+    if (strides[1] % 16 != 0) strides[1] = (strides[1] + 15) / 16 * 16;  // unused when there is one slice
+    cuuint32_t box[3] = {o.mn_major ? 128u : (cuuint32_t)ST_BK, o.mn_major ? (cuuint32_t)ST_BK : 128u, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, o.mn_major ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return tenmo_set_error(ctx, TENMO_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (inner %lld outer %lld ld %lld)",
+                               (int)r, (long long)o.inner, (long long)o.outer, (long long)o.ld);
+    return TENMO_OK;
+}
+
+template <bool J_OUTER>
+cudaError_t st_launch(bool a_k, bool b_k, unsigned grid, cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
+                      const StParams& sp) {
+#define ST_LAUNCH(AK, BKM)                                                                                             \
+    {                                                                                                                  \
+        cudaError_t e = cudaFuncSetAttribute(gemm_simt_tma_kernel<AK, BKM, J_OUTER>,                                   \
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM);                    \
+        if (e != cudaSuccess) return e;                                                                                \
+        gemm_simt_tma_kernel<AK, BKM, J_OUTER><<<grid, ST_THREADS, ST_SMEM, s>>>(ma, mb, sp);                          \
+    }
+    if (a_k) { if (b_k) ST_LAUNCH(true, true) else ST_LAUNCH(true, false) }
+    else { if (b_k) ST_LAUNCH(false, true) else ST_LAUNCH(false, false) }
+#undef ST_LAUNCH
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tenmo_gemm_simt_tma_supported(tenmo_ctx* ctx, const TenmoGemmParams& p) {
+    (void)ctx;
+    TenmoOperandPlan a, b;
+    char why[160];
+    if (p.M < 1 || p.N < 1) return false;
+    return tenmo_make_plan(p, &a, &b, why, sizeof(why));
+}
+
+int tenmo_gemm_simt_tma_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
+    int st = tenmo_tma_init(ctx);
+    if (st != TENMO_OK) return st;
+    TenmoOperandPlan a, b;
+    char why[160];
+    if (!tenmo_make_plan(p, &a, &b, why, sizeof(why))) return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm_simt_tma: %s", why);
+    CUtensorMap ma, mb;
+    if ((st = st_encode_map(ctx, &ma, p.A, a)) != TENMO_OK) return st;
+    if ((st = st_encode_map(ctx, &mb, p.B, b)) != TENMO_OK) return st;
+
+    StParams sp;
+    sp.C = p.C; sp.aux = p.aux; sp.bias = p.bias; sp.bias_m = p.bias_m; sp.mul_mask = p.mul_mask;
+    sp.c_lo = p.c_lo; sp.ld_clo = p.ld_clo;
+    sp.M = p.M; sp.N = p.N; sp.K = p.K;
+    sp.tiles_m = (int)((p.M + ST_BM - 1) / ST_BM);
+    sp.tiles_n = (int)((p.N + ST_BN - 1) / ST_BN);
+    sp.a_batched = a.batched; sp.b_batched = b.batched;
+    sp.beta = p.beta; sp.act = p.act;
+    sp.c_vec = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) &&
+               (!p.aux || (reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0);
+    sp.status = ctx->dev_status;
+    const int64_t grid = (int64_t)sp.tiles_m * sp.tiles_n * p.total_batch;
+    if (grid <= 0 || grid > 0x7fffffffLL)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_simt_tma: grid of %lld tiles is out of range", (long long)grid);
+    const char* env = getenv("TENMO_SIMT_ORDER");
+    const bool j_outer = env && atoi(env) == 1;
+    tenmo_prof_before(ctx);
+    cudaError_t e = j_outer ? st_launch<true>(!a.mn_major, !b.mn_major, (unsigned)grid, ctx->stream, ma, mb, sp)
+                            : st_launch<false>(!a.mn_major, !b.mn_major, (unsigned)grid, ctx->stream, ma, mb, sp);
+    tenmo_prof_after(ctx);
+    ctx->launches++;
+    ctx->last_gemm_kernel = "gemm_simt_tma_kernel";
+    if (e != cudaSuccess)
+        return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_simt_tma_kernel failed: %s", cudaGetErrorString(e));
+    return TENMO_OK;
+}

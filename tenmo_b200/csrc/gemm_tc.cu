@@ -27,6 +27,7 @@
 #include <cstdlib>
 
 #include "gemm_tc.cuh"
+#include "tma_util.cuh"
 
 namespace {
 
@@ -40,7 +41,6 @@ static_assert(BK == 32 || BK == 16, "BK must be 16 or 32");
 constexpr int UMMA_K = 8;                    // tf32 k per instruction
 constexpr int SQ = 4;                        // depth of the tile-id ring between the scheduler and its consumers
 constexpr int TILE_COUNTERS = 32;            // ring of global tile counters, one per GEMM launch in flight
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 template <int BN>
 struct TcCfg {
@@ -74,51 +74,6 @@ struct TcParams {
 // ---------------------------------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait: false when another role aborted or the time limit ran out (then *abort is raised).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
-    uint64_t t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if ((it & 255u) == 255u) {
-            if (*abort) return false;
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_NS) { *abort = 1; return false; }
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-        : "memory");
-}
-
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -295,7 +250,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         asm volatile(
                             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                             : "=r"(done) : "r"(full_bar(s)), "r"(ph) : "memory");
-                        if (done || globaltimer_ns() - t0 > WAIT_LIMIT_NS) break;
+                        if (done || globaltimer_ns() - t0 > TENMO_WAIT_LIMIT_NS) break;
                     }
                 }
             }
@@ -498,22 +453,10 @@ split_lo_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t 
 // ---------------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-struct OperandPlan {
-    bool mn_major;        // unit-stride axis is m / n (not k)
-    int64_t inner, outer; // extents of the storage matrix (inner = unit-stride axis)
-    int64_t ld;           // elements between consecutive `outer` indices
-    int batched;          // 1: one slice per batch with a uniform stride, 0: broadcast
-    int64_t batch_stride; // elements
-    int64_t batches;      // slices that exist in memory (1 when broadcast)
-    int64_t ld_lo, bstride_lo;
-};
+}  // namespace
 
 // Collapse an operand's (possibly broadcast) batch dims into "one uniform stride" or "broadcast".
-bool collapse_batch(const TenmoBatch& b, const int64_t* stride, int64_t total, int* batched, int64_t* bstride) {
+bool tenmo_collapse_batch(const TenmoBatch& b, const int64_t* stride, int64_t total, int* batched, int64_t* bstride) {
     if (total == 1) { *batched = 0; *bstride = 0; return true; }
     bool all_zero = true;
     for (int d = 0; d < b.rank; ++d)
@@ -531,8 +474,8 @@ bool collapse_batch(const TenmoBatch& b, const int64_t* stride, int64_t total, i
     return true;
 }
 
-bool plan_operand(int64_t rows, int64_t cols, int64_t rs, int64_t cs, bool rows_are_k, const float* ptr,
-                  const TenmoBatch& b, const int64_t* bstrides, int64_t total_batch, OperandPlan* o, const char* name,
+bool tenmo_plan_operand(int64_t rows, int64_t cols, int64_t rs, int64_t cs, bool rows_are_k, const float* ptr,
+                  const TenmoBatch& b, const int64_t* bstrides, int64_t total_batch, TenmoOperandPlan* o, const char* name,
                   char* why, size_t why_len) {
     // rows x cols view; k is the row index when rows_are_k (operand B) else the column index (operand A)
     bool unit_cols = (cs == 1) || cols == 1, unit_rows = (rs == 1) || rows == 1;
@@ -546,7 +489,7 @@ bool plan_operand(int64_t rows, int64_t cols, int64_t rs, int64_t cs, bool rows_
         return false;
     }
     if (ld < inner) { snprintf(why, why_len, "%s rows overlap", name); return false; }
-    if (!collapse_batch(b, bstrides, total_batch, &o->batched, &o->batch_stride)) {
+    if (!tenmo_collapse_batch(b, bstrides, total_batch, &o->batched, &o->batch_stride)) {
         snprintf(why, why_len, "%s batch dims do not collapse to one stride", name);
         return false;
     }
@@ -562,18 +505,20 @@ bool plan_operand(int64_t rows, int64_t cols, int64_t rs, int64_t cs, bool rows_
     return true;
 }
 
-bool make_plan(const TenmoGemmParams& p, OperandPlan* a, OperandPlan* b, char* why, size_t why_len) {
+bool tenmo_make_plan(const TenmoGemmParams& p, TenmoOperandPlan* a, TenmoOperandPlan* b, char* why, size_t why_len) {
     if (p.K < 1) { snprintf(why, why_len, "K == 0"); return false; }
     if (p.M > 0x7fffffffLL || p.N > 0x7fffffffLL || p.K > 0x7fffffffLL || p.total_batch > 0x7fffffffLL) {
         snprintf(why, why_len, "dimension exceeds 2^31"); return false;
     }
-    if (!plan_operand(p.M, p.K, p.a_rs, p.a_cs, false, p.A, p.batch, p.batch.a_stride, p.total_batch, a, "A", why, why_len)) return false;
-    if (!plan_operand(p.K, p.N, p.b_rs, p.b_cs, true, p.B, p.batch, p.batch.b_stride, p.total_batch, b, "B", why, why_len)) return false;
+    if (!tenmo_plan_operand(p.M, p.K, p.a_rs, p.a_cs, false, p.A, p.batch, p.batch.a_stride, p.total_batch, a, "A", why, why_len)) return false;
+    if (!tenmo_plan_operand(p.K, p.N, p.b_rs, p.b_cs, true, p.B, p.batch, p.batch.b_stride, p.total_batch, b, "B", why, why_len)) return false;
     return true;
 }
 
-int encode_map(tenmo_ctx* ctx, CUtensorMap* map, const float* base, const OperandPlan& o, bool lo, int box_outer) {
-    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+namespace {
+
+int encode_map(tenmo_ctx* ctx, CUtensorMap* map, const float* base, const TenmoOperandPlan& o, bool lo, int box_outer) {
+    TenmoEncodeTiledFn fn = reinterpret_cast<TenmoEncodeTiledFn>(ctx->encode_tiled);
     const int64_t ld = lo ? o.ld_lo : o.ld;
     const int64_t bs = lo ? o.bstride_lo : (o.batched ? o.batch_stride : ld * o.outer);
     cuuint64_t dims[3] = {(cuuint64_t)o.inner, (cuuint64_t)o.outer, (cuuint64_t)o.batches};
@@ -609,7 +554,9 @@ cudaError_t launch_tc(bool a_mn, bool b_mn, int grid, cudaStream_t s, const CUte
     return cudaGetLastError();
 }
 
-int tc_init(tenmo_ctx* ctx) {
+}  // namespace
+
+int tenmo_tma_init(tenmo_ctx* ctx) {
     if (ctx->tc_ready) return TENMO_OK;
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -623,12 +570,11 @@ int tc_init(tenmo_ctx* ctx) {
     return TENMO_OK;
 }
 
-}  // namespace
 
 bool tenmo_gemm_tc_supported(tenmo_ctx* ctx, const TenmoGemmParams& p, char* why, size_t why_len) {
     (void)ctx;
-    OperandPlan a, b;
-    return make_plan(p, &a, &b, why, why_len);
+    TenmoOperandPlan a, b;
+    return tenmo_make_plan(p, &a, &b, why, why_len);
 }
 
 bool tenmo_gemm_tc_profitable(tenmo_ctx* ctx, const TenmoGemmParams& p) {
@@ -640,9 +586,9 @@ bool tenmo_gemm_tc_profitable(tenmo_ctx* ctx, const TenmoGemmParams& p) {
 int tenmo_split_lo_launch(tenmo_ctx* ctx, const float* base, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
                           const TenmoBatch& batch, const int64_t* bstrides, int64_t total_batch, float* out,
                           int64_t* floats_written) {
-    OperandPlan o;
+    TenmoOperandPlan o;
     char why[160];
-    if (!plan_operand(rows, cols, rs, cs, false, base, batch, bstrides, total_batch, &o, "X", why, sizeof(why)))
+    if (!tenmo_plan_operand(rows, cols, rs, cs, false, base, batch, bstrides, total_batch, &o, "X", why, sizeof(why)))
         return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "split_lo: %s", why);
     if (reinterpret_cast<uintptr_t>(out) & 15u) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "split_lo: output is not 16-byte aligned");
     const int64_t work = o.batches * o.outer * (o.ld_lo / 4);
@@ -655,11 +601,11 @@ int tenmo_split_lo_launch(tenmo_ctx* ctx, const float* base, int64_t rows, int64
 }
 
 int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
-    int st = tc_init(ctx);
+    int st = tenmo_tma_init(ctx);
     if (st != TENMO_OK) return st;
-    OperandPlan a, b;
+    TenmoOperandPlan a, b;
     char why[160];
-    if (!make_plan(p, &a, &b, why, sizeof(why))) return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm_tc: %s", why);
+    if (!tenmo_make_plan(p, &a, &b, why, sizeof(why))) return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm_tc: %s", why);
 
     // lo planes: taken from the caller when supplied (same storage geometry: outer x inner rounded up to 4,
     // batches back to back), else split here into the workspace [A_lo | B_lo]
@@ -675,7 +621,7 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     if ((p.a_lo && (reinterpret_cast<uintptr_t>(p.a_lo) & 15u)) || (p.b_lo && (reinterpret_cast<uintptr_t>(p.b_lo) & 15u)))
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_tc: a supplied lo plane is not 16-byte aligned");
 
-    auto split = [&](const float* src, float* dst, const OperandPlan& o) -> int {
+    auto split = [&](const float* src, float* dst, const TenmoOperandPlan& o) -> int {
         const int64_t work = o.batches * o.outer * (o.ld_lo / 4);
         const int grid = tenmo_stream_grid(ctx, work, 256 * 4, 8);
         split_lo_kernel<<<grid, 256, 0, ctx->stream>>>(src, dst, o.outer, o.inner, o.ld, o.ld_lo, o.batches,
@@ -731,6 +677,7 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
                                   : launch_tc<64>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp);
     tenmo_prof_after(ctx);
     ctx->launches++;
+    ctx->last_gemm_kernel = "gemm_tc_kernel";
     if (e != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_tc_kernel failed: %s", cudaGetErrorString(e));
     return TENMO_OK;
 }

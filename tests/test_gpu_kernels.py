@@ -318,7 +318,7 @@ def test_ce_reference_literals(g):
 
 
 @pytest.mark.parametrize("mc", [(64, 10), (256, 10), (3, 3), (1, 1), (100, 33), (1024, 1000), (8192, 1000), (70, 2500),
-                                (5000, 7)], ids=str)
+                                (5000, 7), (300, 36), (257, 64), (999, 1002), (513, 1024), (40, 2048)], ids=str)
 @pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
 def test_ce_vs_oracle(g, oracle, mc, reduction):
     M, C = mc
