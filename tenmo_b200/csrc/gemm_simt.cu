@@ -133,7 +133,11 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
     constexpr int TX = BN / TN;
     const int tx = tid % TX, ty = tid / TX;
 
-    float acc[TM][TN];
+    // accumulators as pairs of neighbouring columns: the k loop multiplies with the packed fma.rn.f32x2 (two
+    // independent round-to-nearest fused multiply-adds, the same bits as two fmaf, half the instructions).  The
+    // 128 x 128 tile holds its next tile in registers as well and spills in the packed form, so it keeps fmaf.
+    constexpr bool PACKED = BM < 128;
+    float2 acc[TM][TN / 2];
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
         // a per-row bias is the accumulator's starting value, as in the reference's convolution (cnn.mojo:435)
@@ -143,7 +147,7 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
             if (m < p.M) init = __ldg(p.bias_m + m);
         }
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = init;
+        for (int j = 0; j < TN / 2; ++j) acc[i][j] = make_float2(init, init);
     }
 
     LoaderA la;
@@ -190,7 +194,9 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
 #pragma unroll
             for (int i = 0; i < TM; ++i)
 #pragma unroll
-                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < TN / 2; ++j)
+                    acc[i][j] = PACKED ? __ffma2_rn(make_float2(a[i], a[i]), make_float2(b[2 * j], b[2 * j + 1]), acc[i][j])
+                                       : make_float2(fmaf(a[i], b[2 * j], acc[i][j].x), fmaf(a[i], b[2 * j + 1], acc[i][j].y));
         }
         if (has_next) {
             la.store(As[cur ^ 1], tid);
@@ -212,7 +218,7 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
             float v[CW], mk[CW];
 #pragma unroll
             for (int q = 0; q < CW; ++q) {
-                float x = acc[i][jg * CW + q];
+                float x = ((jg * CW + q) & 1) ? acc[i][(jg * CW + q) >> 1].y : acc[i][(jg * CW + q) >> 1].x;
                 if (p.bias && n + q < p.N) x += __ldg(p.bias + n + q);
                 mk[q] = x > 0.f ? 1.f : 0.f;
                 v[q] = apply_act(x, p.act);

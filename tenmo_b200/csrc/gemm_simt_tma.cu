@@ -64,9 +64,16 @@ __device__ __forceinline__ float4 lds128(const uint8_t* p) { return *reinterpret
 // row / column of register index i in the quadrant split (two runs of four, 64 apart)
 __device__ __forceinline__ int quad_index(int t, int i) { return (i >> 2) * 64 + t * 4 + (i & 3); }
 
-// A_K / B_K: the operand's unit-stride axis is k.  J_OUTER only reorders the independent fmaf of one k step
-// (columns outer, rows inner) where both loop orders are legal.
-template <bool A_K, bool B_K, bool J_OUTER>
+// Two independent fused multiply-adds: one packed fma.rn.f32x2 (both halves rounded to
+// nearest exactly like fmaf, so the bits do not change) or, for comparison, two scalar fmaf.
+template <bool PACKED>
+__device__ __forceinline__ float2 fma_pair(float a0, float a1, float b0, float b1, float2 c) {
+    if (PACKED) return __ffma2_rn(make_float2(a0, a1), make_float2(b0, b1), c);
+    return make_float2(fmaf(a0, b0, c.x), fmaf(a1, b1, c.y));
+}
+
+// A_K / B_K: the operand's unit-stride axis is k.  PACKED: the k loop multiplies with fma.rn.f32x2.
+template <bool A_K, bool B_K, bool PACKED>
 __global__ void __launch_bounds__(ST_THREADS, 2)
 gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const StParams p) {
     extern __shared__ uint8_t st_smem_raw[];
@@ -120,17 +127,25 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         for (; issued < pre; ++issued) issue(issued);
     }
 
-    float acc[8][8];
+    // 32 accumulator pairs.  With B read as [k][n] (its pairs of neighbouring columns are neighbouring registers)
+    // a pair holds (row i, columns 2jj and 2jj+1) at index i*4 + jj; with B read along k the pairs run down the
+    // rows instead, (rows 2ii and 2ii+1, column j) at index ii*8 + j, and the row values of A form the pair.
+    constexpr bool PAIR_ROWS = B_K;
+    float2 acc[32];
+    {
+        float init[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        // a per-row bias is the accumulator's starting value, as in the reference's convolution (cnn.mojo:435)
-        float init = 0.f;
-        if (p.bias_m) {
-            const int64_t m = (int64_t)m0 + quad_index(ty, i);
-            if (m < p.M) init = __ldg(p.bias_m + m);
+        for (int i = 0; i < 8; ++i) {
+            // a per-row bias is the accumulator's starting value, as in the reference's convolution (cnn.mojo:435)
+            init[i] = 0.f;
+            if (p.bias_m) {
+                const int64_t m = (int64_t)m0 + quad_index(ty, i);
+                if (m < p.M) init[i] = __ldg(p.bias_m + m);
+            }
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = init;
+        for (int q = 0; q < 32; ++q)
+            acc[q] = PAIR_ROWS ? make_float2(init[2 * (q >> 3)], init[2 * (q >> 3) + 1]) : make_float2(init[q >> 2], init[q >> 2]);
     }
 
     // per-thread constants of the fragment addresses
@@ -146,8 +161,8 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const uint8_t* As = smem_gen + s * ST_STAGE;
         const uint8_t* Bs = As + ST_TILE;
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
-            if (k4 == 1 && tid == 0 && kt >= 1 && issued < k_tiles) {
+        for (int k2 = 0; k2 < ST_BK / 2; ++k2) {  // two k steps at a time: K-major fragments are read as float2 along k
+            if (k2 == 2 && tid == 0 && kt >= 1 && issued < k_tiles) {
                 // refill the stage k-tile kt-1 used, once all eight warps have released it
                 const int prev = kt - 1;
                 if (mbar_wait(empty_bar(prev % ST_STAGES), (uint32_t)((prev / ST_STAGES) & 1), abort_flag)) {
@@ -155,82 +170,61 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     ++issued;
                 }
             }
-            if (A_K) {
-                float af[8][4];  // af[i][kk] = A[row i][4*k4 + kk]
-                const int x0 = (k4 ^ sa0) << 4, x1 = (k4 ^ sa1) << 4;
+            // byte offset of k = 2*k2 inside a 64-byte K-major row: swizzled 16-byte chunk, then the half of the chunk
+            const int xa0 = (((k2 >> 1) ^ sa0) << 4) + (k2 & 1) * 8, xa1 = (((k2 >> 1) ^ sa1) << 4) + (k2 & 1) * 8;
+            const int xb = (((k2 >> 1) ^ sb) << 4) + (k2 & 1) * 8;
+            if (!B_K) {
+                float af[8][2];  // A_K only: af[i][kk] = A[row i][2*k2 + kk]
+                if (A_K) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int off = (i >> 2) * 4096 + (i & 3) * 64 + (((i & 3) >> 1) ? x1 : x0);
-                    *reinterpret_cast<float4*>(&af[i][0]) = lds128(As + a_base + off);
+                    for (int i = 0; i < 8; ++i) {
+                        const int off = (i >> 2) * 4096 + (i & 3) * 64 + (((i & 3) >> 1) ? xa1 : xa0);
+                        *reinterpret_cast<float2*>(&af[i][0]) = *reinterpret_cast<const float2*>(As + a_base + off);
+                    }
                 }
-                if (!B_K) {
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        float b[8];
-                        *reinterpret_cast<float4*>(&b[0]) = lds128(Bs + (k4 * 4 + kk) * 512 + b_base);
-                        *reinterpret_cast<float4*>(&b[4]) = lds128(Bs + (k4 * 4 + kk) * 512 + b_base + 256);
-                        if (J_OUTER) {
+                for (int kk = 0; kk < 2; ++kk) {
+                    float a[8], b[8];
+                    if (A_K) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) acc[i][j] = fmaf(af[i][kk], b[j], acc[i][j]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(af[i][kk], b[j], acc[i][j]);
-                        }
+                        for (int i = 0; i < 8; ++i) a[i] = af[i][kk];
+                    } else {
+                        *reinterpret_cast<float4*>(&a[0]) = lds128(As + (k2 * 2 + kk) * 512 + a_base);
+                        *reinterpret_cast<float4*>(&a[4]) = lds128(As + (k2 * 2 + kk) * 512 + a_base + 256);
                     }
-                } else {
-                    const int xb = (k4 ^ sb) << 4;
+                    *reinterpret_cast<float4*>(&b[0]) = lds128(Bs + (k2 * 2 + kk) * 512 + b_base);
+                    *reinterpret_cast<float4*>(&b[4]) = lds128(Bs + (k2 * 2 + kk) * 512 + b_base + 256);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float bf[4];  // bf[kk] = B[4*k4 + kk][column tx + 16 j]
-                        *reinterpret_cast<float4*>(&bf[0]) = lds128(Bs + b_base + j * 1024 + xb);
+                    for (int i = 0; i < 8; ++i)
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) acc[i][j] = fmaf(af[i][kk], bf[kk], acc[i][j]);
-                    }
+                        for (int jj = 0; jj < 4; ++jj)
+                            acc[i * 4 + jj] = fma_pair<PACKED>(a[i], a[i], b[2 * jj], b[2 * jj + 1], acc[i * 4 + jj]);
                 }
             } else {
-                if (!B_K) {
+                float bf[8][2];  // bf[j][kk] = B[2*k2 + kk][column tx + 16 j]
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        float a[8], b[8];
-                        *reinterpret_cast<float4*>(&a[0]) = lds128(As + (k4 * 4 + kk) * 512 + a_base);
-                        *reinterpret_cast<float4*>(&a[4]) = lds128(As + (k4 * 4 + kk) * 512 + a_base + 256);
-                        *reinterpret_cast<float4*>(&b[0]) = lds128(Bs + (k4 * 4 + kk) * 512 + b_base);
-                        *reinterpret_cast<float4*>(&b[4]) = lds128(Bs + (k4 * 4 + kk) * 512 + b_base + 256);
-                        if (J_OUTER) {
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<float2*>(&bf[j][0]) = *reinterpret_cast<const float2*>(Bs + b_base + j * 1024 + xb);
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
+                for (int kk = 0; kk < 2; ++kk) {
+                    float a[8];
+                    if (A_K) {
+                        // scalar reads: neighbouring rows of a K-major tile are 64 B apart, and the pair (row 2ii, row 2ii+1)
+                        // has to sit in neighbouring registers
 #pragma unroll
-                                for (int i = 0; i < 8; ++i) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                        for (int i = 0; i < 8; ++i) {
+                            const int off = (i >> 2) * 4096 + (i & 3) * 64 + (((i & 3) >> 1) ? xa1 : xa0);
+                            a[i] = *reinterpret_cast<const float*>(As + a_base + off + kk * 4);
                         }
+                    } else {
+                        *reinterpret_cast<float4*>(&a[0]) = lds128(As + (k2 * 2 + kk) * 512 + a_base);
+                        *reinterpret_cast<float4*>(&a[4]) = lds128(As + (k2 * 2 + kk) * 512 + a_base + 256);
                     }
-                } else {
-                    float am[4][8];  // am[kk][i] = A[row i][4*k4 + kk]
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        *reinterpret_cast<float4*>(&am[kk][0]) = lds128(As + (k4 * 4 + kk) * 512 + a_base);
-                        *reinterpret_cast<float4*>(&am[kk][4]) = lds128(As + (k4 * 4 + kk) * 512 + a_base + 256);
-                    }
-                    const int xb = (k4 ^ sb) << 4;
+                    for (int ii = 0; ii < 4; ++ii)
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float bf[4];
-                        *reinterpret_cast<float4*>(&bf[0]) = lds128(Bs + b_base + j * 1024 + xb);
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) acc[i][j] = fmaf(am[kk][i], bf[kk], acc[i][j]);
-                    }
+                        for (int j = 0; j < 8; ++j)
+                            acc[ii * 8 + j] = fma_pair<PACKED>(a[2 * ii], a[2 * ii + 1], bf[j][kk], bf[j][kk], acc[ii * 8 + j]);
                 }
             }
         }
@@ -258,6 +252,10 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const float* MASK = p.mul_mask ? p.mul_mask + batch * p.M * p.N : nullptr;
     float* CLO = p.c_lo ? p.c_lo + batch * p.M * p.ld_clo : nullptr;
     const bool extended = MASK != nullptr || CLO != nullptr;
+    auto acc_at = [&](int i, int j) {  // indices are compile-time constants after unrolling
+        if (PAIR_ROWS) return (i & 1) ? acc[(i >> 1) * 8 + j].y : acc[(i >> 1) * 8 + j].x;
+        return (j & 1) ? acc[i * 4 + (j >> 1)].y : acc[i * 4 + (j >> 1)].x;
+    };
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int64_t m = (int64_t)m0 + quad_index(ty, i);
@@ -270,7 +268,7 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 float v[4], mk[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    float x = acc[i][jg * 4 + q];
+                    float x = acc_at(i, jg * 4 + q);
                     if (p.bias) x += __ldg(p.bias + n + q);
                     mk[q] = x > 0.f ? 1.f : 0.f;
                     v[q] = st_act(x, p.act);
@@ -289,7 +287,7 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             for (int j = 0; j < 8; ++j) {
                 const int64_t n = (int64_t)n0 + (B_K ? tx + 16 * j : quad_index(tx, j));
                 if (n >= p.N) continue;
-                float x = acc[i][j];
+                float x = acc_at(i, j);
                 if (p.bias) x += __ldg(p.bias + n);
                 const float mk = x > 0.f ? 1.f : 0.f;
                 float o = st_act(x, p.act);
@@ -322,15 +320,15 @@ int st_encode_map(tenmo_ctx* ctx, CUtensorMap* map, const float* base, const Ten
     return TENMO_OK;
 }
 
-template <bool J_OUTER>
+template <bool PACKED>
 cudaError_t st_launch(bool a_k, bool b_k, unsigned grid, cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb,
                       const StParams& sp) {
 #define ST_LAUNCH(AK, BKM)                                                                                             \
     {                                                                                                                  \
-        cudaError_t e = cudaFuncSetAttribute(gemm_simt_tma_kernel<AK, BKM, J_OUTER>,                                   \
+        cudaError_t e = cudaFuncSetAttribute(gemm_simt_tma_kernel<AK, BKM, PACKED>,                                   \
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM);                    \
         if (e != cudaSuccess) return e;                                                                                \
-        gemm_simt_tma_kernel<AK, BKM, J_OUTER><<<grid, ST_THREADS, ST_SMEM, s>>>(ma, mb, sp);                          \
+        gemm_simt_tma_kernel<AK, BKM, PACKED><<<grid, ST_THREADS, ST_SMEM, s>>>(ma, mb, sp);                          \
     }
     if (a_k) { if (b_k) ST_LAUNCH(true, true) else ST_LAUNCH(true, false) }
     else { if (b_k) ST_LAUNCH(false, true) else ST_LAUNCH(false, false) }
@@ -372,10 +370,15 @@ int tenmo_gemm_simt_tma_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     const int64_t grid = (int64_t)sp.tiles_m * sp.tiles_n * p.total_batch;
     if (grid <= 0 || grid > 0x7fffffffLL)
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_simt_tma: grid of %lld tiles is out of range", (long long)grid);
-    const char* env = getenv("TENMO_SIMT_ORDER");
-    const bool j_outer = env && atoi(env) == 1;
+    // Packed fma.rn.f32x2 halves the instructions the FP32 pipe has to be fed with and is what lifts the kernel
+    // from ~0.66 to 0.75-0.83 of the pipe's peak.  It needs one operand as a pair of neighbouring registers, which a
+    // K-major tile cannot deliver (neighbouring rows lie 64 B apart): with both operands K-major the pairs cost
+    // register moves and the scalar form is faster, so that layout keeps fmaf.  TENMO_SIMT_FFMA2=0/1 forces a form.
+    bool packed = a.mn_major || b.mn_major;
+    const char* env = getenv("TENMO_SIMT_FFMA2");
+    if (env && (env[0] == '0' || env[0] == '1')) packed = env[0] == '1';
     tenmo_prof_before(ctx);
-    cudaError_t e = j_outer ? st_launch<true>(!a.mn_major, !b.mn_major, (unsigned)grid, ctx->stream, ma, mb, sp)
+    cudaError_t e = packed ? st_launch<true>(!a.mn_major, !b.mn_major, (unsigned)grid, ctx->stream, ma, mb, sp)
                             : st_launch<false>(!a.mn_major, !b.mn_major, (unsigned)grid, ctx->stream, ma, mb, sp);
     tenmo_prof_after(ctx);
     ctx->launches++;
