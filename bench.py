@@ -196,20 +196,37 @@ def measure_mlps(h, rank, world, local_rank, timed, args):
     from tenmo_b200.trainer import MLPTrainer
 
     out = {}
+    legs = set(args.legs.split(","))
     rng = np.random.default_rng(4321)  # same stream on every rank: identical replicas
+    gen = torch.Generator(device="cpu").manual_seed(777)
 
     def uniform_init(dims, limit_fn):
         return ([rng.uniform(-1, 1, (dims[i], dims[i + 1])).astype(np.float32) * np.float32(limit_fn(dims[i], dims[i + 1]))
                  for i in range(len(dims) - 1)], [np.zeros(d, np.float32) for d in dims[1:]])
 
-    # ---- wide MLP, data parallel ----
+    if "wide_mlp" in legs:
+        out["wide_mlp"] = measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen)
+    if "cnn" in legs:
+        out["cnn"] = measure_cnn(h, rank, world, local_rank, timed, args, rng, gen)
+    if "mnist_mlp" in legs and world == 1:
+        out["mnist_mlp"] = measure_mnist_mlp(h, local_rank, timed, uniform_init, gen)
+    return out
+
+
+def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen):
+    import numpy as np
+    import torch
+
+    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_broadcast_bytes
+    from tenmo_b200.trainer import MLPTrainer
+
+    torch.cuda.nvtx.range_push("wide_mlp")
     dims, gb = [4096, 4096, 4096, 4096, 1000], 8192
     Ws, bs = uniform_init(dims, lambda i, o: np.sqrt(6.0 / i))  # "Kaiming-uniform": U(+-sqrt(6/in))
     lo, hi = shard_rows(gb, rank, world)
     uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(torch.device("cuda", local_rank)))
     tr = MLPTrainer(Ws, bs, batch=hi - lo, lr=0.01, momentum=0.9, algo="3xtf32", handle=h, rank=rank, world=world,
                     unique_id=uid, device=local_rank)
-    gen = torch.Generator(device="cpu").manual_seed(777)
     Xg = torch.randn(gb, dims[0], generator=gen)
     yg = torch.randint(0, dims[-1], (gb,), generator=gen)
     Xh, yh = Xg[lo:hi].contiguous().pin_memory(), yg[lo:hi].contiguous().pin_memory()
@@ -226,7 +243,7 @@ def measure_mlps(h, rank, world, local_rank, timed, args):
     e2e_step()
     ms_e2e = timed(e2e_step, args.mlp_steps)
     flops = sum(2.0 * gb * dims[l] * dims[l + 1] * (3 if l > 0 else 2) for l in range(4))
-    out["wide_mlp"] = {
+    res = {
         "metric": "mlp_train_samples_per_s", "value": gb * args.mlp_steps / (ms * 1e-3), "unit": "samples/s",
         "ms_per_step": ms / args.mlp_steps, "tflops": flops * args.mlp_steps / (ms * 1e-3) / 1e12, "scaling": "strong",
         "global_batch": gb, "per_rank_batch": hi - lo, "allreduce_bytes_per_step": 0 if world == 1 else tr.numel * 4,
@@ -237,10 +254,19 @@ def measure_mlps(h, rank, world, local_rank, timed, args):
         h.dp_finalize()
     del tr
     torch.cuda.empty_cache()
+    torch.cuda.nvtx.range_pop()
+    return res
 
-    # ---- CIFAR-shaped CNN, data parallel (global batch 256) ----
+
+def measure_cnn(h, rank, world, local_rank, timed, args, rng, gen):
+    """CIFAR-shaped CNN, data parallel (global batch 256 split by images over the ranks)."""
+    import numpy as np
+    import torch
+
     from tenmo_b200.cnn import CNNTrainer
+    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_broadcast_bytes
 
+    torch.cuda.nvtx.range_push("cnn")
     gbc = 256
     lo, hi = shard_rows(gbc, rank, world)
     he = lambda shape, fan_in: (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
@@ -255,7 +281,7 @@ def measure_mlps(h, rank, world, local_rank, timed, args):
     for _ in range(3):
         cnn.step()
     ms = timed(cnn.step, args.mlp_steps)
-    out["cnn"] = {
+    res = {
         "metric": "cnn_train_samples_per_s", "value": gbc * args.mlp_steps / (ms * 1e-3), "unit": "samples/s",
         "ms_per_step": ms / args.mlp_steps, "scaling": "strong", "global_batch": gbc, "per_rank_batch": hi - lo,
         "steps": args.mlp_steps,
@@ -266,35 +292,45 @@ def measure_mlps(h, rank, world, local_rank, timed, args):
         h.dp_finalize()
     del cnn
     torch.cuda.empty_cache()
+    torch.cuda.nvtx.range_pop()
+    return res
 
-    # ---- MNIST-shaped MLP, one GPU ----
-    if world == 1:
-        dims = [784, 128, 32, 10]
-        Ws, bs = uniform_init(dims, lambda i, o: np.sqrt(6.0 / (i + o)))  # Xavier-uniform (net.mojo:87-116)
-        tr = MLPTrainer(Ws, bs, batch=64, lr=0.01, momentum=0.9, algo="simt", handle=h, device=local_rank)
-        pool = torch.rand(938 * 64, 784, generator=gen).cuda()   # one epoch of synthetic pixels in [0,1)
-        labels = torch.randint(0, 10, (938 * 64,), generator=gen).cuda()
-        tr.load_batch(pool[:64], labels[:64])
-        tr.capture()
-        k = [0]
 
-        def epoch_step():
-            i = k[0] % 938
-            tr.load_batch(pool[i * 64:(i + 1) * 64], labels[i * 64:(i + 1) * 64])
-            tr.replay()
-            k[0] += 1
+def measure_mnist_mlp(h, local_rank, timed, uniform_init, gen):
+    """MNIST-shaped MLP on one GPU, the step replayed as a CUDA graph."""
+    import numpy as np
+    import torch
 
-        for _ in range(20):
-            epoch_step()
-        ms = timed(epoch_step, 938)
-        out["mnist_mlp"] = {
-            "metric": "mlp_train_samples_per_s", "value": 938 * 64 / (ms * 1e-3), "unit": "samples/s",
-            "us_per_step": ms / 938 * 1e3, "steps": 938, "batch": 64, "final_loss": tr.loss_value(),
-            "config": "784-128-32-10 Linear+ReLU, softmax-CE, SGD lr 0.01 momentum 0.9, strict-fp32 GEMMs, one epoch "
-                      "(938 steps) of synthetic U[0,1) pixels, step replayed as a CUDA graph; latency-bound",
-        }
-        h.set_stream(torch.cuda.current_stream(local_rank).cuda_stream)
-    return out
+    from tenmo_b200.trainer import MLPTrainer
+
+    torch.cuda.nvtx.range_push("mnist_mlp")
+    dims = [784, 128, 32, 10]
+    Ws, bs = uniform_init(dims, lambda i, o: np.sqrt(6.0 / (i + o)))  # Xavier-uniform (net.mojo:87-116)
+    tr = MLPTrainer(Ws, bs, batch=64, lr=0.01, momentum=0.9, algo="simt", handle=h, device=local_rank)
+    pool = torch.rand(938 * 64, 784, generator=gen).cuda()   # one epoch of synthetic pixels in [0,1)
+    labels = torch.randint(0, 10, (938 * 64,), generator=gen).cuda()
+    tr.load_batch(pool[:64], labels[:64])
+    tr.capture()
+    k = [0]
+
+    def epoch_step():
+        i = k[0] % 938
+        tr.load_batch(pool[i * 64:(i + 1) * 64], labels[i * 64:(i + 1) * 64])
+        tr.replay()
+        k[0] += 1
+
+    for _ in range(20):
+        epoch_step()
+    ms = timed(epoch_step, 938)
+    res = {
+        "metric": "mlp_train_samples_per_s", "value": 938 * 64 / (ms * 1e-3), "unit": "samples/s",
+        "us_per_step": ms / 938 * 1e3, "steps": 938, "batch": 64, "final_loss": tr.loss_value(),
+        "config": "784-128-32-10 Linear+ReLU, softmax-CE, SGD lr 0.01 momentum 0.9, strict-fp32 GEMMs, one epoch "
+                  "(938 steps) of synthetic U[0,1) pixels, step replayed as a CUDA graph; latency-bound",
+    }
+    h.set_stream(torch.cuda.current_stream(local_rank).cuda_stream)
+    torch.cuda.nvtx.range_pop()
+    return res
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -524,6 +560,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-mlp", action="store_true", help="skip the MLP training legs")
     ap.add_argument("--mlp-steps", type=int, default=20)
+    ap.add_argument("--legs", default="wide_mlp,cnn,mnist_mlp", help="which training legs to run after the GEMM arm")
     ap.add_argument("--kernels", action="store_true",
                     help="time the bandwidth-bound kernels of the path against the HBM roofline (one JSON line each)")
     args = ap.parse_args()

@@ -46,7 +46,7 @@ class Conv2d:
                  self.patches.data_ptr())
         mW = make_mat(weight.data_ptr(), (self.Cout, K), (K, 1))                 # broadcast over the batch
         mPt = make_mat(self.patches.data_ptr(), (N, K, S), (S * K, 1, K))         # patches[n]^T as a stride view
-        h.gemm_ex(self.Cout, S, K, mW, mPt, self.out.data_ptr(), bias_m=bias.data_ptr(),
+        h.gemm_ex(self.Cout, S, K, mW, mPt, self.out.data_ptr(), algo=_lib.ALGO_SIMT_FP32, bias_m=bias.data_ptr(),
                   act=_lib.ACT_RELU if self.relu else _lib.ACT_NONE, aux=self.mask.data_ptr() if self.relu else 0)
         return self.out
 
@@ -58,12 +58,12 @@ class Conv2d:
         h.channel_sum(g.data_ptr(), N, Cout, S, db.data_ptr())
         mG = make_mat(g.data_ptr(), (N, Cout, S), (Cout * S, S, 1))
         mP = make_mat(self.patches.data_ptr(), (N, S, K), (S * K, K, 1))
-        h.gemm_ex(Cout, K, S, mG, mP, self.dW_full.data_ptr())
+        h.gemm_ex(Cout, K, S, mG, mP, self.dW_full.data_ptr(), algo=_lib.ALGO_SIMT_FP32)
         h.colsum(self.dW_full.data_ptr(), N, Cout * K, Cout * K, dW.data_ptr())   # sum over the batch
         if self.need_dx:
             mGt = make_mat(g.data_ptr(), (N, S, Cout), (Cout * S, 1, S))
             mW = make_mat(weight.data_ptr(), (Cout, K), (K, 1))
-            h.gemm_ex(S, K, Cout, mGt, mW, self.dpatches.data_ptr())
+            h.gemm_ex(S, K, Cout, mGt, mW, self.dpatches.data_ptr(), algo=_lib.ALGO_SIMT_FP32)
             h.col2im(self.dpatches.data_ptr(), N, self.Cin, self.H, self.W, self.k, self.k, self.stride, self.dil, self.pad,
                      self.dx.data_ptr())
         return self.dx
@@ -155,15 +155,16 @@ class CNNTrainer:
         a2 = self.pool2.forward(self.conv2.forward(a1, p["conv2.weight"], p["conv2.bias"]))
         flat = make_mat(a2.data_ptr(), (B, self.feat), (self.feat, 1))            # Flatten: NCHW order, a view
         mWfc = make_mat(p["fc.weight"].data_ptr(), (self.feat, C), (C, 1))
-        h.gemm_ex(B, C, self.feat, flat, mWfc, self.logits.data_ptr(), bias=p["fc.bias"].data_ptr())
+        h.gemm_ex(B, C, self.feat, flat, mWfc, self.logits.data_ptr(), algo=_lib.ALGO_SIMT_FP32, bias=p["fc.bias"].data_ptr())
         h.ce_fwd(self.logits.data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
                  self.loss.data_ptr(), self.valid.data_ptr())
         h.ce_bwd(self.softmax.data_ptr(), self.y.data_ptr(), True, B, C, -100, 0.0, 0, 0, self.valid.data_ptr(),
                  self.dlogits.data_ptr())
         mdl = make_mat(self.dlogits.data_ptr(), (B, C), (C, 1))
         h.gemm_ex(self.feat, C, B, make_mat(a2.data_ptr(), (self.feat, B), (1, self.feat)), mdl, g["fc.weight"].data_ptr(),
-                  colsum=g["fc.bias"].data_ptr())
-        h.gemm_ex(B, self.feat, C, mdl, make_mat(p["fc.weight"].data_ptr(), (C, self.feat), (1, C)), self.dfeat.data_ptr())
+                  algo=_lib.ALGO_SIMT_FP32, colsum=g["fc.bias"].data_ptr())
+        h.gemm_ex(B, self.feat, C, mdl, make_mat(p["fc.weight"].data_ptr(), (C, self.feat), (1, C)), self.dfeat.data_ptr(),
+                  algo=_lib.ALGO_SIMT_FP32)
         d2 = self.pool2.backward(self.dfeat)                                       # (B, C2, 16, 16)
         d1p = self.conv2.backward(d2, p["conv2.weight"], g["conv2.weight"], g["conv2.bias"])
         d1 = self.pool1.backward(d1p)

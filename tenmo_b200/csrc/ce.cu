@@ -73,13 +73,21 @@ __device__ __forceinline__ float row_loss_from_stats(const CeFwdArgs& p, int64_t
 // sequential `scalar_loss += loss`), fixed-shape tree otherwise.
 __device__ void ce_finalize(const CeFwdArgs& p, float* red_smem) {
     const int tid = threadIdx.x;
-    if (p.M <= CE_SEQ_ROWS) {  // a serial walk costs ~100 ns per row: fine for a small batch, not beyond
+    if (p.M <= CE_SEQ_ROWS) {
+        // the reference's row-ascending sequential sum: all threads fetch (one row each), thread 0 adds in row order
+        __shared__ float row_vals[CE_SEQ_ROWS];
+        __shared__ int row_counted[CE_SEQ_ROWS];
+        for (int r = tid; r < (int)p.M; r += CE_THREADS) {
+            row_vals[r] = p.reduction != 2 ? __ldcg(p.row_loss + r) : 0.f;
+            row_counted[r] = load_label(p.labels, p.label_is_i64, r) != p.ignore_index ? 1 : 0;
+        }
+        __syncthreads();
         if (tid == 0) {
             float s = 0.f;
             int cnt = 0;
-            for (int64_t r = 0; r < p.M; ++r) {
-                if (p.reduction != 2) s += __ldcg(p.row_loss + r);
-                cnt += load_label(p.labels, p.label_is_i64, r) != p.ignore_index ? 1 : 0;
+            for (int r = 0; r < (int)p.M; ++r) {
+                s += row_vals[r];
+                cnt += row_counted[r];
             }
             if (p.reduction == 0 && cnt > 0) s = s / (float)cnt;
             if (p.reduction != 2) p.loss[0] = s;

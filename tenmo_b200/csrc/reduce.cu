@@ -20,8 +20,18 @@ __global__ void __launch_bounds__(CS_THREADS) colsum_seq_kernel(const float* __r
                                                                int64_t ldx, float* __restrict__ out, float beta) {
     const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (n >= N) return;
+    // rows are added in ascending order (the reference's sequential sum); sixteen loads are issued before the
+    // first add so that the walk is not one memory latency per row
     float acc = 0.f;
-    for (int64_t m = 0; m < M; ++m) acc += __ldg(x + m * ldx + n);
+    int64_t m = 0;
+    for (; m + 16 <= M; m += 16) {
+        float v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) v[u] = __ldg(x + (m + u) * ldx + n);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) acc += v[u];
+    }
+    for (; m < M; ++m) acc += __ldg(x + m * ldx + n);
     out[n] = beta != 0.f ? out[n] + acc : acc;
 }
 
