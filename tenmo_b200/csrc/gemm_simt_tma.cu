@@ -1,21 +1,28 @@
 // Strict-FP32 SIMT GEMM with TMA-staged shared-memory tiles.
 //
 // Same arithmetic contract as gemm_simt.cu: every output element is one k-ascending fmaf chain, so the two
-// kernels give identical bits.  What differs is how the 128 x 128 x 16 tiles reach shared memory: one
-// elected thread issues two tiled bulk copies (cp.async.bulk.tensor, no multicast) per k-tile into a ring
-// of four 16 KB stages guarded by full / empty mbarriers, so the 256 threads spend their issue slots on
-// fmaf and on the 16-byte fragment reads only: no global loads, no address arithmetic, no transposing
-// stores and no block-wide barrier in the k loop.  The FP32 pipe issues one warp instruction per cycle per
-// scheduler, which is also the issue limit, so every instruction that is not an fmaf costs throughput.
-//
+// kernels give identical bits.  What differs is how the 128 x 128 x 16 tiles reach shared memory and how the
+// multiplies are issued.
+//   * Staging: one elected thread issues two tiled bulk copies (cp.async.bulk.tensor, no multicast) per k-tile
+//     into a ring of four 16 KB stages guarded by full / empty mbarriers, so the k loop holds no global load,
+//     no address arithmetic, no staging store and no block-wide barrier.
+//   * Multiply: the packed fma.rn.f32x2 (two independent round-to-nearest FMAs per lane and instruction, the
+//     same bits as two fmaf).  The FP32 pipe takes one warp-level FFMA per cycle per scheduler, which is also
+//     the issue limit, so with scalar fmaf every fragment read displaces an FFMA and three-operand delivery
+//     shows up as dispatch stalls (0.61-0.66 of peak); the packed form needs half the instructions and runs
+//     into the pipe itself (0.74-0.83).  It wants one operand as a pair of neighbouring registers.
 // Shared-memory layouts (what the copy engine writes) and the fragment reads that go with them:
 //   unit stride along m / n ("MN-major", e.g. row-major B or a transposed view of A): box {128, 16} ->
-//       [k][128] rows of 512 B; per k a thread reads its 8 values as two float4 (columns tx*4.. and 64+tx*4..).
+//       [k][128] rows of 512 B; per k a thread reads its 8 values as two float4 (columns tx*4.. and 64+tx*4..);
+//       neighbouring columns are neighbouring registers, so B supplies the pairs and a value of A is used twice.
 //   unit stride along k ("K-major", e.g. row-major A): box {16, 128} -> [row][16] rows of 64 B, written with
-//       the 64-byte swizzle (16-byte chunk index ^= (row >> 1) & 3).  TMA cannot transpose 32-bit elements,
-//       so fragments are read as float4 ALONG k (four k steps of one row at once) and the 4 x 8 x 8 fmaf
-//       block is ordered so that each accumulator still sees k ascending.  For operand B the thread's
-//       columns are interleaved (n = tx + 16 j): 16 consecutive rows hit all banks through the swizzle.
+//       the 64-byte swizzle (16-byte chunk index ^= (row >> 1) & 3).  The copy engine cannot transpose 32-bit
+//       elements.  Operand A: each warp only multiplies with 16 rows of the tile, and transposes those for
+//       itself into a private [k][16] block (two 16-byte reads, eight 4-byte writes per lane and k-tile, a
+//       __syncwarp), after which its fragments read like the MN-major ones.  Operand B (all 128 rows are needed
+//       by every warp): fragments are read as float2 ALONG k from the swizzled tile, a thread's columns are
+//       interleaved (n = tx + 16 j: 16 consecutive rows spread over the banks), the pairs run down the rows of A
+//       and a value of B is used twice.
 // Fragments are shared inside a warp by same-address shared-memory reads (a broadcast costs no extra
 // wavefront); a shuffle-based exchange would put one more instruction per value into the issue stream.
 // Every mbarrier wait is bounded (2 s); on expiry the kernel raises the context status word, waits for the
@@ -33,7 +40,10 @@ constexpr int ST_STAGES = 4;
 constexpr int ST_THREADS = 256;
 constexpr int ST_TILE = 128 * ST_BK * 4;  // bytes of one operand tile
 constexpr int ST_STAGE = 2 * ST_TILE;
-constexpr int ST_SMEM = ST_STAGES * ST_STAGE + 1024 /*alignment slack*/ + 128 /*barriers, abort flag*/;
+constexpr int ST_LDT = 20;                          // floats per k row of a warp's transposed A fragment block
+constexpr int ST_TBUF = ST_BK * ST_LDT * 4;         // bytes of that block (one per warp)
+constexpr int ST_SMEM = ST_STAGES * ST_STAGE + 1024 /*alignment slack*/ + 128 /*barriers, abort flag*/ +
+                        (ST_THREADS / 32) * ST_TBUF;
 constexpr int ST_GROUP_M = 16;  // tile order: groups of 16 row tiles walked column by column (L2 reuse)
 
 struct StParams {
@@ -149,10 +159,17 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     }
 
     // per-thread constants of the fragment addresses
-    const int a_base = A_K ? ty * 256 : ty * 16;   // K-major: row ty*4 at 64 B per row; MN-major: column ty*4
+    const int warp = tid >> 5, ty_l = ty & 1;
     const int b_base = B_K ? tx * 64 : tx * 16;    // K-major: row tx (rows tx + 16 j); MN-major: column tx*4
-    const int sa0 = (2 * ty) & 3, sa1 = (2 * ty + 1) & 3;  // swizzle term (row >> 1) & 3 of rows ty*4 + {0,1} / {2,3}
-    const int sb = (tx >> 1) & 3;                            // of rows tx + 16 j
+    const int sb = (tx >> 1) & 3;                   // swizzle term (row >> 1) & 3 of rows tx + 16 j
+    // A K-major tile is transposed by each warp for itself (see below): lane = (local row lr, 16-byte chunk c)
+    uint8_t* Tw = smem_gen + ST_STAGES * ST_STAGE + 128 + warp * ST_TBUF;
+    const int lr = lane >> 2, lc = lane & 3;
+    const int t_src = (8 * warp + lr) * 64 + ((lc ^ ((lr >> 1) & 3)) << 4);  // chunk lc of row 8w + lr (+ 64 rows: + 4096 B)
+    // k = 4*lc + e lands in row k of the block; column = 4 * (quad ^ swap) + (lr & 3), quad = 2*pass + (lr >> 2),
+    // swap = 2 for k >= 8
+    const int t_dst0 = ((4 * lc) * ST_LDT + (((lr >> 2) ^ ((lc >> 1) << 1)) << 2) + (lr & 3)) * 4;
+    const int t_dst1 = ((4 * lc) * ST_LDT + (((2 + (lr >> 2)) ^ ((lc >> 1) << 1)) << 2) + (lr & 3)) * 4;
 
     int kt = 0;
     for (; kt < k_tiles; ++kt) {
@@ -160,8 +177,30 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (!mbar_wait(full_bar(s), (uint32_t)((kt / ST_STAGES) & 1), abort_flag)) break;
         const uint8_t* As = smem_gen + s * ST_STAGE;
         const uint8_t* Bs = As + ST_TILE;
+        if (A_K) {
+            // The copy engine cannot transpose 32-bit elements, and a fragment along m must be neighbouring registers
+            // (float4 reads, register pairs for the packed FMA).  Each warp therefore transposes the 16 rows of A it
+            // multiplies with (rows 8w..8w+7 and 64+8w..64+8w+7) from [row][16 k] into its own [k][16 rows] block:
+            // two 16-byte reads and eight 4-byte writes per lane and k-tile, synchronised inside the warp only.  With
+            // 20 floats per k row and the two 8-row halves swapped for k >= 8 the 32 writes of a step hit 32 banks.
 #pragma unroll
-        for (int k2 = 0; k2 < ST_BK / 2; ++k2) {  // two k steps at a time: K-major fragments are read as float2 along k
+            for (int pass = 0; pass < 2; ++pass) {
+                const float4 v = lds128(As + pass * 4096 + t_src);
+                float* dst = reinterpret_cast<float*>(Tw + (pass ? t_dst1 : t_dst0));
+                dst[0 * ST_LDT] = v.x;
+                dst[1 * ST_LDT] = v.y;
+                dst[2 * ST_LDT] = v.z;
+                dst[3 * ST_LDT] = v.w;
+            }
+            __syncwarp();
+        }
+        // a fragment of k: rows ty*4..+3 and 64+ty*4..+3
+        const uint8_t* Af = A_K ? Tw + ty_l * 16 : As + ty * 16;
+        constexpr int A_ROW = A_K ? ST_LDT * 4 : 512;
+        auto a_lo = [&](int k) { return Af + k * A_ROW + (A_K && k >= 8 ? 32 : 0); };   // rows ty*4 .. ty*4+3
+        auto a_hi = [&](int k) { return Af + k * A_ROW + (A_K ? (k >= 8 ? 0 : 32) : 256); };  // rows 64+ty*4 ..
+#pragma unroll
+        for (int k2 = 0; k2 < ST_BK / 2; ++k2) {  // two k steps at a time: K-major B fragments are read as float2 along k
             if (k2 == 2 && tid == 0 && kt >= 1 && issued < k_tiles) {
                 // refill the stage k-tile kt-1 used, once all eight warps have released it
                 const int prev = kt - 1;
@@ -170,28 +209,12 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     ++issued;
                 }
             }
-            // byte offset of k = 2*k2 inside a 64-byte K-major row: swizzled 16-byte chunk, then the half of the chunk
-            const int xa0 = (((k2 >> 1) ^ sa0) << 4) + (k2 & 1) * 8, xa1 = (((k2 >> 1) ^ sa1) << 4) + (k2 & 1) * 8;
-            const int xb = (((k2 >> 1) ^ sb) << 4) + (k2 & 1) * 8;
             if (!B_K) {
-                float af[8][2];  // A_K only: af[i][kk] = A[row i][2*k2 + kk]
-                if (A_K) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int off = (i >> 2) * 4096 + (i & 3) * 64 + (((i & 3) >> 1) ? xa1 : xa0);
-                        *reinterpret_cast<float2*>(&af[i][0]) = *reinterpret_cast<const float2*>(As + a_base + off);
-                    }
-                }
 #pragma unroll
                 for (int kk = 0; kk < 2; ++kk) {
                     float a[8], b[8];
-                    if (A_K) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) a[i] = af[i][kk];
-                    } else {
-                        *reinterpret_cast<float4*>(&a[0]) = lds128(As + (k2 * 2 + kk) * 512 + a_base);
-                        *reinterpret_cast<float4*>(&a[4]) = lds128(As + (k2 * 2 + kk) * 512 + a_base + 256);
-                    }
+                    *reinterpret_cast<float4*>(&a[0]) = lds128(a_lo(k2 * 2 + kk));
+                    *reinterpret_cast<float4*>(&a[4]) = lds128(a_hi(k2 * 2 + kk));
                     *reinterpret_cast<float4*>(&b[0]) = lds128(Bs + (k2 * 2 + kk) * 512 + b_base);
                     *reinterpret_cast<float4*>(&b[4]) = lds128(Bs + (k2 * 2 + kk) * 512 + b_base + 256);
 #pragma unroll
@@ -201,6 +224,8 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                             acc[i * 4 + jj] = fma_pair<PACKED>(a[i], a[i], b[2 * jj], b[2 * jj + 1], acc[i * 4 + jj]);
                 }
             } else {
+                // byte offset of k = 2*k2 inside a 64-byte K-major row: swizzled 16-byte chunk, then the half of the chunk
+                const int xb = (((k2 >> 1) ^ sb) << 4) + (k2 & 1) * 8;
                 float bf[8][2];  // bf[j][kk] = B[2*k2 + kk][column tx + 16 j]
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
@@ -208,18 +233,8 @@ gemm_simt_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
                 for (int kk = 0; kk < 2; ++kk) {
                     float a[8];
-                    if (A_K) {
-                        // scalar reads: neighbouring rows of a K-major tile are 64 B apart, and the pair (row 2ii, row 2ii+1)
-                        // has to sit in neighbouring registers
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int off = (i >> 2) * 4096 + (i & 3) * 64 + (((i & 3) >> 1) ? xa1 : xa0);
-                            a[i] = *reinterpret_cast<const float*>(As + a_base + off + kk * 4);
-                        }
-                    } else {
-                        *reinterpret_cast<float4*>(&a[0]) = lds128(As + (k2 * 2 + kk) * 512 + a_base);
-                        *reinterpret_cast<float4*>(&a[4]) = lds128(As + (k2 * 2 + kk) * 512 + a_base + 256);
-                    }
+                    *reinterpret_cast<float4*>(&a[0]) = lds128(a_lo(k2 * 2 + kk));
+                    *reinterpret_cast<float4*>(&a[4]) = lds128(a_hi(k2 * 2 + kk));
 #pragma unroll
                     for (int ii = 0; ii < 4; ++ii)
 #pragma unroll
@@ -370,11 +385,8 @@ int tenmo_gemm_simt_tma_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     const int64_t grid = (int64_t)sp.tiles_m * sp.tiles_n * p.total_batch;
     if (grid <= 0 || grid > 0x7fffffffLL)
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_simt_tma: grid of %lld tiles is out of range", (long long)grid);
-    // Packed fma.rn.f32x2 halves the instructions the FP32 pipe has to be fed with and is what lifts the kernel
-    // from ~0.66 to 0.75-0.83 of the pipe's peak.  It needs one operand as a pair of neighbouring registers, which a
-    // K-major tile cannot deliver (neighbouring rows lie 64 B apart): with both operands K-major the pairs cost
-    // register moves and the scalar form is faster, so that layout keeps fmaf.  TENMO_SIMT_FFMA2=0/1 forces a form.
-    bool packed = a.mn_major || b.mn_major;
+    // TENMO_SIMT_FFMA2=0 switches the k loop to scalar fmaf (same bits; kept for comparisons).
+    bool packed = true;
     const char* env = getenv("TENMO_SIMT_FFMA2");
     if (env && (env[0] == '0' || env[0] == '1')) packed = env[0] == '1';
     tenmo_prof_before(ctx);
