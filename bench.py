@@ -372,10 +372,34 @@ def run_gpu_arm(args):
 
     mA, mB, mBt, mAt, mdC = mats(A, B, dC)
 
+    # 3xTF32: each input is split into its lo plane once per step (the transposed view of a matrix shares the plane of
+    # its storage) and the three GEMMs are handed the planes; the plain tenmo_gemm_f32 call would split both operands
+    # of every GEMM again.  Strict fp32 has no planes.
+    use_planes = algo == ALGO_TC_3XTF32
+
+    def new_planes():
+        return tuple(torch.empty(S * S, device="cuda") for _ in range(3)) if use_planes else None
+
+    def run_step(m, outs, planes):
+        m_a, m_b, m_bt, m_at, m_dc = m
+        c, da, db = outs
+        if not use_planes:
+            h.gemm(M, N, K, m_a, m_b, c.data_ptr(), algo=algo)       # C  = A . B
+            h.gemm(M, K, N, m_dc, m_bt, da.data_ptr(), algo=algo)    # dA = dC . B^T
+            h.gemm(K, N, M, m_at, m_dc, db.data_ptr(), algo=algo)    # dB = A^T . dC
+            return
+        a_lo, b_lo, dc_lo = (t.data_ptr() for t in planes)
+        h.split_lo(m_a, M, K, a_lo, S * S)
+        h.split_lo(m_b, K, N, b_lo, S * S)
+        h.gemm_ex(M, N, K, m_a, m_b, c.data_ptr(), algo=algo, a_lo=a_lo, b_lo=b_lo)
+        h.split_lo(m_dc, M, N, dc_lo, S * S)
+        h.gemm_ex(M, K, N, m_dc, m_bt, da.data_ptr(), algo=algo, a_lo=dc_lo, b_lo=b_lo)
+        h.gemm_ex(K, N, M, m_at, m_dc, db.data_ptr(), algo=algo, a_lo=a_lo, b_lo=dc_lo)
+
+    planes0 = new_planes()
+
     def step_device():
-        h.gemm(M, N, K, mA, mB, C.data_ptr(), algo=algo)       # C  = A . B
-        h.gemm(M, K, N, mdC, mBt, dA.data_ptr(), algo=algo)    # dA = dC . B^T
-        h.gemm(K, N, M, mAt, mdC, dB.data_ptr(), algo=algo)    # dB = A^T . dC
+        run_step((mA, mB, mBt, mAt, mdC), (C, dA, dB), planes0)
 
     # End to end: every step copies A, B, dC from pinned host memory and reads C, dA, dB back.  The copies run on their
     # own streams and two sets of device buffers alternate, so that the uploads of step i+1 and the read-back of step
@@ -385,6 +409,7 @@ def run_gpu_arm(args):
     sets.append(dict(inp=tuple(torch.empty_like(t) for t in (A, B, dC)), out=tuple(torch.empty_like(t) for t in (C, dA, dB))))
     for st in sets:
         st["mats"] = mats(*st["inp"])
+        st["planes"] = planes0 if st is sets[0] else new_planes()
         st["ev_ab"], st["ev_dc"], st["ev_c"], st["ev_da"], st["ev_db"], st["ev_read"] = (torch.cuda.Event() for _ in range(6))
         st["used"] = False
     e2e_count = [0]
@@ -406,12 +431,25 @@ def run_gpu_arm(args):
         if st["used"]:
             stream.wait_event(st["ev_read"])           # this set's previous results have been read back
         stream.wait_event(st["ev_ab"])
-        h.gemm(M, N, K, m_a, m_b, c.data_ptr(), algo=algo)
+        if use_planes:
+            a_lo, b_lo, dc_lo = (t.data_ptr() for t in st["planes"])
+            h.split_lo(m_a, M, K, a_lo, S * S)
+            h.split_lo(m_b, K, N, b_lo, S * S)
+            h.gemm_ex(M, N, K, m_a, m_b, c.data_ptr(), algo=algo, a_lo=a_lo, b_lo=b_lo)
+        else:
+            h.gemm(M, N, K, m_a, m_b, c.data_ptr(), algo=algo)
         st["ev_c"].record(stream)
         stream.wait_event(st["ev_dc"])
-        h.gemm(M, K, N, m_dc, m_bt, da.data_ptr(), algo=algo)
+        if use_planes:
+            h.split_lo(m_dc, M, N, dc_lo, S * S)
+            h.gemm_ex(M, K, N, m_dc, m_bt, da.data_ptr(), algo=algo, a_lo=dc_lo, b_lo=b_lo)
+        else:
+            h.gemm(M, K, N, m_dc, m_bt, da.data_ptr(), algo=algo)
         st["ev_da"].record(stream)
-        h.gemm(K, N, M, m_at, m_dc, db.data_ptr(), algo=algo)
+        if use_planes:
+            h.gemm_ex(K, N, M, m_at, m_dc, db.data_ptr(), algo=algo, a_lo=a_lo, b_lo=dc_lo)
+        else:
+            h.gemm(K, N, M, m_at, m_dc, db.data_ptr(), algo=algo)
         st["ev_db"].record(stream)
         with torch.cuda.stream(s_d2h):
             s_d2h.wait_event(st["ev_c"])
@@ -474,7 +512,7 @@ def run_gpu_arm(args):
     last_kernel = h.gemm_last_kernel()  # which GEMM kernel the steps above launched
 
     # release the GEMM buffers before the MLP legs
-    del A, B, dC, C, dA, dB, host_in, host_out, sets
+    del A, B, dC, C, dA, dB, host_in, host_out, sets, planes0
     torch.cuda.empty_cache()
     mlp = None if args.no_mlp else measure_mlps(h, rank, world, local_rank, timed, args)
 
@@ -501,7 +539,7 @@ def run_gpu_arm(args):
             "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"fp32 GEMM fwd+bwd (C=A.B, dA=dC.B^T, dB=A^T.dC) at M=N=K={S}, N(0,1) seeded, "
-                                   f"transposes as stride views", "size": S, "algo": "3xtf32-tcgen05" if algo == 1 else "simt-fp32",
+                                   f"transposes as stride views; 3xTF32: each input split into its lo plane once per step", "size": S, "algo": "3xtf32-tcgen05" if algo == 1 else "simt-fp32",
                        "parallelism": f"replicas x{world}", "l2": "inputs (3 x %.0f MB) exceed the 126 MB L2" % (S * S * 4 / 1e6)},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": 3 * S * S * 4, "d2h_bytes_per_step": 3 * S * S * 4,
