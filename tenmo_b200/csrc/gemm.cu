@@ -1,6 +1,7 @@
 // tenmo_gemm_f32 / tenmo_gemm_f32_ex: argument validation, batch broadcasting and kernel selection.
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "reduce.cuh"
 
 namespace {
 
@@ -84,11 +85,17 @@ int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K,
             return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm: tensor-core kernel cannot take this call: %s", why);
         if (ok && (algo == TENMO_ALGO_TC_3XTF32 || tenmo_gemm_tc_profitable(ctx, p))) chosen = TENMO_ALGO_TC_3XTF32;
     }
-    if (chosen == TENMO_ALGO_TC_3XTF32) st = tenmo_gemm_tc_launch(ctx, p);
-    else st = tenmo_gemm_simt_launch(ctx, p);
+    bool colsum_done = false;
+    if (chosen == TENMO_ALGO_TC_3XTF32) {
+        st = tenmo_gemm_tc_launch(ctx, p);
+    } else {
+        // up to TENMO_COLSUM_SEQ_ROWS rows the column sum is the sequential one, which the GEMM kernel can produce itself
+        if (o->colsum && B->col_stride == 1 && K <= TENMO_COLSUM_SEQ_ROWS && K > 0) p.colsum = o->colsum;
+        st = tenmo_gemm_simt_launch(ctx, p, &colsum_done);
+    }
     if (st != TENMO_OK) return st;
     ctx->last_gemm_algo = chosen;
-    if (o->colsum) {
+    if (o->colsum && !colsum_done) {
         // column sums of the right operand: db when this call is dW = X^T . dY
         if (B->col_stride != 1)
             return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm: colsum needs a unit column stride on B");

@@ -150,6 +150,14 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
         for (int j = 0; j < TN / 2; ++j) acc[i][j] = make_float2(init, init);
     }
 
+    // Column sums of B riding along (2-D calls only): the CTAs of the first tile row see every k of their columns pass
+    // through shared memory; their ty == 0 threads add them in ascending k, the reference's sequential sum.
+    constexpr bool CAN_COLSUM = BM < 128;
+    const bool do_cs = CAN_COLSUM && p.colsum != nullptr && tile_m == 0 && ty == 0;
+    float cs[TN];
+#pragma unroll
+    for (int j = 0; j < TN; ++j) cs[j] = 0.f;
+
     LoaderA la;
     LoaderB lb;
     const int64_t k_tiles = (p.K + BK - 1) / BK;
@@ -191,6 +199,10 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
 #pragma unroll
                 for (int j = 0; j < TN; ++j) b[j] = bs[kk * LoaderB::LD + tx * TN + j];
             }
+            if (CAN_COLSUM && do_cs) {
+#pragma unroll
+                for (int j = 0; j < TN; ++j) cs[j] += b[j];
+            }
 #pragma unroll
             for (int i = 0; i < TM; ++i)
 #pragma unroll
@@ -203,6 +215,14 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
             lb.store(Bs[cur ^ 1], tid);
         }
         __syncthreads();
+    }
+
+    if (CAN_COLSUM && do_cs) {
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int64_t n = n0 + frag_index<TN, BN>(tx, j);
+            if (n < p.N) p.colsum[n] = p.beta != 0.f ? p.colsum[n] + cs[j] : cs[j];
+        }
     }
 
     // Epilogue: bias, activation (+ mask), accumulate, store.
@@ -264,8 +284,9 @@ cudaError_t launch_cfg(const TenmoGemmParams& p, bool a_inner_k, bool b_inner_k,
 
 }  // namespace
 
-int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p_in) {
+int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p_in, bool* colsum_done) {
     TenmoGemmParams p = p_in;
+    if (colsum_done) *colsum_done = false;
     auto absl = [](int64_t v) { return v < 0 ? -v : v; };
     // Group loads along the axis with the smaller stride (the unit-stride axis when there is one).
     const bool a_inner_k = absl(p.a_cs) <= absl(p.a_rs);
@@ -292,6 +313,7 @@ int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p_in) {
     else cfg = 32;
     if (cfg == 128 && (p.M <= 64 || p.N <= 64)) cfg = 64;
     if (cfg == 64 && (p.M <= 32 || p.N <= 32)) cfg = 32;
+    if (cfg == 128) p.colsum = nullptr;  // the 128 x 128 tiles leave the column sum to its own kernel
     if (cfg == 128 && p.K >= 64) {
         const char* env = getenv("TENMO_SIMT_TMA");  // "0" keeps the register-staged kernel (for comparisons)
         if (!(env && env[0] == '0') && tenmo_gemm_simt_tma_supported(ctx, p)) return tenmo_gemm_simt_tma_launch(ctx, p);
@@ -306,7 +328,9 @@ int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p_in) {
     tenmo_prof_before(ctx);
     if (cfg == 128) e = launch_cfg<128, 128, 16, 8, 8>(p, a_inner_k, b_inner_k, grid, ctx->stream);
     else if (cfg == 64) e = launch_cfg<64, 64, 16, 4, 4>(p, a_inner_k, b_inner_k, grid, ctx->stream);
-    else e = launch_cfg<32, 32, 32, 2, 2>(p, a_inner_k, b_inner_k, grid, ctx->stream);
+    else if (p.K <= 32) e = launch_cfg<32, 32, 32, 2, 2>(p, a_inner_k, b_inner_k, grid, ctx->stream);
+    else e = launch_cfg<32, 32, 64, 2, 2>(p, a_inner_k, b_inner_k, grid, ctx->stream);  // deep k-tiles: fewer load round trips
+    if (colsum_done) *colsum_done = p.colsum != nullptr;
     tenmo_prof_after(ctx);
     ctx->launches++;
     ctx->last_gemm_kernel = "gemm_simt_kernel";

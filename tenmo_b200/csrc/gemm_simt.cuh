@@ -33,6 +33,8 @@ struct TenmoGemmParams {
     int64_t ld_clo;
     const float* mul_mask;  // optional (total_batch, M, N): result is multiplied by it before beta / store
     const float* bias_m;    // optional M floats: per-row bias (the per-channel bias of a convolution)
+    float* colsum;          // optional N floats: column sums of B over k, k ascending (the bias gradient riding along with
+                            // dW = X^T . dY); honoured by the 64 / 32 tiles of the register-staged kernel only, see colsum_done
     int tiles_m, tiles_n;
     int64_t total_batch;
     TenmoBatch batch;
@@ -42,6 +44,7 @@ struct TenmoGemmParams {
 // 16-byte aligned base and leading stride, batch dims that collapse to one stride) go to the TMA-staged
 // kernel of gemm_simt_tma.cu, everything else to the register-staged kernels of gemm_simt.cu.  Both give the
 // same bits.
-int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p);
+// *colsum_done (may be NULL) tells whether the kernel also wrote p.colsum; if not, the caller runs the column sum.
+int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p, bool* colsum_done = nullptr);
 bool tenmo_gemm_simt_tma_supported(tenmo_ctx* ctx, const TenmoGemmParams& p);
 int tenmo_gemm_simt_tma_launch(tenmo_ctx* ctx, const TenmoGemmParams& p);
