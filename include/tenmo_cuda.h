@@ -60,6 +60,12 @@ int tenmo_cuda_device_info(tenmo_ctx* ctx, int* sm_count, int* cc_major, int* cc
 /* Synchronises, then reads the device status word kernels set when a bounded wait (mbarrier) gave up.
  * Returns TENMO_OK or TENMO_ERR_TIMEOUT; the word is cleared. */
 int tenmo_cuda_check_device_status(tenmo_ctx* ctx);
+/* Launches a one-thread kernel that waits, with the bounded wait of the GEMM kernels and a limit of limit_us
+ * microseconds (1 .. 1 000 000), on a barrier nothing ever arrives on.  The kernel gives up, raises the status word and
+ * returns like any other; the next tenmo_cuda_check_device_status then answers TENMO_ERR_TIMEOUT and the context stays
+ * usable.  No reference counterpart: it exists so that the expiry path of the device-side waits can be exercised
+ * without a fault. */
+int tenmo_cuda_wait_probe(tenmo_ctx* ctx, int limit_us);
 /* Counts kernel launches made through this context since the last reset (bookkeeping for benchmarks). */
 int64_t tenmo_cuda_launch_count(tenmo_ctx* ctx, int reset);
 /* Device timing of the GEMM main kernels (not the split / reduction helpers around them): between

@@ -571,6 +571,28 @@ int tenmo_tma_init(tenmo_ctx* ctx) {
 }
 
 
+namespace {
+// One thread waits on an mbarrier nothing will ever arrive on, with the wait routine the GEMM kernels use and a short
+// limit: the expiry path (give up, raise the status word, leave) as a normal, returning kernel.
+__global__ void wait_probe_kernel(uint64_t limit_ns, uint32_t* status) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!mbar_wait(smem_u32(&bar), 0, &abort_flag, limit_ns)) atomicOr(status, TENMO_DEV_TIMEOUT);
+}
+}  // namespace
+
+extern "C" int tenmo_cuda_wait_probe(tenmo_ctx* ctx, int limit_us) {
+    TENMO_CHECK_CTX(ctx);
+    if (limit_us < 1 || limit_us > 1000000) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "wait_probe: limit must be 1 us .. 1 s");
+    TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    wait_probe_kernel<<<1, 1, 0, ctx->stream>>>((uint64_t)limit_us * 1000ull, ctx->dev_status);
+    TENMO_LAUNCH_CHECK(ctx, "wait_probe_kernel");
+    return TENMO_OK;
+}
+
 bool tenmo_gemm_tc_supported(tenmo_ctx* ctx, const TenmoGemmParams& p, char* why, size_t why_len) {
     (void)ctx;
     TenmoOperandPlan a, b;

@@ -36,7 +36,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: false when another role aborted or the time limit ran out (then *abort is raised).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort,
+                                          uint64_t limit_ns = TENMO_WAIT_LIMIT_NS) {
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -44,7 +45,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort) return false;
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > TENMO_WAIT_LIMIT_NS) { *abort = 1; return false; }
+            else if (now - t0 > limit_ns) { *abort = 1; return false; }
         }
     }
 }
