@@ -38,6 +38,54 @@ int build_batch(tenmo_ctx* ctx, const tenmo_mat* A, const tenmo_mat* B, TenmoBat
 
 extern "C" {
 
+// Split-K for the tensor-core kernel: a product with a small output and a very long k (the weight gradient of a narrow
+// layer at a large batch, K = batch) leaves most SMs without a tile.  The k range is cut into S equal slices that run
+// as the S batches of one batched GEMM (operand batch stride = one slice along k) into S partial results, which the
+// sequential column-sum kernel then adds in slice order (deterministic) into C.  Only for calls without an epilogue and
+// without caller-supplied lo planes; the strict-fp32 kernel never splits (one k-ascending chain per output is its contract).
+static int tc_split_k(tenmo_ctx* ctx, const TenmoGemmParams& p, const tenmo_gemm_opts* o, bool* done) {
+    *done = false;
+    if (p.total_batch != 1 || p.batch.rank != 0) return TENMO_OK;
+    if (o->bias || o->act != TENMO_ACT_NONE || o->aux || o->mul_mask || o->c_lo || o->bias_m || o->a_lo || o->b_lo) return TENMO_OK;
+    const int64_t tiles = ((p.M + 127) / 128) * ((p.N + 127) / 128);
+    if (p.K < 4096 || tiles * 2 > ctx->sm_count) return TENMO_OK;
+    // slices: enough for about 1.5 work units per SM, each at least 512 long and a multiple of the k-block, K = S * slice
+    const int64_t want = (3 * (int64_t)ctx->sm_count / 2 + tiles - 1) / tiles;
+    const int64_t s_max = p.K / 512 < TENMO_COLSUM_SEQ_ROWS ? p.K / 512 : TENMO_COLSUM_SEQ_ROWS;
+    auto fits = [&](int64_t s) { return s >= 2 && p.K % s == 0 && (p.K / s) % 32 == 0; };
+    int64_t S = 0;
+    for (int64_t s = want; s <= s_max && S == 0; ++s)
+        if (fits(s)) S = s;
+    for (int64_t s = (want < s_max ? want : s_max); s >= 2 && S == 0; --s)
+        if (fits(s)) S = s;
+    if (S == 0) return TENMO_OK;
+    const int64_t Ks = p.K / S;
+    TenmoGemmParams q = p;
+    q.K = Ks;
+    q.total_batch = S;
+    q.batch.rank = 1;
+    q.batch.shape[0] = S;
+    q.batch.a_stride[0] = Ks * p.a_cs;
+    q.batch.b_stride[0] = Ks * p.b_rs;
+    q.beta = 0.f;
+    char why[160];
+    if (!tenmo_gemm_tc_supported(ctx, q, why, sizeof(why))) return TENMO_OK;
+    const size_t part_bytes = (((size_t)S * (size_t)p.M * (size_t)p.N * sizeof(float)) + 1023) & ~(size_t)1023;
+    // reserve partials + lo planes in one request so that the kernel launch below does not move the block
+    const size_t lo_bytes = ((size_t)(p.M + 4) * (size_t)(p.K + 4) + (size_t)(p.N + 4) * (size_t)(p.K + 4)) * sizeof(float) + 8192;
+    void* ws = nullptr;
+    int st = tenmo_workspace(ctx, part_bytes + lo_bytes, &ws);
+    if (st != TENMO_OK) return st;
+    q.C = static_cast<float*>(ws);
+    q.ws_skip = part_bytes;
+    st = tenmo_gemm_tc_launch(ctx, q);
+    if (st != TENMO_OK) return st;
+    st = tenmo_colsum_f32(ctx, q.C, S, p.M * p.N, p.M * p.N, p.C, p.beta);
+    if (st != TENMO_OK) return st;
+    *done = true;
+    return TENMO_OK;
+}
+
 int tenmo_gemm_last_algo(tenmo_ctx* ctx) { return ctx ? ctx->last_gemm_algo : -1; }
 const char* tenmo_gemm_last_kernel(tenmo_ctx* ctx) { return ctx ? ctx->last_gemm_kernel : ""; }
 
@@ -87,7 +135,9 @@ int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K,
     }
     bool colsum_done = false;
     if (chosen == TENMO_ALGO_TC_3XTF32) {
-        st = tenmo_gemm_tc_launch(ctx, p);
+        bool split_done = false;
+        st = tc_split_k(ctx, p, o, &split_done);
+        if (st == TENMO_OK && !split_done) st = tenmo_gemm_tc_launch(ctx, p);
     } else {
         // up to TENMO_COLSUM_SEQ_ROWS rows the column sum is the sequential one, which the GEMM kernel can produce itself
         if (o->colsum && B->col_stride == 1 && K <= TENMO_COLSUM_SEQ_ROWS && K > 0) p.colsum = o->colsum;

@@ -35,6 +35,7 @@ struct TenmoGemmParams {
     const float* bias_m;    // optional M floats: per-row bias (the per-channel bias of a convolution)
     float* colsum;          // optional N floats: column sums of B over k, k ascending (the bias gradient riding along with
                             // dW = X^T . dY); honoured by the 64 / 32 tiles of the register-staged kernel only, see colsum_done
+    size_t ws_skip;         // bytes at the start of the context workspace that belong to the caller (split-K partials)
     int tiles_m, tiles_n;
     int64_t total_batch;
     TenmoBatch batch;

@@ -635,8 +635,9 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     const size_t b_lo_bytes = p.b_lo ? 0 : (((size_t)b.bstride_lo * b.batches * 4 + 1023) & ~(size_t)1023);
     void* ws = nullptr;
     if (a_lo_bytes + b_lo_bytes > 0) {
-        st = tenmo_workspace(ctx, a_lo_bytes + b_lo_bytes, &ws);
+        st = tenmo_workspace(ctx, p.ws_skip + a_lo_bytes + b_lo_bytes, &ws);
         if (st != TENMO_OK) return st;
+        ws = static_cast<char*>(ws) + p.ws_skip;
     }
     const float* a_lo = p.a_lo ? p.a_lo : static_cast<float*>(ws);
     const float* b_lo = p.b_lo ? p.b_lo : reinterpret_cast<float*>(static_cast<char*>(ws) + a_lo_bytes);

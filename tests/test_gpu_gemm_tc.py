@@ -181,3 +181,25 @@ def test_tc_run_to_run_identical(g, oracle):
     C1, _, _ = g.gpu_matmul(oracle.View.of(A), oracle.View.of(B), algo=TC)
     C2, _, _ = g.gpu_matmul(oracle.View.of(A), oracle.View.of(B), algo=TC)
     assert np.array_equal(C1, C2)
+
+
+@pytest.mark.parametrize("mkn", [(784, 65536, 128), (200, 8192, 96), (128, 16384, 256)], ids=str)
+@pytest.mark.parametrize("layout", ["nn", "tn"])
+def test_tc_split_k_for_small_outputs_with_long_k(g, oracle, mkn, layout):
+    """A small output with a very long k (dW of a narrow layer at a large batch) is cut along k into the batches of one
+    batched launch plus an ordered sum: same bar as the unsplit kernel, beta = 1 honoured, repeatable."""
+    M, K, N = mkn
+    rng = np.random.default_rng(M + N)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32)
+    Av, Bv = layouts(oracle, A, B, layout)
+    launches = g.handle().launch_count()
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert g.handle().launch_count() - launches == 4  # two lo-plane splits, the batched GEMM, the ordered sum
+    ref64 = A.astype(np.float64) @ B.astype(np.float64)
+    assert rel_err(C, ref64, np.abs(A), np.abs(B)) <= TOL
+    init = rng.standard_normal((M, N), np.float32)
+    C1, _, _ = g.gpu_matmul(Av, Bv, algo=TC, beta=1.0, c_init=init)
+    assert rel_err(C1, init.astype(np.float64) + ref64, np.abs(A), np.abs(B)) <= TOL
+    C2, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert np.array_equal(C, C2)
+    g.handle().check_device_status()
