@@ -42,13 +42,15 @@ constexpr int UMMA_K = 8;                    // tf32 k per instruction
 constexpr int SQ = 4;                        // depth of the tile-id ring between the scheduler and its consumers
 constexpr int TILE_COUNTERS = 32;            // ring of global tile counters, one per GEMM launch in flight
 
+constexpr int EP_LD = 36;  // floats per row of an epilogue warp's 32 x 32 staging block (144 B: conflict-free both ways)
+
 template <int BN>
 struct TcCfg {
     static constexpr int A_TILE = BM * BK * 4;   // bytes of one plane of A per stage
     static constexpr int B_TILE = BN * BK * 4;
     static constexpr int STAGE = 2 * A_TILE + 2 * B_TILE;
     static constexpr int STAGES = ((BN == 256) ? 2 : (BN == 128 ? 3 : 4)) * (32 / BK);
-    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * 32 * EP_LD * 4 /*epilogue staging*/;
     static constexpr int TMEM_COLS = 2 * BN;     // two accumulators
 };
 
@@ -312,6 +314,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // ------------------------------- epilogue (warps 2..5) -------------------------------
         const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
+        float* ebuf = reinterpret_cast<float*>(smem_gen + Cfg::STAGES * Cfg::STAGE + 256) + quarter * (32 * EP_LD);
         uint32_t acc_phase[2] = {0, 0};
         int acc = 0;
         bool ok = true;
@@ -338,62 +341,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
             if (!warp_wait(tfull_bar(acc), acc_phase[acc])) { ok = false; break; }
             tcgen05_fence_after();
-            const int64_t m = (int64_t)tm * BM + quarter * 32 + lane;
+            // A thread's tcgen05.ld delivers 32 consecutive columns of ONE row, so storing straight from those
+            // registers would make every warp-wide store touch 32 rows, 16 bytes each.  The 32 x 32 block goes through a
+            // per-warp shared-memory buffer instead (rows padded to 36 floats: conflict-free both ways) and comes back
+            // as (row = 4i + lane/8, columns 4*(lane%8)..+3): a warp-wide access then covers four full 128-byte row
+            // segments, for the result as for the mask, the old C, the ReLU mask and the lo plane.
+            const int64_t m_warp = (int64_t)tm * BM + quarter * 32;
             const int64_t n_base = (int64_t)tn * BN;
-            float* crow = p.C + (batch * p.M + m) * p.N;
-            float* auxrow = p.aux ? p.aux + (batch * p.M + m) * p.N : nullptr;
-            const float* maskrow = p.mul_mask ? p.mul_mask + (batch * p.M + m) * p.N : nullptr;
-            float* clorow = p.c_lo ? p.c_lo + (batch * p.M + m) * p.ld_clo : nullptr;
-            const float row_bias = (p.bias_m && m < p.M) ? __ldg(p.bias_m + m) : 0.f;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+            const int col4 = (lane & 7) * 4, row_sub = lane >> 3;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
+                const int64_t n0 = n_base + c * 32;
+                if (n0 >= p.N) break;  // uniform: the rest of the tile lies outside the matrix
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), r);
                 tmem_ld_wait();
-                const int64_t n0 = n_base + c * 32;
-                if (m < p.M && n0 < p.N) {
 #pragma unroll
-                    for (int q = 0; q < 32; q += 4) {
-                        const int64_t n = n0 + q;
-                        if (n >= p.N) break;
-                        float v[4], mk[4];
+                for (int q = 0; q < 32; q += 4)
+                    *reinterpret_cast<float4*>(ebuf + lane * EP_LD + q) =
+                        make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]), __uint_as_float(r[q + 2]),
+                                    __uint_as_float(r[q + 3]));
+                __syncwarp();
+                const int64_t n = n0 + col4;
+                float cb[4] = {0.f, 0.f, 0.f, 0.f};
+                if (p.bias) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float x = __uint_as_float(r[q + e]) + row_bias;
-                            if (p.bias && n + e < p.N) x += __ldg(p.bias + n + e);
-                            mk[e] = x > 0.f ? 1.f : 0.f;
-                            v[e] = act_apply(x, p.act);
+                    for (int e = 0; e < 4; ++e)
+                        if (n + e < p.N) cb[e] = __ldg(p.bias + n + e);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int row_l = 4 * i + row_sub;
+                    const int64_t m = m_warp + row_l;
+                    const float4 x4 = *reinterpret_cast<const float4*>(ebuf + row_l * EP_LD + col4);
+                    if (m >= p.M || n >= p.N) continue;
+                    const float row_bias = p.bias_m ? __ldg(p.bias_m + m) : 0.f;
+                    const int64_t row_off = (batch * p.M + m) * p.N;
+                    float* crow = p.C + row_off;
+                    const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
+                    float v[4], mk[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float x = xs[e] + row_bias + cb[e];
+                        mk[e] = x > 0.f ? 1.f : 0.f;
+                        v[e] = act_apply(x, p.act);
+                    }
+                    if (p.c_vec && n + 3 < p.N) {
+                        float4 o = make_float4(v[0], v[1], v[2], v[3]);
+                        if (p.mul_mask) {
+                            const float4 mm = __ldg(reinterpret_cast<const float4*>(p.mul_mask + row_off + n));
+                            o.x *= mm.x; o.y *= mm.y; o.z *= mm.z; o.w *= mm.w;
                         }
-                        if (p.c_vec && n + 3 < p.N) {
-                            float4 o = make_float4(v[0], v[1], v[2], v[3]);
-                            if (maskrow) {
-                                const float4 mm = __ldg(reinterpret_cast<const float4*>(maskrow + n));
-                                o.x *= mm.x; o.y *= mm.y; o.z *= mm.z; o.w *= mm.w;
-                            }
-                            if (p.beta != 0.f) {
-                                const float4 old = *reinterpret_cast<const float4*>(crow + n);
-                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                            }
-                            *reinterpret_cast<float4*>(crow + n) = o;
-                            if (auxrow) *reinterpret_cast<float4*>(auxrow + n) = make_float4(mk[0], mk[1], mk[2], mk[3]);
-                            if (clorow)
-                                *reinterpret_cast<float4*>(clorow + n) = make_float4(tenmo_tf32_lo(o.x), tenmo_tf32_lo(o.y),
-                                                                                     tenmo_tf32_lo(o.z), tenmo_tf32_lo(o.w));
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                if (n + e < p.N) {
-                                    float o = v[e];
-                                    if (maskrow) o *= __ldg(maskrow + n + e);
-                                    if (p.beta != 0.f) o += crow[n + e];
-                                    crow[n + e] = o;
-                                    if (auxrow) auxrow[n + e] = mk[e];
-                                    if (clorow) clorow[n + e] = tenmo_tf32_lo(o);
-                                }
+                        if (p.beta != 0.f) {
+                            const float4 old = *reinterpret_cast<const float4*>(crow + n);
+                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                         }
+                        *reinterpret_cast<float4*>(crow + n) = o;
+                        if (p.aux) *reinterpret_cast<float4*>(p.aux + row_off + n) = make_float4(mk[0], mk[1], mk[2], mk[3]);
+                        if (p.c_lo)
+                            *reinterpret_cast<float4*>(p.c_lo + (batch * p.M + m) * p.ld_clo + n) =
+                                make_float4(tenmo_tf32_lo(o.x), tenmo_tf32_lo(o.y), tenmo_tf32_lo(o.z), tenmo_tf32_lo(o.w));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (n + e < p.N) {
+                                float o = v[e];
+                                if (p.mul_mask) o *= __ldg(p.mul_mask + row_off + n + e);
+                                if (p.beta != 0.f) o += crow[n + e];
+                                crow[n + e] = o;
+                                if (p.aux) p.aux[row_off + n + e] = mk[e];
+                                if (p.c_lo) p.c_lo[(batch * p.M + m) * p.ld_clo + n + e] = tenmo_tf32_lo(o);
+                            }
                     }
                 }
+                __syncwarp();  // the buffer is rewritten by the next chunk
             }
             tcgen05_fence_before();
             __syncwarp();
