@@ -213,6 +213,36 @@ def measure_mlps(h, rank, world, local_rank, timed, args):
     return out
 
 
+def measure_other_sizes(h, algo, timed):
+    """The other sizes of the GEMM configuration (square 1024 / 2048 / 4096, skinny 65536 x 784 x 128): forward +
+    backward through the plain tenmo_gemm_f32 call, device-resident, a few steps each.  Secondary figures; the
+    headline is the largest square size."""
+    import torch
+
+    from tenmo_b200 import make_mat
+
+    res = {}
+    for name, (M, K, N) in (("1024", (1024,) * 3), ("2048", (2048,) * 3), ("4096", (4096,) * 3), ("skinny_65536x784x128", (65536, 784, 128))):
+        A, B, dC = torch.randn(M, K, device="cuda"), torch.randn(K, N, device="cuda"), torch.randn(M, N, device="cuda")
+        C, dA, dB = torch.empty(M, N, device="cuda"), torch.empty(M, K, device="cuda"), torch.empty(K, N, device="cuda")
+        mA, mB, mdC = (make_mat(t.data_ptr(), tuple(t.shape), (t.shape[1], 1)) for t in (A, B, dC))
+        mBt, mAt = make_mat(B.data_ptr(), (N, K), (1, N)), make_mat(A.data_ptr(), (K, M), (1, K))
+
+        def step():
+            h.gemm(M, N, K, mA, mB, C.data_ptr(), algo=algo)
+            h.gemm(M, K, N, mdC, mBt, dA.data_ptr(), algo=algo)
+            h.gemm(K, N, M, mAt, mdC, dB.data_ptr(), algo=algo)
+
+        for _ in range(3):
+            step()
+        steps = 10
+        ms = timed(step, steps)
+        res[name] = {"tflops": 6.0 * M * N * K * steps / (ms * 1e-3) / 1e12, "ms_per_step": ms / steps}
+        del A, B, dC, C, dA, dB
+    torch.cuda.empty_cache()
+    return res
+
+
 def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen):
     import numpy as np
     import torch
@@ -514,6 +544,7 @@ def run_gpu_arm(args):
     # release the GEMM buffers before the MLP legs
     del A, B, dC, C, dA, dB, host_in, host_out, sets, planes0
     torch.cuda.empty_cache()
+    sweep = None if (args.no_sweep or world > 1) else measure_other_sizes(h, algo, timed)
     mlp = None if args.no_mlp else measure_mlps(h, rank, world, local_rank, timed, args)
 
     flop_step = 6.0 * M * N * K
@@ -552,6 +583,8 @@ def run_gpu_arm(args):
                          "traffic": NCU_TRAFFIC_BYTES.get((kernel, S)), "traffic_unit": "bytes per launch (ncu, dram read+write)",
                          "launches_timed": n_kernel, "avg_launch_ms": kernel_ms / max(n_kernel, 1), "peak_note": peak_note},
         }
+        if sweep:
+            out["other_sizes"] = sweep
         if mlp:
             out.update(mlp)
         if world == 1 and not args.no_cpu:
@@ -644,6 +677,7 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=20.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-mlp", action="store_true", help="skip the MLP training legs")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the smaller / skinny GEMM sizes of the same configuration")
     ap.add_argument("--mlp-steps", type=int, default=20)
     ap.add_argument("--legs", default="wide_mlp,cnn,mnist_mlp", help="which training legs to run after the GEMM arm")
     ap.add_argument("--kernels", action="store_true",
