@@ -265,6 +265,22 @@ int tenmo_dp_init(tenmo_ctx* ctx, int rank, int world, const void* id, size_t id
 int tenmo_dp_allreduce_sum_f32(tenmo_ctx* ctx, float* buf, int64_t count);
 int tenmo_dp_finalize(tenmo_ctx* ctx);
 
+/* The same exchange as one kernel of this library over NVLink peer memory (no NCCL; no reference counterpart).
+ * Every rank allocates the gradient bucket inside the library (tenmo_dp_p2p_alloc: `count` floats, zeroed; the
+ * pointer is the caller's to fill, the memory stays the library's) and receives TENMO_DP_P2P_HANDLE_BYTES of CUDA IPC
+ * handles; the ranks share their handle blocks out of band, rank-major, and every rank calls tenmo_dp_p2p_connect
+ * with all of them.  tenmo_dp_p2p_allreduce_sum_f32 then sums bucket[offset, offset + count) over the ranks in place,
+ * asynchronously on the context stream: every element is added once, in rank order, by the rank that owns its
+ * shard, so all ranks end with identical bits.  All ranks must make the same calls in the same order.  The kernel is
+ * small enough to run beside the persistent GEMM kernels; its waits on the peers are bounded (2 s) and report through
+ * tenmo_cuda_check_device_status.  At most 8 ranks, all on one node.  tenmo_dp_p2p_close unmaps and frees; the ranks
+ * must have finished using each other's buckets (a host barrier) before any of them calls it. */
+#define TENMO_DP_P2P_HANDLE_BYTES 128
+int tenmo_dp_p2p_alloc(tenmo_ctx* ctx, int64_t count, float** buf_out, void* handles_out, size_t handles_bytes);
+int tenmo_dp_p2p_connect(tenmo_ctx* ctx, int rank, int world, const void* all_handles, size_t handles_bytes);
+int tenmo_dp_p2p_allreduce_sum_f32(tenmo_ctx* ctx, int64_t offset, int64_t count);
+int tenmo_dp_p2p_close(tenmo_ctx* ctx);
+
 #ifdef __cplusplus
 }
 #endif

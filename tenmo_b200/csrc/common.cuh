@@ -51,6 +51,14 @@ struct tenmo_ctx {
     void* nccl_lib = nullptr;
     void* nccl_comm = nullptr;
     int dp_rank = 0, dp_world = 1;
+    // peer-memory exchange (dp_p2p.cu): own bucket + flag block, and every rank's, mapped through CUDA IPC
+    void* p2p_buf = nullptr;
+    void* p2p_flags = nullptr;
+    void* p2p_peer_buf[8] = {nullptr};
+    void* p2p_peer_flags[8] = {nullptr};
+    int64_t p2p_count = 0;
+    uint32_t p2p_epoch = 0;
+    int p2p_rank = 0, p2p_world = 0;
 };
 
 int tenmo_set_error(tenmo_ctx* ctx, int status, const char* fmt, ...);

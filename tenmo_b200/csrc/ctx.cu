@@ -124,6 +124,7 @@ void tenmo_cuda_destroy(tenmo_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->nccl_comm) tenmo_dp_finalize(ctx);
+    if (ctx->p2p_buf) tenmo_dp_p2p_close(ctx);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->dev_status) cudaFree(ctx->dev_status);

@@ -1,0 +1,229 @@
+// Data-parallel gradient exchange over NVLink peer memory: a sum all-reduce written as ONE kernel per call.
+//
+// Why not only NCCL: the exchange of a layer's gradients should run beside the backward GEMMs of the layers below,
+// but the persistent GEMM kernel holds every SM with one large CTA, and NCCL's CTAs (hundreds of threads, ~100
+// registers each) cannot share an SM with it, so they wait for GEMM CTAs to leave.  The kernel here is built to
+// co-reside: 64 CTAs of 512 threads, ~32 registers, no shared-memory tile.
+//
+// Setup (one process per GPU): every rank allocates the gradient bucket and a small flag block with
+// tenmo_dp_p2p_alloc, the ranks exchange the two CUDA IPC handles out of band (the host's job, like NCCL's unique id),
+// and tenmo_dp_p2p_connect maps every peer's bucket and flags into this process.
+// One call sums bucket[offset, offset + count) over the ranks in place:
+//   wait until every peer's kernel for this call has started (its bucket holds its finished gradients: they were
+//       written by earlier work on its stream);
+//   reduce-scatter: rank r owns shard r of the range and adds the W copies of it in rank order 0..W-1 (peer copies
+//       are read over NVLink with 16-byte loads) into its own bucket -- every element is added once, by its owner,
+//       so all ranks end with identical bits;
+//   wait until every peer has reduced its shard; all-gather: copy the peers' reduced shards into the own bucket;
+//   wait until every peer has finished reading this rank's bucket (the next backward pass overwrites it).
+// The three waits are flags in peer memory, one per (phase, source rank, CTA): CTA b of a rank only ever depends on
+// CTA b of its peers (a shard is cut into chunks dealt round-robin to the CTAs, identically on every rank), so no
+// grid-wide synchronisation is needed.  Flags carry the call's epoch (monotonic), so nothing is ever reset.
+// Every wait is bounded (2 s): on expiry the CTA raises the context status word and returns.
+// No multicast, no TMA: plain peer loads and stores.  Roofline: NVLink, 2 * (W-1)/W * 4 * count bytes read per rank.
+#include "common.cuh"
+
+namespace {
+
+constexpr int P2P_CTAS = 64;
+constexpr int P2P_THREADS = 512;
+constexpr int P2P_MAX_WORLD = 8;
+constexpr int P2P_FLAG_WORDS = 3 * P2P_MAX_WORLD * P2P_CTAS;
+constexpr int P2P_CHUNK = 4 * P2P_THREADS;  // floats per chunk: one float4 per thread
+constexpr uint64_t P2P_WAIT_LIMIT_NS = 2000000000ull;
+
+struct P2PArgs {
+    float* buf[P2P_MAX_WORLD];       // bucket of every rank, mapped into this process
+    uint32_t* flags[P2P_MAX_WORLD];  // flag block of every rank
+    int rank, world;
+    int64_t off, count;
+    uint32_t epoch;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ uint64_t p2p_now_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Signal "CTA b of this rank has reached `phase` of call `epoch`" to every rank, then wait for the same from every
+// rank's CTA b.  False if a wait ran out.
+__device__ bool p2p_barrier(const P2PArgs& a, int phase, int* ok_smem) {
+    __threadfence_system();  // this thread's bucket writes are visible system-wide before the flag is
+    __syncthreads();
+    const int t = threadIdx.x;
+    if (t < a.world) {
+        uint32_t* dst = a.flags[t] + (phase * P2P_MAX_WORLD + a.rank) * P2P_CTAS + blockIdx.x;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(a.epoch) : "memory");
+        const uint32_t* src = a.flags[a.rank] + (phase * P2P_MAX_WORLD + t) * P2P_CTAS + blockIdx.x;
+        const uint64_t t0 = p2p_now_ns();
+        for (uint32_t it = 0;; ++it) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
+            if ((int32_t)(v - a.epoch) >= 0) break;
+            if ((it & 63u) == 63u && p2p_now_ns() - t0 > P2P_WAIT_LIMIT_NS) {
+                *ok_smem = 0;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    return *ok_smem != 0;
+}
+
+__global__ void __launch_bounds__(P2P_THREADS) dp_p2p_allreduce_kernel(const P2PArgs a) {
+    __shared__ int ok_smem;
+    if (threadIdx.x == 0) ok_smem = 1;
+    __syncthreads();
+    const int W = a.world, r = a.rank, b = blockIdx.x, t = threadIdx.x;
+    // shards: equal sizes, multiples of a chunk's float4 granularity; the last may be short or empty
+    const int64_t sz = ((a.count + W - 1) / W + 3) & ~(int64_t)3;
+    auto shard_len = [&](int p) {
+        const int64_t lo = (int64_t)p * sz;
+        return lo >= a.count ? (int64_t)0 : (a.count - lo < sz ? a.count - lo : sz);
+    };
+    const bool vec = ((a.off | sz) & 3) == 0;  // buckets come from cudaMalloc: 16-byte alignment follows from the offsets
+
+    if (!p2p_barrier(a, 0, &ok_smem)) { if (t == 0) atomicOr(a.status, TENMO_DEV_TIMEOUT); return; }
+
+    {   // reduce-scatter: this rank's shard, chunks b, b + CTAS, ...
+        const int64_t base = a.off + (int64_t)r * sz, len = shard_len(r);
+        for (int64_t c0 = (int64_t)b * P2P_CHUNK; c0 < len; c0 += (int64_t)P2P_CTAS * P2P_CHUNK) {
+            const int64_t j = c0 + 4 * t;
+            if (j >= len) continue;
+            if (vec && j + 3 < len) {
+                float4 acc = __ldcg(reinterpret_cast<const float4*>(a.buf[0] + base + j));
+                for (int p = 1; p < W; ++p) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + base + j));
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+                *reinterpret_cast<float4*>(a.buf[r] + base + j) = acc;
+            } else {
+                for (int e = 0; e < 4 && j + e < len; ++e) {
+                    float acc = __ldcg(a.buf[0] + base + j + e);
+                    for (int p = 1; p < W; ++p) acc += __ldcg(a.buf[p] + base + j + e);
+                    a.buf[r][base + j + e] = acc;
+                }
+            }
+        }
+    }
+
+    if (!p2p_barrier(a, 1, &ok_smem)) { if (t == 0) atomicOr(a.status, TENMO_DEV_TIMEOUT); return; }
+
+    for (int q = 1; q < W; ++q) {  // all-gather: the peers' reduced shards, starting with the next rank
+        const int p = (r + q) % W;
+        const int64_t base = a.off + (int64_t)p * sz, len = shard_len(p);
+        for (int64_t c0 = (int64_t)b * P2P_CHUNK; c0 < len; c0 += (int64_t)P2P_CTAS * P2P_CHUNK) {
+            const int64_t j = c0 + 4 * t;
+            if (j >= len) continue;
+            if (vec && j + 3 < len) {
+                *reinterpret_cast<float4*>(a.buf[r] + base + j) = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + base + j));
+            } else {
+                for (int e = 0; e < 4 && j + e < len; ++e) a.buf[r][base + j + e] = __ldcg(a.buf[p] + base + j + e);
+            }
+        }
+    }
+
+    if (!p2p_barrier(a, 2, &ok_smem)) { if (t == 0) atomicOr(a.status, TENMO_DEV_TIMEOUT); return; }
+}
+
+}  // namespace
+
+extern "C" {
+
+int tenmo_dp_p2p_alloc(tenmo_ctx* ctx, int64_t count, float** buf_out, void* handles_out, size_t handles_bytes) {
+    TENMO_CHECK_CTX(ctx);
+    if (count <= 0 || !buf_out || !handles_out || handles_bytes < TENMO_DP_P2P_HANDLE_BYTES)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "dp_p2p_alloc: need count > 0, buf_out and %d bytes for the handles",
+                               TENMO_DP_P2P_HANDLE_BYTES);
+    if (ctx->p2p_buf) return tenmo_set_error(ctx, TENMO_ERR_STATE, "dp_p2p_alloc: already allocated");
+    TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const size_t bytes = (((size_t)count * sizeof(float)) + 255) & ~(size_t)255;
+    TENMO_CUDA_TRY(ctx, cudaMalloc(&ctx->p2p_buf, bytes));
+    TENMO_CUDA_TRY(ctx, cudaMalloc(&ctx->p2p_flags, P2P_FLAG_WORDS * sizeof(uint32_t)));
+    TENMO_CUDA_TRY(ctx, cudaMemset(ctx->p2p_buf, 0, bytes));
+    TENMO_CUDA_TRY(ctx, cudaMemset(ctx->p2p_flags, 0, P2P_FLAG_WORDS * sizeof(uint32_t)));
+    cudaIpcMemHandle_t hb, hf;
+    TENMO_CUDA_TRY(ctx, cudaIpcGetMemHandle(&hb, ctx->p2p_buf));
+    TENMO_CUDA_TRY(ctx, cudaIpcGetMemHandle(&hf, ctx->p2p_flags));
+    static_assert(2 * sizeof(cudaIpcMemHandle_t) == TENMO_DP_P2P_HANDLE_BYTES, "handle block size");
+    memcpy(handles_out, &hb, sizeof(hb));
+    memcpy(static_cast<char*>(handles_out) + sizeof(hb), &hf, sizeof(hf));
+    ctx->p2p_count = count;
+    *buf_out = static_cast<float*>(ctx->p2p_buf);
+    return TENMO_OK;
+}
+
+int tenmo_dp_p2p_connect(tenmo_ctx* ctx, int rank, int world, const void* all_handles, size_t handles_bytes) {
+    TENMO_CHECK_CTX(ctx);
+    if (!ctx->p2p_buf) return tenmo_set_error(ctx, TENMO_ERR_STATE, "dp_p2p_connect: call tenmo_dp_p2p_alloc first");
+    if (ctx->p2p_world) return tenmo_set_error(ctx, TENMO_ERR_STATE, "dp_p2p_connect: already connected");
+    if (world < 1 || world > P2P_MAX_WORLD || rank < 0 || rank >= world)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "dp_p2p_connect: rank %d / world %d (at most %d ranks)", rank, world,
+                               P2P_MAX_WORLD);
+    if (!all_handles || handles_bytes < (size_t)world * TENMO_DP_P2P_HANDLE_BYTES)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "dp_p2p_connect: need %d x %d handle bytes", world, TENMO_DP_P2P_HANDLE_BYTES);
+    TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    for (int p = 0; p < world; ++p) {
+        if (p == rank) {
+            ctx->p2p_peer_buf[p] = ctx->p2p_buf;
+            ctx->p2p_peer_flags[p] = ctx->p2p_flags;
+            continue;
+        }
+        cudaIpcMemHandle_t hb, hf;
+        const char* src = static_cast<const char*>(all_handles) + (size_t)p * TENMO_DP_P2P_HANDLE_BYTES;
+        memcpy(&hb, src, sizeof(hb));
+        memcpy(&hf, src + sizeof(hb), sizeof(hf));
+        TENMO_CUDA_TRY(ctx, cudaIpcOpenMemHandle(&ctx->p2p_peer_buf[p], hb, cudaIpcMemLazyEnablePeerAccess));
+        TENMO_CUDA_TRY(ctx, cudaIpcOpenMemHandle(&ctx->p2p_peer_flags[p], hf, cudaIpcMemLazyEnablePeerAccess));
+    }
+    ctx->p2p_rank = rank;
+    ctx->p2p_world = world;
+    ctx->p2p_epoch = 0;
+    return TENMO_OK;
+}
+
+int tenmo_dp_p2p_allreduce_sum_f32(tenmo_ctx* ctx, int64_t offset, int64_t count) {
+    TENMO_CHECK_CTX(ctx);
+    if (!ctx->p2p_world) return tenmo_set_error(ctx, TENMO_ERR_STATE, "dp_p2p_allreduce: call tenmo_dp_p2p_connect first");
+    if (offset < 0 || count < 0 || offset + count > ctx->p2p_count)
+        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "dp_p2p_allreduce: [%lld, %lld) outside the bucket of %lld floats",
+                               (long long)offset, (long long)(offset + count), (long long)ctx->p2p_count);
+    if (ctx->p2p_world == 1 || count == 0) return TENMO_OK;
+    TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    P2PArgs a;
+    for (int p = 0; p < P2P_MAX_WORLD; ++p) {
+        a.buf[p] = static_cast<float*>(ctx->p2p_peer_buf[p]);
+        a.flags[p] = static_cast<uint32_t*>(ctx->p2p_peer_flags[p]);
+    }
+    a.rank = ctx->p2p_rank; a.world = ctx->p2p_world;
+    a.off = offset; a.count = count;
+    a.epoch = ++ctx->p2p_epoch;  // every rank makes the same calls in the same order
+    a.status = ctx->dev_status;
+    dp_p2p_allreduce_kernel<<<P2P_CTAS, P2P_THREADS, 0, ctx->stream>>>(a);
+    TENMO_LAUNCH_CHECK(ctx, "dp_p2p_allreduce_kernel");
+    return TENMO_OK;
+}
+
+int tenmo_dp_p2p_close(tenmo_ctx* ctx) {
+    TENMO_CHECK_CTX(ctx);
+    if (!ctx->p2p_buf) return TENMO_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (int p = 0; p < ctx->p2p_world; ++p) {
+        if (p == ctx->p2p_rank) continue;
+        if (ctx->p2p_peer_buf[p]) cudaIpcCloseMemHandle(ctx->p2p_peer_buf[p]);
+        if (ctx->p2p_peer_flags[p]) cudaIpcCloseMemHandle(ctx->p2p_peer_flags[p]);
+    }
+    for (int p = 0; p < P2P_MAX_WORLD; ++p) ctx->p2p_peer_buf[p] = ctx->p2p_peer_flags[p] = nullptr;
+    cudaFree(ctx->p2p_buf);
+    cudaFree(ctx->p2p_flags);
+    ctx->p2p_buf = ctx->p2p_flags = nullptr;
+    ctx->p2p_world = 0;
+    ctx->p2p_count = 0;
+    cudaGetLastError();
+    return TENMO_OK;
+}
+
+}  // extern "C"

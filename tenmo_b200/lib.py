@@ -15,6 +15,7 @@ LIB_PATH = os.environ.get("TENMO_CUDA_PATH", os.path.join(_HERE, "libtenmo_cuda.
 
 MAX_BATCH_RANK = 6
 ALGO_AUTO, ALGO_SIMT_FP32, ALGO_TC_3XTF32 = -1, 0, 1
+DP_P2P_HANDLE_BYTES = 128
 ACT_NONE, ACT_RELU, ACT_SIGMOID = 0, 1, 2
 REDUCTION = {"mean": 0, "sum": 1, "none": 2}  # shared/__init__.mojo:4-40
 DP_ID_BYTES = 128
@@ -30,6 +31,7 @@ EXPORTS = [
     "tenmo_maxpool2d_bwd_f32",
     "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
     "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
+    "tenmo_dp_p2p_alloc", "tenmo_dp_p2p_connect", "tenmo_dp_p2p_allreduce_sum_f32", "tenmo_dp_p2p_close",
 ]
 
 
@@ -132,6 +134,10 @@ def _bind(lib):
         "tenmo_dp_init": (I, [P, I, I, P, C.c_size_t]),
         "tenmo_dp_allreduce_sum_f32": (I, [P, P, I64]),
         "tenmo_dp_finalize": (I, [P]),
+        "tenmo_dp_p2p_alloc": (I, [P, I64, C.POINTER(C.c_void_p), P, C.c_size_t]),
+        "tenmo_dp_p2p_connect": (I, [P, I, I, P, C.c_size_t]),
+        "tenmo_dp_p2p_allreduce_sum_f32": (I, [P, I64, I64]),
+        "tenmo_dp_p2p_close": (I, [P]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -342,3 +348,21 @@ class TenmoCuda:
 
     def dp_finalize(self):
         self._call("tenmo_dp_finalize")
+
+    # -- data parallel over peer memory (one kernel of this library instead of NCCL) --------------------
+    def dp_p2p_alloc(self, count: int):
+        """The gradient bucket (count floats, zeroed, owned by the library): (device pointer, IPC handle bytes)."""
+        ptr = C.c_void_p()
+        handles = C.create_string_buffer(DP_P2P_HANDLE_BYTES)
+        self._call("tenmo_dp_p2p_alloc", count, C.byref(ptr), handles, DP_P2P_HANDLE_BYTES)
+        return int(ptr.value), handles.raw
+
+    def dp_p2p_connect(self, rank: int, world: int, all_handles: bytes):
+        buf = C.create_string_buffer(all_handles, len(all_handles))
+        self._call("tenmo_dp_p2p_connect", rank, world, buf, len(all_handles))
+
+    def dp_p2p_allreduce_sum(self, offset: int, count: int):
+        self._call("tenmo_dp_p2p_allreduce_sum_f32", offset, count)
+
+    def dp_p2p_close(self):
+        self._call("tenmo_dp_p2p_close")

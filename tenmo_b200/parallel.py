@@ -51,6 +51,41 @@ def torch_broadcast_bytes(device=None):
     return bcast
 
 
+def torch_all_gather_bytes(device=None):
+    """An ``all_gather_bytes(data) -> [bytes per rank]`` built on the default torch.distributed process group (every
+    rank passes the same length)."""
+    import torch
+    import torch.distributed as dist
+
+    def gather(data: bytes):
+        mine = torch.tensor(list(data), dtype=torch.uint8, device=device)
+        out = [torch.empty_like(mine) for _ in range(dist.get_world_size())]
+        dist.all_gather(out, mine)
+        return [bytes(t.cpu().tolist()) for t in out]
+
+    return gather
+
+
+def connect_peer_buckets(handle, count: int, rank: int, world: int, all_gather_bytes):
+    """The peer-memory exchange's setup: allocate this rank's gradient bucket inside the library, share its CUDA IPC
+    handles with the other ranks through ``all_gather_bytes`` and map theirs.  Returns the device pointer of the
+    bucket (``count`` floats, zeroed)."""
+    ptr, handles = handle.dp_p2p_alloc(count)
+    blocks = all_gather_bytes(handles)
+    if len(blocks) != world or any(len(b) != len(handles) for b in blocks):
+        raise ValueError("all_gather_bytes must return one handle block per rank")
+    handle.dp_p2p_connect(rank, world, b"".join(blocks))
+    return ptr
+
+
+class DeviceFloats:
+    """Device memory owned by someone else, exposed through __cuda_array_interface__ so that torch.as_tensor wraps it
+    without a copy."""
+
+    def __init__(self, ptr: int, count: int):
+        self.__cuda_array_interface__ = {"shape": (int(count),), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
+
+
 def averaged_gradients(local_grads: np.ndarray, allreduce_sum, world: int) -> np.ndarray:
     """sum over ranks, then 1/world: what the fused SGD kernel applies through ``grad_scale``."""
     total = allreduce_sum(np.ascontiguousarray(local_grads, np.float32))

@@ -29,7 +29,9 @@ class MLPTrainer:
     def __init__(self, weights, biases, batch: int, lr: float = 0.01, momentum: float = 0.9, weight_decay: float = 0.0,
                  algo: str = "auto", handle: TenmoCuda | None = None, rank: int = 0, world: int = 1,
                  unique_id: bytes | None = None, device: int | None = None, overlap: bool = True,
-                 reserve_sms: int = 0):
+                 reserve_sms: int = 0, exchange: str = "nccl", all_gather_bytes=None):
+        """exchange: "nccl" (tenmo_dp_allreduce_sum_f32; needs unique_id) or "p2p" (the library's own kernel over NVLink
+        peer memory; needs all_gather_bytes(data) -> [bytes per rank] to share the IPC handles of the gradient bucket)."""
         self.dev = torch.cuda.current_device() if device is None else device
         self.h = handle or TenmoCuda(self.dev).require()
         self.algo = {"auto": _lib.ALGO_AUTO, "simt": _lib.ALGO_SIMT_FP32, "3xtf32": _lib.ALGO_TC_3XTF32}[algo]
@@ -47,8 +49,18 @@ class MLPTrainer:
                 sizes.append(n)
                 off += (n + 3) // 4 * 4
         self.numel = off
+        self.exchange = exchange if world > 1 else "none"
+        if self.exchange not in ("none", "nccl", "p2p"):
+            raise ValueError(f"unknown exchange {exchange!r}")
         self.P = torch.zeros(off, **f32)
-        self.G = torch.zeros(off, **f32)
+        if self.exchange == "p2p":
+            # the gradient bucket lives in memory the library allocated and every peer has mapped
+            from .parallel import DeviceFloats, connect_peer_buckets
+
+            ptr = connect_peer_buckets(self.h, off, rank, world, all_gather_bytes)
+            self.G = torch.as_tensor(DeviceFloats(ptr, off), device=f"cuda:{self.dev}")
+        else:
+            self.G = torch.zeros(off, **f32)
         self.V = torch.zeros(off, **f32)
         self.W = [self.P[offs[2 * l]:offs[2 * l] + sizes[2 * l]].view(self.dims[l], self.dims[l + 1]) for l in range(self.L)]
         self.b = [self.P[offs[2 * l + 1]:offs[2 * l + 1] + sizes[2 * l + 1]] for l in range(self.L)]
@@ -83,7 +95,7 @@ class MLPTrainer:
         self.overlap = overlap and world > 1
         self._side = torch.cuda.Stream(self.dev) if self.overlap else None
         self.reserve_sms = int(reserve_sms) if self.overlap else 0
-        if world > 1:
+        if self.exchange == "nccl":
             self.h.dp_init(rank, world, unique_id)
         if self.fused_lo:
             self.h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
@@ -132,6 +144,24 @@ class MLPTrainer:
         h.ce_fwd(self.act[L].data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
                  self.loss.data_ptr(), self.valid.data_ptr())
 
+    def _allreduce(self, start: int, count: int):
+        """Sum G[start, start + count) over the ranks on the library's current stream."""
+        if self.exchange == "p2p":
+            self.h.dp_p2p_allreduce_sum(start, count)
+        else:
+            self.h.dp_allreduce_sum(self.G.data_ptr() + 4 * start, count)
+
+    def close(self):
+        """Release the data-parallel resources (every rank, after a host barrier)."""
+        if self.exchange == "p2p":
+            torch.cuda.synchronize(self.dev)
+            self.G = None
+            self.dW = self.db = None
+            self.h.dp_p2p_close()
+        elif self.exchange == "nccl":
+            self.h.dp_finalize()
+        self.exchange = "none"
+
     def _exchange_layer(self, l: int):
         """Side stream: wait for layer l's gradients (and for the dX GEMM that still reads W[l]), sum them over
         the ranks, apply SGD to that layer's slice.  The main stream goes on with layer l-1 meanwhile."""
@@ -142,7 +172,7 @@ class MLPTrainer:
         start, count = self.layer_span[l]
         h = self.h
         h.set_stream(self._side.cuda_stream)
-        h.dp_allreduce_sum(self.G.data_ptr() + 4 * start, count)
+        self._allreduce(start, count)
         h.sgd_step([self.P.data_ptr() + 4 * start], [self.G.data_ptr() + 4 * start], [self.V.data_ptr() + 4 * start], [count],
                    self.lr, self.momentum, self.wd, 1.0 / self.world)
         if self.fused_lo:
@@ -179,7 +209,7 @@ class MLPTrainer:
     def _update(self):
         h = self.h
         if self.world > 1:
-            h.dp_allreduce_sum(self.G.data_ptr(), self.numel)
+            self._allreduce(0, self.numel)
         h.sgd_step([self.P.data_ptr()], [self.G.data_ptr()], [self.V.data_ptr()], [self.numel], self.lr, self.momentum,
                    self.wd, 1.0 / self.world)
         if self.fused_lo:

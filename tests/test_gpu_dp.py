@@ -1,4 +1,5 @@
-"""Data-parallel training over NCCL: two ranks on two GPUs equal one rank on the global batch.
+"""Data-parallel training, over NCCL and over the library's own peer-memory kernel: two ranks on two GPUs equal one
+rank on the global batch.
 
 Runs as child processes, one per GPU (skipped with fewer than two GPUs).  NVLS is switched off and every
 rank leaves only between steps, as this pool asks of multi-process GPU tests.
@@ -31,7 +32,7 @@ def _problem():
     return Ws, bs, X, y
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, exchange):
     import sys
 
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -40,18 +41,40 @@ def _worker(rank, world, port, out_dir):
     import torch.distributed as dist
 
     from tenmo_b200 import TenmoCuda
-    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_broadcast_bytes
+    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_all_gather_bytes, torch_broadcast_bytes
     from tenmo_b200.trainer import MLPTrainer
 
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         h = TenmoCuda(rank).require()
-        uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes())
+        uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes()) if exchange == "nccl" else None
         Ws, bs, X, y = _problem()
         lo, hi = shard_rows(128, rank, world)
         tr = MLPTrainer(Ws, bs, batch=hi - lo, lr=0.05, momentum=0.9, algo="simt", handle=h, rank=rank, world=world,
-                        unique_id=uid, device=rank)
+                        unique_id=uid, device=rank, exchange=exchange, all_gather_bytes=torch_all_gather_bytes())
+        if exchange == "p2p":
+            # the collective on its own: ragged ranges, every rank ends with the same bits = the sum in rank order
+            g = torch.Generator(device="cpu").manual_seed(5 + rank)
+            mine = torch.randn(tr.numel, generator=g)
+            for off, cnt in ((0, tr.numel), (4, 1001), (8, 3), (12, 0), (256, 4096)):
+                tr.G.copy_(mine)
+                torch.cuda.synchronize()
+                dist.barrier()
+                h.dp_p2p_allreduce_sum(off, cnt)
+                torch.cuda.synchronize()
+                h.check_device_status()
+                parts = [torch.randn(tr.numel, generator=torch.Generator(device="cpu").manual_seed(5 + r)) for r in range(world)]
+                want = mine.clone()
+                acc = parts[0][off:off + cnt].clone()
+                for r in range(1, world):
+                    acc += parts[r][off:off + cnt]
+                want[off:off + cnt] = acc
+                assert torch.equal(tr.G.cpu(), want), (off, cnt)
+                dist.barrier()
+            tr.G.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
         losses = []
         for s in range(4):
             tr.step(X[s, lo:hi], y[s, lo:hi])
@@ -61,19 +84,21 @@ def _worker(rank, world, port, out_dir):
         np.save(os.path.join(out_dir, f"w{rank}.npy"), np.concatenate([w.reshape(-1) for w in tr.weights() + tr.biases()]))
         np.save(os.path.join(out_dir, f"l{rank}.npy"), np.array(losses))
         dist.barrier()  # leave only between steps, with nothing in flight
-        h.dp_finalize()
+        tr.close()
+        dist.barrier()
     finally:
         dist.destroy_process_group()
 
 
-def test_two_ranks_equal_one_rank_on_the_global_batch(tmp_path):
+@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
+def test_two_ranks_equal_one_rank_on_the_global_batch(tmp_path, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
 
     from tenmo_b200.trainer import MLPTrainer
 
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), exchange), nprocs=2, join=True)
     Ws, bs, X, y = _problem()
     single = MLPTrainer(Ws, bs, batch=128, lr=0.05, momentum=0.9, algo="simt")
     losses = []
