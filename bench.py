@@ -247,16 +247,17 @@ def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen)
     import numpy as np
     import torch
 
-    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_broadcast_bytes
+    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_all_gather_bytes, torch_broadcast_bytes
     from tenmo_b200.trainer import MLPTrainer
 
     torch.cuda.nvtx.range_push("wide_mlp")
     dims, gb = [4096, 4096, 4096, 4096, 1000], 8192
     Ws, bs = uniform_init(dims, lambda i, o: np.sqrt(6.0 / i))  # "Kaiming-uniform": U(+-sqrt(6/in))
     lo, hi = shard_rows(gb, rank, world)
-    uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(torch.device("cuda", local_rank)))
+    dev = torch.device("cuda", local_rank)
+    uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(dev)) if args.dp_exchange == "nccl" else None
     tr = MLPTrainer(Ws, bs, batch=hi - lo, lr=0.01, momentum=0.9, algo="3xtf32", handle=h, rank=rank, world=world,
-                    unique_id=uid, device=local_rank)
+                    unique_id=uid, device=local_rank, exchange=args.dp_exchange, all_gather_bytes=torch_all_gather_bytes(dev))
     Xg = torch.randn(gb, dims[0], generator=gen)
     yg = torch.randint(0, dims[-1], (gb,), generator=gen)
     Xh, yh = Xg[lo:hi].contiguous().pin_memory(), yg[lo:hi].contiguous().pin_memory()
@@ -280,8 +281,14 @@ def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen)
         "e2e_value": gb * args.mlp_steps / (ms_e2e * 1e-3), "steps": args.mlp_steps,
         "config": "4096-4096-4096-4096-1000 Linear+ReLU, softmax-CE, fp32 (3xTF32 GEMMs), N(0,1) inputs, U(+-sqrt(6/in)) weights",
     }
+    res["exchange"] = tr.exchange
     if world > 1:
-        h.dp_finalize()
+        import torch.distributed as dist
+
+        torch.cuda.synchronize()
+        dist.barrier()
+        tr.close()
+        dist.barrier()
     del tr
     torch.cuda.empty_cache()
     torch.cuda.nvtx.range_pop()
@@ -679,6 +686,8 @@ def main():
     ap.add_argument("--no-mlp", action="store_true", help="skip the MLP training legs")
     ap.add_argument("--no-sweep", action="store_true", help="skip the smaller / skinny GEMM sizes of the same configuration")
     ap.add_argument("--mlp-steps", type=int, default=20)
+    ap.add_argument("--dp-exchange", choices=["nccl", "p2p"], default="p2p",
+                    help="gradient exchange of the wide-MLP leg at N > 1: NCCL all-reduce or the library's peer-memory kernel")
     ap.add_argument("--legs", default="wide_mlp,cnn,mnist_mlp", help="which training legs to run after the GEMM arm")
     ap.add_argument("--kernels", action="store_true",
                     help="time the bandwidth-bound kernels of the path against the HBM roofline (one JSON line each)")
