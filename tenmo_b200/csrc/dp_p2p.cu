@@ -3,7 +3,7 @@
 // Why not only NCCL: the exchange of a layer's gradients should run beside the backward GEMMs of the layers below,
 // but the persistent GEMM kernel holds every SM with one large CTA, and NCCL's CTAs (hundreds of threads, ~100
 // registers each) cannot share an SM with it, so they wait for GEMM CTAs to leave.  The kernel here is built to
-// co-reside: 64 CTAs of 512 threads, ~32 registers, no shared-memory tile.
+// co-reside: 64 CTAs of 512 threads, 64 registers, no shared-memory tile.
 //
 // Setup (one process per GPU): every rank allocates the gradient bucket and a small flag block with
 // tenmo_dp_p2p_alloc, the ranks exchange the two CUDA IPC handles out of band (the host's job, like NCCL's unique id),
@@ -93,11 +93,15 @@ __global__ void __launch_bounds__(P2P_THREADS) dp_p2p_allreduce_kernel(const P2P
             const int64_t j = c0 + 4 * t;
             if (j >= len) continue;
             if (vec && j + 3 < len) {
-                float4 acc = __ldcg(reinterpret_cast<const float4*>(a.buf[0] + base + j));
-                for (int p = 1; p < W; ++p) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + base + j));
-                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-                }
+                // all W loads are issued before the first add: one NVLink round trip per element, not W
+                float4 v[P2P_MAX_WORLD];
+#pragma unroll
+                for (int p = 0; p < P2P_MAX_WORLD; ++p)
+                    if (p < W) v[p] = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + base + j));
+                float4 acc = v[0];
+#pragma unroll
+                for (int p = 1; p < P2P_MAX_WORLD; ++p)
+                    if (p < W) { acc.x += v[p].x; acc.y += v[p].y; acc.z += v[p].z; acc.w += v[p].w; }
                 *reinterpret_cast<float4*>(a.buf[r] + base + j) = acc;
             } else {
                 for (int e = 0; e < 4 && j + e < len; ++e) {
@@ -111,16 +115,30 @@ __global__ void __launch_bounds__(P2P_THREADS) dp_p2p_allreduce_kernel(const P2P
 
     if (!p2p_barrier(a, 1, &ok_smem)) { if (t == 0) atomicOr(a.status, TENMO_DEV_TIMEOUT); return; }
 
-    for (int q = 1; q < W; ++q) {  // all-gather: the peers' reduced shards, starting with the next rank
-        const int p = (r + q) % W;
-        const int64_t base = a.off + (int64_t)p * sz, len = shard_len(p);
-        for (int64_t c0 = (int64_t)b * P2P_CHUNK; c0 < len; c0 += (int64_t)P2P_CTAS * P2P_CHUNK) {
-            const int64_t j = c0 + 4 * t;
-            if (j >= len) continue;
-            if (vec && j + 3 < len) {
-                *reinterpret_cast<float4*>(a.buf[r] + base + j) = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + base + j));
-            } else {
-                for (int e = 0; e < 4 && j + e < len; ++e) a.buf[r][base + j + e] = __ldcg(a.buf[p] + base + j + e);
+    // all-gather: the peers' reduced shards (the same chunk of every peer in one go, so that W-1 loads are in flight)
+    for (int64_t c0 = (int64_t)b * P2P_CHUNK; c0 < sz; c0 += (int64_t)P2P_CTAS * P2P_CHUNK) {
+        const int64_t j = c0 + 4 * t;
+        float4 v[P2P_MAX_WORLD];
+        bool full[P2P_MAX_WORLD];
+#pragma unroll
+        for (int q = 1; q < P2P_MAX_WORLD; ++q) {
+            full[q] = false;
+            if (q < W) {
+                const int p = (r + q) % W;  // start with the next rank: the ranks do not all read the same peer at once
+                full[q] = vec && j + 3 < shard_len(p);
+                if (full[q]) v[q] = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + a.off + (int64_t)p * sz + j));
+            }
+        }
+#pragma unroll
+        for (int q = 1; q < P2P_MAX_WORLD; ++q) {
+            if (q < W) {
+                const int p = (r + q) % W;
+                const int64_t base = a.off + (int64_t)p * sz, len = shard_len(p);
+                if (full[q]) {
+                    *reinterpret_cast<float4*>(a.buf[r] + base + j) = v[q];
+                } else {
+                    for (int e = 0; e < 4 && j + e < len; ++e) a.buf[r][base + j + e] = __ldcg(a.buf[p] + base + j + e);
+                }
             }
         }
     }

@@ -14,7 +14,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from tenmo_b200.parallel import averaged_gradients, exchange_unique_id, shard_rows, torch_broadcast_bytes
+from tenmo_b200.parallel import (DeviceFloats, averaged_gradients, connect_peer_buckets, exchange_unique_id, shard_rows,
+                                 torch_all_gather_bytes, torch_broadcast_bytes)
 
 
 def test_shard_rows():
@@ -48,6 +49,20 @@ def _worker(rank, world, port, out_dir):
         uid = exchange_unique_id(lambda: bytes(range(128)), rank, world, torch_broadcast_bytes())
         assert uid == bytes(range(128))
 
+        # (b') the peer-memory exchange's setup: every rank's handle block reaches every rank, rank-major
+        class FakeHandle:
+            def dp_p2p_alloc(self, count):
+                self.count = count
+                return 0x1000 * (rank + 1), bytes([rank]) * 128
+
+            def dp_p2p_connect(self, r, w, blob):
+                self.connected = (r, w, blob)
+
+        fake = FakeHandle()
+        ptr = connect_peer_buckets(fake, 77, rank, world, torch_all_gather_bytes())
+        assert ptr == 0x1000 * (rank + 1) and fake.count == 77
+        assert fake.connected == (rank, world, b"".join(bytes([r]) * 128 for r in range(world)))
+
         # (c) one data-parallel step == one global-batch step
         rng = np.random.default_rng(99)  # same stream on every rank: identical replicas and global batch
         dims = [40, 24, 12, 6]
@@ -80,3 +95,9 @@ def test_two_gloo_ranks_match_single_process(tmp_path):
     for r in range(world):
         err, scale = np.load(tmp_path / f"diff{r}.npy")
         assert err <= 1e-6 * max(1.0, scale), (err, scale)
+
+
+def test_device_floats_interface():
+    d = DeviceFloats(0xABC000, 12)
+    iface = d.__cuda_array_interface__
+    assert iface["shape"] == (12,) and iface["typestr"] == "<f4" and iface["data"] == (0xABC000, False)
