@@ -301,7 +301,7 @@ def measure_cnn(h, rank, world, local_rank, timed, args, rng, gen):
     import torch
 
     from tenmo_b200.cnn import CNNTrainer
-    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_broadcast_bytes
+    from tenmo_b200.parallel import exchange_unique_id, shard_rows, torch_all_gather_bytes, torch_broadcast_bytes
 
     torch.cuda.nvtx.range_push("cnn")
     gbc = 256
@@ -310,8 +310,10 @@ def measure_cnn(h, rank, world, local_rank, timed, args, rng, gen):
     cp = {"conv1.weight": he((32, 3, 3, 3), 27), "conv1.bias": np.zeros(32, np.float32),
           "conv2.weight": he((64, 32, 3, 3), 288), "conv2.bias": np.zeros(64, np.float32),
           "fc.weight": he((4096, 10), 4096), "fc.bias": np.zeros(10, np.float32)}
-    uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(torch.device("cuda", local_rank)))
-    cnn = CNNTrainer(cp, batch=hi - lo, handle=h, rank=rank, world=world, unique_id=uid, device=local_rank)
+    dev = torch.device("cuda", local_rank)
+    uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(dev)) if args.dp_exchange == "nccl" else None
+    cnn = CNNTrainer(cp, batch=hi - lo, handle=h, rank=rank, world=world, unique_id=uid, device=local_rank,
+                     exchange=args.dp_exchange, all_gather_bytes=torch_all_gather_bytes(dev))
     Xc = torch.rand(gbc, 3, 32, 32, generator=gen)[lo:hi].contiguous().pin_memory()
     yc = torch.randint(0, 10, (gbc,), generator=gen)[lo:hi].contiguous().pin_memory()
     cnn.load_batch(Xc, yc)
@@ -325,8 +327,14 @@ def measure_cnn(h, rank, world, local_rank, timed, args, rng, gen):
         "config": "(256,3,32,32) U[0,1): conv3x3 3->32 pad1, ReLU, maxpool2, conv3x3 32->64 pad1, ReLU, maxpool2, "
                   "Linear 4096->10, softmax-CE, SGD momentum 0.9; convolutions as im2col + strict-fp32 GEMM",
     }
+    res["exchange"] = cnn.exchange
     if world > 1:
-        h.dp_finalize()
+        import torch.distributed as dist
+
+        torch.cuda.synchronize()
+        dist.barrier()
+        cnn.close()
+        dist.barrier()
     del cnn
     torch.cuda.empty_cache()
     torch.cuda.nvtx.range_pop()
@@ -687,7 +695,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the smaller / skinny GEMM sizes of the same configuration")
     ap.add_argument("--mlp-steps", type=int, default=20)
     ap.add_argument("--dp-exchange", choices=["nccl", "p2p"], default="p2p",
-                    help="gradient exchange of the wide-MLP leg at N > 1: NCCL all-reduce or the library's peer-memory kernel")
+                    help="gradient exchange of the training legs at N > 1: NCCL all-reduce or the library's peer-memory kernel")
     ap.add_argument("--legs", default="wide_mlp,cnn,mnist_mlp", help="which training legs to run after the GEMM arm")
     ap.add_argument("--kernels", action="store_true",
                     help="time the bandwidth-bound kernels of the path against the HBM roofline (one JSON line each)")

@@ -97,7 +97,8 @@ class CNNTrainer:
 
     def __init__(self, params: dict, batch: int, hw: int = 32, lr: float = 0.01, momentum: float = 0.9,
                  handle: TenmoCuda | None = None, rank: int = 0, world: int = 1, unique_id: bytes | None = None,
-                 device: int | None = None):
+                 device: int | None = None, exchange: str = "nccl", all_gather_bytes=None):
+        """exchange: "nccl" (needs unique_id) or "p2p" (the library's peer-memory kernel; needs all_gather_bytes)."""
         self.dev = torch.cuda.current_device() if device is None else device
         self.h = handle or TenmoCuda(self.dev).require()
         self.rank, self.world, self.lr, self.momentum, self.batch = rank, world, float(lr), float(momentum), int(batch)
@@ -109,7 +110,15 @@ class CNNTrainer:
             offs.append(off)
             off += (int(np.prod(s)) + 3) // 4 * 4
         self.numel = off
-        self.P, self.G, self.V = (torch.zeros(off, **f32) for _ in range(3))
+        self.exchange = exchange if world > 1 else "none"
+        self.P, self.V = (torch.zeros(off, **f32) for _ in range(2))
+        if self.exchange == "p2p":
+            from .parallel import DeviceFloats, connect_peer_buckets
+
+            ptr = connect_peer_buckets(self.h, off, rank, world, all_gather_bytes)
+            self.G = torch.as_tensor(DeviceFloats(ptr, off), device=f"cuda:{self.dev}")
+        else:
+            self.G = torch.zeros(off, **f32)
         view = lambda buf, i: buf[offs[i]:offs[i] + int(np.prod(shapes[i]))].view(*shapes[i])
         self.p = {n: view(self.P, i) for i, n in enumerate(names)}
         self.g = {n: view(self.G, i) for i, n in enumerate(names)}
@@ -133,7 +142,7 @@ class CNNTrainer:
         self.loss = torch.zeros(1, **f32)
         self.valid = torch.zeros(1, dtype=torch.int32, device=f"cuda:{self.dev}")
         self.correct = torch.zeros(1, dtype=torch.int64, device=f"cuda:{self.dev}")
-        if world > 1:
+        if self.exchange == "nccl":
             self.h.dp_init(rank, world, unique_id)
         torch.cuda.synchronize(self.dev)
 
@@ -170,10 +179,23 @@ class CNNTrainer:
         d1 = self.pool1.backward(d1p)
         self.conv1.backward(d1, p["conv1.weight"], g["conv1.weight"], g["conv1.bias"])
         if update:
-            if self.world > 1:
+            if self.exchange == "p2p":
+                h.dp_p2p_allreduce_sum(0, self.numel)
+            elif self.exchange == "nccl":
                 h.dp_allreduce_sum(self.G.data_ptr(), self.numel)
             h.sgd_step([self.P.data_ptr()], [self.G.data_ptr()], [self.V.data_ptr()], [self.numel], self.lr, self.momentum,
                        0.0, 1.0 / self.world)
+
+    def close(self):
+        """Release the data-parallel resources (every rank, after a host barrier)."""
+        if self.exchange == "p2p":
+            torch.cuda.synchronize(self.dev)
+            self.G = None
+            self.g = None
+            self.h.dp_p2p_close()
+        elif self.exchange == "nccl":
+            self.h.dp_finalize()
+        self.exchange = "none"
 
     def loss_value(self) -> float:
         return float(self.loss.item())
