@@ -243,6 +243,37 @@ def measure_other_sizes(h, algo, timed):
     return res
 
 
+def build_with_fallback(build, exchange, uid, h, rank, world, dev):
+    """Build a trainer with the requested gradient exchange.  The peer-memory exchange needs CUDA IPC between the
+    ranks' processes; where that is refused, every rank falls back to the NCCL exchange together (both run on the GPU)."""
+    import torch
+    import torch.distributed as dist
+
+    from tenmo_b200 import TenmoError
+    from tenmo_b200.parallel import exchange_unique_id, torch_broadcast_bytes
+
+    if world == 1 or exchange == "nccl":
+        return build(exchange, uid)
+    tr, ok = None, 1
+    try:
+        tr = build("p2p", None)
+    except TenmoError as e:
+        ok = 0
+        print(f"rank {rank}: peer-memory exchange unavailable ({e}); using NCCL", file=sys.stderr, flush=True)
+    flag = torch.tensor([ok], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) == 1:
+        return tr
+    if tr is not None:
+        tr.close()
+    try:
+        h.dp_p2p_close()
+    except TenmoError:
+        pass
+    uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(dev))
+    return build("nccl", uid)
+
+
 def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen):
     import numpy as np
     import torch
@@ -256,8 +287,11 @@ def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen)
     lo, hi = shard_rows(gb, rank, world)
     dev = torch.device("cuda", local_rank)
     uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(dev)) if args.dp_exchange == "nccl" else None
-    tr = MLPTrainer(Ws, bs, batch=hi - lo, lr=0.01, momentum=0.9, algo="3xtf32", handle=h, rank=rank, world=world,
-                    unique_id=uid, device=local_rank, exchange=args.dp_exchange, all_gather_bytes=torch_all_gather_bytes(dev))
+    def build(exchange, unique_id):
+        return MLPTrainer(Ws, bs, batch=hi - lo, lr=0.01, momentum=0.9, algo="3xtf32", handle=h, rank=rank, world=world,
+                          unique_id=unique_id, device=local_rank, exchange=exchange, all_gather_bytes=torch_all_gather_bytes(dev))
+
+    tr = build_with_fallback(build, args.dp_exchange, uid, h, rank, world, dev)
     Xg = torch.randn(gb, dims[0], generator=gen)
     yg = torch.randint(0, dims[-1], (gb,), generator=gen)
     Xh, yh = Xg[lo:hi].contiguous().pin_memory(), yg[lo:hi].contiguous().pin_memory()
@@ -312,8 +346,11 @@ def measure_cnn(h, rank, world, local_rank, timed, args, rng, gen):
           "fc.weight": he((4096, 10), 4096), "fc.bias": np.zeros(10, np.float32)}
     dev = torch.device("cuda", local_rank)
     uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(dev)) if args.dp_exchange == "nccl" else None
-    cnn = CNNTrainer(cp, batch=hi - lo, handle=h, rank=rank, world=world, unique_id=uid, device=local_rank,
-                     exchange=args.dp_exchange, all_gather_bytes=torch_all_gather_bytes(dev))
+    def build(exchange, unique_id):
+        return CNNTrainer(cp, batch=hi - lo, handle=h, rank=rank, world=world, unique_id=unique_id, device=local_rank,
+                          exchange=exchange, all_gather_bytes=torch_all_gather_bytes(dev))
+
+    cnn = build_with_fallback(build, args.dp_exchange, uid, h, rank, world, dev)
     Xc = torch.rand(gbc, 3, 32, 32, generator=gen)[lo:hi].contiguous().pin_memory()
     yc = torch.randint(0, 10, (gbc,), generator=gen)[lo:hi].contiguous().pin_memory()
     cnn.load_batch(Xc, yc)
