@@ -247,6 +247,13 @@ int tenmo_ce_bwd_f32(tenmo_ctx* ctx, const float* softmax, const void* labels, i
  * p, g, v are HOST arrays of n_tensors device pointers (v may be NULL when momentum == 0). */
 int tenmo_sgd_step_f32(tenmo_ctx* ctx, int n_tensors, float* const* p, const float* const* g, float* const* v,
                        const int64_t* numel, float lr, float momentum, float weight_decay, float grad_scale);
+/* The same step that also leaves the 3xTF32 lo plane of the updated parameters: p_lo[t] (may be NULL per tensor)
+ * receives tf32_lo of the first lo_numel[t] updated elements of tensor t, in the same order (the layout of
+ * tenmo_split_lo_f32 for a matrix whose rows are a multiple of 4 long).  Saves the separate split pass over the
+ * weights after every update; the parameters come out bit-identical to tenmo_sgd_step_f32. */
+int tenmo_sgd_step_lo_f32(tenmo_ctx* ctx, int n_tensors, float* const* p, const float* const* g, float* const* v,
+                          const int64_t* numel, float* const* p_lo, const int64_t* lo_numel, float lr, float momentum,
+                          float weight_decay, float grad_scale);
 
 /* ---- accuracy -----------------------------------------------------------------------------------
  * Accuracy.compute (accuracy.mojo:7-85, kernels/accuracy_kernel.mojo:9-84): rows whose first-index

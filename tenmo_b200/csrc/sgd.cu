@@ -19,6 +19,8 @@ struct SgdBatch {
     const float* g[SGD_MAX_TENSORS];
     float* v[SGD_MAX_TENSORS];
     int64_t numel[SGD_MAX_TENSORS];
+    float* lo[SGD_MAX_TENSORS];         // optional: 3xTF32 lo plane of the updated parameters, first lo_numel elements
+    int64_t lo_numel[SGD_MAX_TENSORS];
     int64_t chunk_start[SGD_MAX_TENSORS + 1];  // prefix sum of chunks per tensor
     int n;
     float lr, momentum, wd, grad_scale;
@@ -46,6 +48,8 @@ __global__ void __launch_bounds__(SGD_THREADS) sgd_kernel(const SgdBatch b) {
         float* __restrict__ p = b.p[t];
         const float* __restrict__ g = b.g[t];
         float* __restrict__ v = b.v[t];
+        float* __restrict__ lo = b.lo[t];
+        const int64_t n_lo = lo ? b.lo_numel[t] : 0;
         const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
                            reinterpret_cast<uintptr_t>(v)) & 15u) == 0;
 #pragma unroll
@@ -62,12 +66,21 @@ __global__ void __launch_bounds__(SGD_THREADS) sgd_kernel(const SgdBatch b) {
                 sgd_one(pp.w, gg.w, vv.w, b, has_v);
                 *reinterpret_cast<float4*>(p + i) = pp;
                 if (has_v) *reinterpret_cast<float4*>(v + i) = vv;
+                if (i + 3 < n_lo) {
+                    *reinterpret_cast<float4*>(lo + i) =
+                        make_float4(tenmo_tf32_lo(pp.x), tenmo_tf32_lo(pp.y), tenmo_tf32_lo(pp.z), tenmo_tf32_lo(pp.w));
+                } else {
+                    const float e4[4] = {pp.x, pp.y, pp.z, pp.w};
+                    for (int q = 0; q < 4; ++q)
+                        if (i + q < n_lo) lo[i + q] = tenmo_tf32_lo(e4[q]);
+                }
             } else {
                 for (int q = 0; q < 4 && i + q < n; ++q) {
                     float pp = p[i + q], vv = has_v ? v[i + q] : 0.f;
                     sgd_one(pp, __ldg(g + i + q), vv, b, has_v);
                     p[i + q] = pp;
                     if (has_v) v[i + q] = vv;
+                    if (i + q < n_lo) lo[i + q] = tenmo_tf32_lo(pp);
                 }
             }
         }
@@ -76,9 +89,9 @@ __global__ void __launch_bounds__(SGD_THREADS) sgd_kernel(const SgdBatch b) {
 
 }  // namespace
 
-extern "C" int tenmo_sgd_step_f32(tenmo_ctx* ctx, int n_tensors, float* const* p, const float* const* g,
-                                  float* const* v, const int64_t* numel, float lr, float momentum,
-                                  float weight_decay, float grad_scale) {
+static int sgd_launch(tenmo_ctx* ctx, int n_tensors, float* const* p, const float* const* g, float* const* v,
+                      const int64_t* numel, float* const* p_lo, const int64_t* lo_numel, float lr, float momentum,
+                      float weight_decay, float grad_scale) {
     TENMO_CHECK_CTX(ctx);
     if (n_tensors < 0) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "sgd: negative tensor count");
     if (n_tensors == 0) return TENMO_OK;
@@ -99,6 +112,12 @@ extern "C" int tenmo_sgd_step_f32(tenmo_ctx* ctx, int n_tensors, float* const* p
                 if (!p[done] || !g[done] || (momentum > 0.f && !v[done]))
                     return tenmo_set_error(ctx, TENMO_ERR_INVALID, "sgd: tensor %d has a NULL pointer", done);
                 b.p[n] = p[done]; b.g[n] = g[done]; b.v[n] = momentum > 0.f ? v[done] : nullptr; b.numel[n] = ne;
+                if (p_lo && p_lo[done]) {
+                    if (!lo_numel || lo_numel[done] < 0 || lo_numel[done] > ne || (reinterpret_cast<uintptr_t>(p_lo[done]) & 15u))
+                        return tenmo_set_error(ctx, TENMO_ERR_INVALID, "sgd: tensor %d has a bad lo plane (0 <= lo_numel <= numel, 16-byte aligned)", done);
+                    b.lo[n] = p_lo[done];
+                    b.lo_numel[n] = lo_numel[done];
+                }
                 chunks += (ne + SGD_CHUNK - 1) / SGD_CHUNK;
                 b.chunk_start[++n] = chunks;
             }
@@ -112,4 +131,16 @@ extern "C" int tenmo_sgd_step_f32(tenmo_ctx* ctx, int n_tensors, float* const* p
         TENMO_LAUNCH_CHECK(ctx, "sgd_kernel");
     }
     return TENMO_OK;
+}
+
+extern "C" int tenmo_sgd_step_f32(tenmo_ctx* ctx, int n_tensors, float* const* p, const float* const* g,
+                                  float* const* v, const int64_t* numel, float lr, float momentum,
+                                  float weight_decay, float grad_scale) {
+    return sgd_launch(ctx, n_tensors, p, g, v, numel, nullptr, nullptr, lr, momentum, weight_decay, grad_scale);
+}
+
+extern "C" int tenmo_sgd_step_lo_f32(tenmo_ctx* ctx, int n_tensors, float* const* p, const float* const* g,
+                                     float* const* v, const int64_t* numel, float* const* p_lo, const int64_t* lo_numel,
+                                     float lr, float momentum, float weight_decay, float grad_scale) {
+    return sgd_launch(ctx, n_tensors, p, g, v, numel, p_lo, lo_numel, lr, momentum, weight_decay, grad_scale);
 }

@@ -29,7 +29,7 @@ EXPORTS = [
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
     "tenmo_conv_out_size", "tenmo_im2col_f32", "tenmo_col2im_f32", "tenmo_channel_sum_f32", "tenmo_maxpool2d_fwd_f32",
     "tenmo_maxpool2d_bwd_f32",
-    "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
+    "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_sgd_step_lo_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
     "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
     "tenmo_dp_p2p_alloc", "tenmo_dp_p2p_connect", "tenmo_dp_p2p_allreduce_sum_f32", "tenmo_dp_p2p_close",
 ]
@@ -129,6 +129,7 @@ def _bind(lib):
         "tenmo_ce_fwd_f32": (I, [P, P, I64, P, I, I64, I64, I64, F, I, P, P, P]),
         "tenmo_ce_bwd_f32": (I, [P, P, P, I, I64, I64, I64, F, I, P, P, P, F]),
         "tenmo_sgd_step_f32": (I, [P, I, P, P, P, P, F, F, F, F]),
+        "tenmo_sgd_step_lo_f32": (I, [P, I, P, P, P, P, P, P, F, F, F, F]),
         "tenmo_accuracy_f32": (I, [P, P, I64, P, I, I64, I64, P, P]),
         "tenmo_dp_get_unique_id": (I, [P, P, C.c_size_t]),
         "tenmo_dp_init": (I, [P, I, I, P, C.c_size_t]),
@@ -316,13 +317,19 @@ class TenmoCuda:
         self._call("tenmo_ce_bwd_f32", softmax, labels, 1 if label_is_i64 else 0, M, Cn, ignore_index,
                    label_smoothing, reduction, upstream or None, valid_count or None, dlogits, beta)
 
-    def sgd_step(self, p_ptrs, g_ptrs, v_ptrs, numels, lr, momentum=0.0, weight_decay=0.0, grad_scale=1.0):
+    def sgd_step(self, p_ptrs, g_ptrs, v_ptrs, numels, lr, momentum=0.0, weight_decay=0.0, grad_scale=1.0, lo_ptrs=None,
+                 lo_numels=None):
+        """lo_ptrs / lo_numels: optional per-tensor lo planes of the updated parameters (tenmo_sgd_step_lo_f32)."""
         n = len(p_ptrs)
         arr = lambda xs: (C.c_void_p * n)(*xs)
         pa, ga = arr(p_ptrs), arr(g_ptrs)
         va = arr(v_ptrs) if v_ptrs is not None else None
         na = (C.c_int64 * n)(*numels)
-        self._call("tenmo_sgd_step_f32", n, pa, ga, va, na, lr, momentum, weight_decay, grad_scale)
+        if lo_ptrs is None:
+            self._call("tenmo_sgd_step_f32", n, pa, ga, va, na, lr, momentum, weight_decay, grad_scale)
+        else:
+            la, ln = arr([x or None for x in lo_ptrs]), (C.c_int64 * n)(*lo_numels)
+            self._call("tenmo_sgd_step_lo_f32", n, pa, ga, va, na, la, ln, lr, momentum, weight_decay, grad_scale)
 
     def accuracy(self, logits, ld, labels, label_is_i64, M, Cn, correct_dev) -> int:
         host = C.c_int64(0)

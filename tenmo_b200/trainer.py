@@ -162,6 +162,25 @@ class MLPTrainer:
             self.h.dp_finalize()
         self.exchange = "none"
 
+    def _sgd_layers(self, layers):
+        """SGD on the flat slices of these layers (weight + bias each) in one launch.  On the 3xTF32 path the kernel
+        also writes the weights' lo planes (a weight row that is a multiple of 4 long has the plane's layout as it
+        stands; any other width is split separately)."""
+        h = self.h
+        spans = [self.layer_span[l] for l in layers]
+        ptr = lambda buf, s: buf.data_ptr() + 4 * s
+        kw = {}
+        if self.fused_lo:
+            fusable = [self.dims[l + 1] % 4 == 0 for l in layers]
+            kw = dict(lo_ptrs=[self.W_lo[l].data_ptr() if ok else 0 for l, ok in zip(layers, fusable)],
+                      lo_numels=[self.dims[l] * self.dims[l + 1] if ok else 0 for l, ok in zip(layers, fusable)])
+        h.sgd_step([ptr(self.P, s) for s, _ in spans], [ptr(self.G, s) for s, _ in spans], [ptr(self.V, s) for s, _ in spans],
+                   [c for _, c in spans], self.lr, self.momentum, self.wd, 1.0 / self.world, **kw)
+        if self.fused_lo:
+            for l, ok in zip(layers, fusable):
+                if not ok:
+                    self._split_weight(l)
+
     def _exchange_layer(self, l: int):
         """Side stream: wait for layer l's gradients (and for the dX GEMM that still reads W[l]), sum them over
         the ranks, apply SGD to that layer's slice.  The main stream goes on with layer l-1 meanwhile."""
@@ -173,10 +192,7 @@ class MLPTrainer:
         h = self.h
         h.set_stream(self._side.cuda_stream)
         self._allreduce(start, count)
-        h.sgd_step([self.P.data_ptr() + 4 * start], [self.G.data_ptr() + 4 * start], [self.V.data_ptr() + 4 * start], [count],
-                   self.lr, self.momentum, self.wd, 1.0 / self.world)
-        if self.fused_lo:
-            self._split_weight(l)
+        self._sgd_layers([l])
         h.set_stream(main.cuda_stream)
 
     def _backward(self, exchange: bool = False):
@@ -210,11 +226,7 @@ class MLPTrainer:
         h = self.h
         if self.world > 1:
             self._allreduce(0, self.numel)
-        h.sgd_step([self.P.data_ptr()], [self.G.data_ptr()], [self.V.data_ptr()], [self.numel], self.lr, self.momentum,
-                   self.wd, 1.0 / self.world)
-        if self.fused_lo:
-            for l in range(self.L):
-                self._split_weight(l)
+        self._sgd_layers(list(range(self.L)))
 
     # ------------------------------------------------------------------------------------------------
     def load_batch(self, X, y):

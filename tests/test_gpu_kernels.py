@@ -374,6 +374,34 @@ def test_sgd_multi_tensor_bit_exact(g, oracle):
         assert np.array_equal(g.host(pd), p) and np.array_equal(g.host(vd), v)
 
 
+def test_sgd_with_lo_planes_matches_update_then_split(g, oracle):
+    """tenmo_sgd_step_lo_f32: the parameters come out as from tenmo_sgd_step_f32, and the lo plane written along is what
+    tenmo_split_lo_f32 gives for the updated weights (only the first lo_numel elements, nothing beyond)."""
+    from tenmo_b200 import make_mat
+
+    h = g.handle()
+    rng = np.random.default_rng(8)
+    shapes = [(96, 64), (33, 20), (5, 4)]          # (rows, cols) of the weight part; a bias of `cols` follows it
+    sizes = [r * c + (c + 3) // 4 * 4 for r, c in shapes]
+    P = [rng.standard_normal(n).astype(np.float32) for n in sizes]
+    G = [rng.standard_normal(n).astype(np.float32) for n in sizes]
+    Pd, Gd, Vd = [g.dev(x) for x in P], [g.dev(x) for x in G], [g.dev(np.zeros(n, np.float32)) for n in sizes]
+    Pd2, Vd2 = [g.dev(x) for x in P], [g.dev(np.zeros(n, np.float32)) for n in sizes]
+    lo = [torch.full((r * c + 8,), 7.0, device="cuda") for r, c in shapes]
+    for _ in range(2):
+        h.sgd_step([t.data_ptr() for t in Pd], [t.data_ptr() for t in Gd], [t.data_ptr() for t in Vd], sizes, 0.05, 0.9, 1e-3, 0.5,
+                   lo_ptrs=[t.data_ptr() for t in lo], lo_numels=[r * c for r, c in shapes])
+        h.sgd_step([t.data_ptr() for t in Pd2], [t.data_ptr() for t in Gd], [t.data_ptr() for t in Vd2], sizes, 0.05, 0.9, 1e-3, 0.5)
+    torch.cuda.synchronize()
+    for (r, c), pd, pd2, l in zip(shapes, Pd, Pd2, lo):
+        assert torch.equal(pd, pd2)
+        want = g.empty(r * c)
+        h.split_lo(make_mat(pd.data_ptr(), (r, c), (c, 1)), r, c, want.data_ptr(), r * c)
+        torch.cuda.synchronize()
+        assert torch.equal(l[:r * c], want) and bool((l[r * c:] == 7.0).all())
+    h.check_device_status()
+
+
 @pytest.mark.parametrize("case", kat.ACCURACY, ids=lambda c: str(c["correct"]))
 def test_accuracy_literals(g, case):
     h = g.handle()
