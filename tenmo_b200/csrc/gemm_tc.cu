@@ -13,7 +13,7 @@
 //   warp 1   MMA issuer     one elected thread issues 4 k-steps x 3 products of 128 x BN x 8 per stage,
 //                           tcgen05.commit releases the stage and, at the end of a tile, publishes the
 //                           accumulator; also owns the TMEM allocation (2 accumulators, double buffered)
-//   warps 2-5 epilogue      tcgen05.ld the accumulator (one TMEM lane = one row per thread), add bias,
+//   warps 2-9 epilogue      tcgen05.ld the accumulator (one TMEM lane = one row per thread), add bias,
 //                           activation / ReLU mask / beta accumulate, store to C
 // Operand layouts.  "K-major" = the contraction index is the unit-stride axis (row-major A, or B given
 // as a transposed view); "MN-major" = the other axis is (A given as a transposed view, row-major B).
@@ -31,7 +31,8 @@
 
 namespace {
 
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;                // producer warp, MMA warp, eight epilogue warps
+constexpr int EPI_WARPS = 8;
 constexpr int BM = 128;
 #ifndef TENMO_TC_BK
 #define TENMO_TC_BK 32
@@ -42,7 +43,8 @@ constexpr int UMMA_K = 8;                    // tf32 k per instruction
 constexpr int SQ = 4;                        // depth of the tile-id ring between the scheduler and its consumers
 constexpr int TILE_COUNTERS = 32;            // ring of global tile counters, one per GEMM launch in flight
 
-constexpr int EP_LD = 36;  // floats per row of an epilogue warp's 32 x 32 staging block (144 B: conflict-free both ways)
+constexpr int EP_LD = 32;  // floats per row of an epilogue warp's 32 x 32 staging block; 16-byte chunk q of row r sits at
+                           // chunk q ^ (r & 7), which keeps the row-wise writes and the 4-rows-at-a-time reads conflict-free
 
 template <int BN>
 struct TcCfg {
@@ -50,7 +52,7 @@ struct TcCfg {
     static constexpr int B_TILE = BN * BK * 4;
     static constexpr int STAGE = 2 * A_TILE + 2 * B_TILE;
     static constexpr int STAGES = ((BN == 256) ? 2 : (BN == 128 ? 3 : 4)) * (32 / BK);
-    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * 32 * EP_LD * 4 /*epilogue staging*/;
+    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_WARPS * 32 * EP_LD * 4 /*epilogue staging*/;
     static constexpr int TMEM_COLS = 2 * BN;     // two accumulators
 };
 
@@ -168,8 +170,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
-        for (int q = 0; q < SQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 5); }  // MMA thread + 4 epilogue warps
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI_WARPS); }
+        for (int q = 0; q < SQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 1 + EPI_WARPS); }  // MMA thread + the epilogue warps
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -312,9 +314,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else {
-        // ------------------------------- epilogue (warps 2..5) -------------------------------
+        // ------------------------------- epilogue (warps 2..9) -------------------------------
+        // Two warps per TMEM lane quarter: warp w and w + 4 take the even and the odd 32-column blocks of their 32 rows.
+        // The epilogue of a short-k tile is a chain of dependent instructions per warp; with one warp per scheduler
+        // nothing hides their latency, with two the drain of a tile takes half as long.
         const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warp%4), +32)
-        float* ebuf = reinterpret_cast<float*>(smem_gen + Cfg::STAGES * Cfg::STAGE + 256) + quarter * (32 * EP_LD);
+        float* ebuf = reinterpret_cast<float*>(smem_gen + Cfg::STAGES * Cfg::STAGE + 256) + (warp - 2) * (32 * EP_LD);
+        const int half = (warp - 2) >> 2;
         uint32_t acc_phase[2] = {0, 0};
         int acc = 0;
         bool ok = true;
@@ -350,8 +356,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int64_t n_base = (int64_t)tn * BN;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             const int col4 = (lane & 7) * 4, row_sub = lane >> 3;
+            const bool plain = !p.bias && !p.bias_m && p.act == TENMO_ACT_NONE && !p.aux && !p.mul_mask && !p.c_lo &&
+                               p.beta == 0.f && p.c_vec;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = half; c < BN / 32; c += 2) {
                 const int64_t n0 = n_base + c * 32;
                 if (n0 >= p.N) break;  // uniform: the rest of the tile lies outside the matrix
                 uint32_t r[32];
@@ -359,11 +367,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld_wait();
 #pragma unroll
                 for (int q = 0; q < 32; q += 4)
-                    *reinterpret_cast<float4*>(ebuf + lane * EP_LD + q) =
+                    *reinterpret_cast<float4*>(ebuf + lane * EP_LD + ((((q >> 2) ^ (lane & 7))) << 2)) =
                         make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]), __uint_as_float(r[q + 2]),
                                     __uint_as_float(r[q + 3]));
                 __syncwarp();
                 const int64_t n = n0 + col4;
+                if (plain) {
+                    // no epilogue options: the block goes out as it is (a handful of instructions per 16 bytes; the
+                    // general path below spends ~25 per element on option checks with one warp per scheduler)
+                    float* dst = p.C + (batch * p.M + m_warp + row_sub) * p.N + n;
+                    const int64_t step = 4 * p.N;
+                    if (n < p.N) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rl = 4 * i + row_sub;
+                            const float4 x4 = *reinterpret_cast<const float4*>(ebuf + rl * EP_LD + ((((lane & 7) ^ (rl & 7))) << 2));
+                            if (m_warp + 4 * i + row_sub < p.M) *reinterpret_cast<float4*>(dst + i * step) = x4;
+                        }
+                    }
+                    __syncwarp();
+                    continue;
+                }
                 float cb[4] = {0.f, 0.f, 0.f, 0.f};
                 if (p.bias) {
 #pragma unroll
@@ -374,7 +398,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int i = 0; i < 8; ++i) {
                     const int row_l = 4 * i + row_sub;
                     const int64_t m = m_warp + row_l;
-                    const float4 x4 = *reinterpret_cast<const float4*>(ebuf + row_l * EP_LD + col4);
+                    const float4 x4 = *reinterpret_cast<const float4*>(ebuf + row_l * EP_LD + ((((lane & 7) ^ (row_l & 7))) << 2));
                     if (m >= p.M || n >= p.N) continue;
                     const float row_bias = p.bias_m ? __ldg(p.bias_m + m) : 0.f;
                     const int64_t row_off = (batch * p.M + m) * p.N;
