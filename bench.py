@@ -731,12 +731,15 @@ def main():
     ap.add_argument("--no-mlp", action="store_true", help="skip the MLP training legs")
     ap.add_argument("--no-sweep", action="store_true", help="skip the smaller / skinny GEMM sizes of the same configuration")
     ap.add_argument("--mlp-steps", type=int, default=20)
-    ap.add_argument("--dp-exchange", choices=["nccl", "p2p"], default="p2p",
-                    help="gradient exchange of the training legs at N > 1: NCCL all-reduce or the library's peer-memory kernel")
+    ap.add_argument("--dp-exchange", choices=["auto", "nccl", "p2p"], default="auto",
+                    help="gradient exchange of the training legs at N > 1: NCCL all-reduce or the library's peer-memory kernel; "
+                         "auto = peer-memory from 4 ranks up (measured: 17 %% faster at 8 ranks, 3 %% slower at 2)")
     ap.add_argument("--legs", default="wide_mlp,cnn,mnist_mlp", help="which training legs to run after the GEMM arm")
     ap.add_argument("--kernels", action="store_true",
                     help="time the bandwidth-bound kernels of the path against the HBM roofline (one JSON line each)")
     args = ap.parse_args()
+    if args.dp_exchange == "auto":
+        args.dp_exchange = "p2p" if int(os.environ.get("WORLD_SIZE", "1")) >= 4 else "nccl"
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.kernels:
