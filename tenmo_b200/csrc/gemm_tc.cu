@@ -7,7 +7,7 @@
 // a_lo*b_lo term is below 2^-20 relative.  The lo planes are produced by a bandwidth-bound split
 // kernel into the context workspace (one read + one write per operand element).
 //
-// Kernel.  Persistent, one CTA per SM, 192 threads, warp-specialised:
+// Kernel.  Persistent, one CTA per SM, 320 threads, warp-specialised:
 //   warp 0   TMA producer   cp.async.bulk.tensor (no multicast) of the A, A_lo, B, B_lo tiles of a
 //                           k-block into a ring of shared-memory stages, 128-byte swizzle
 //   warp 1   MMA issuer     one elected thread issues 4 k-steps x 3 products of 128 x BN x 8 per stage,
@@ -349,7 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tcgen05_fence_after();
             // A thread's tcgen05.ld delivers 32 consecutive columns of ONE row, so storing straight from those
             // registers would make every warp-wide store touch 32 rows, 16 bytes each.  The 32 x 32 block goes through a
-            // per-warp shared-memory buffer instead (rows padded to 36 floats: conflict-free both ways) and comes back
+            // per-warp shared-memory buffer instead (16-byte chunks XOR-swizzled by row: conflict-free both ways) and comes back
             // as (row = 4i + lane/8, columns 4*(lane%8)..+3): a warp-wide access then covers four full 128-byte row
             // segments, for the result as for the mask, the old C, the ReLU mask and the lo plane.
             const int64_t m_warp = (int64_t)tm * BM + quarter * 32;
