@@ -356,6 +356,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int64_t n_base = (int64_t)tn * BN;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             const int col4 = (lane & 7) * 4, row_sub = lane >> 3;
+            // element offsets of row (m_warp + row_sub); the other seven rows of a lane lie 4 rows further each
+            const int64_t row_off0 = (batch * p.M + m_warp + row_sub) * p.N;
+            const int64_t clo_off0 = (batch * p.M + m_warp + row_sub) * p.ld_clo;
             const bool plain = !p.bias && !p.bias_m && p.act == TENMO_ACT_NONE && !p.aux && !p.mul_mask && !p.c_lo &&
                                p.beta == 0.f && p.c_vec;
 #pragma unroll 1
@@ -375,7 +378,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (plain) {
                     // no epilogue options: the block goes out as it is (a handful of instructions per 16 bytes; the
                     // general path below spends ~25 per element on option checks with one warp per scheduler)
-                    float* dst = p.C + (batch * p.M + m_warp + row_sub) * p.N + n;
+                    float* dst = p.C + row_off0 + n;
                     const int64_t step = 4 * p.N;
                     if (n < p.N) {
 #pragma unroll
@@ -401,7 +404,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const float4 x4 = *reinterpret_cast<const float4*>(ebuf + row_l * EP_LD + ((((lane & 7) ^ (row_l & 7))) << 2));
                     if (m >= p.M || n >= p.N) continue;
                     const float row_bias = p.bias_m ? __ldg(p.bias_m + m) : 0.f;
-                    const int64_t row_off = (batch * p.M + m) * p.N;
+                    const int64_t row_off = row_off0 + (int64_t)(4 * i) * p.N;
                     float* crow = p.C + row_off;
                     const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
                     float v[4], mk[4];
@@ -424,7 +427,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         *reinterpret_cast<float4*>(crow + n) = o;
                         if (p.aux) *reinterpret_cast<float4*>(p.aux + row_off + n) = make_float4(mk[0], mk[1], mk[2], mk[3]);
                         if (p.c_lo)
-                            *reinterpret_cast<float4*>(p.c_lo + (batch * p.M + m) * p.ld_clo + n) =
+                            *reinterpret_cast<float4*>(p.c_lo + clo_off0 + (int64_t)(4 * i) * p.ld_clo + n) =
                                 make_float4(tenmo_tf32_lo(o.x), tenmo_tf32_lo(o.y), tenmo_tf32_lo(o.z), tenmo_tf32_lo(o.w));
                     } else {
 #pragma unroll
@@ -435,7 +438,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 if (p.beta != 0.f) o += crow[n + e];
                                 crow[n + e] = o;
                                 if (p.aux) p.aux[row_off + n + e] = mk[e];
-                                if (p.c_lo) p.c_lo[(batch * p.M + m) * p.ld_clo + n + e] = tenmo_tf32_lo(o);
+                                if (p.c_lo) p.c_lo[clo_off0 + (int64_t)(4 * i) * p.ld_clo + n + e] = tenmo_tf32_lo(o);
                             }
                     }
                 }
