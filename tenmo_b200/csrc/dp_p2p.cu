@@ -158,13 +158,20 @@ int tenmo_dp_p2p_alloc(tenmo_ctx* ctx, int64_t count, float** buf_out, void* han
     if (ctx->p2p_buf) return tenmo_set_error(ctx, TENMO_ERR_STATE, "dp_p2p_alloc: already allocated");
     TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     const size_t bytes = (((size_t)count * sizeof(float)) + 255) & ~(size_t)255;
-    TENMO_CUDA_TRY(ctx, cudaMalloc(&ctx->p2p_buf, bytes));
-    TENMO_CUDA_TRY(ctx, cudaMalloc(&ctx->p2p_flags, P2P_FLAG_WORDS * sizeof(uint32_t)));
-    TENMO_CUDA_TRY(ctx, cudaMemset(ctx->p2p_buf, 0, bytes));
-    TENMO_CUDA_TRY(ctx, cudaMemset(ctx->p2p_flags, 0, P2P_FLAG_WORDS * sizeof(uint32_t)));
     cudaIpcMemHandle_t hb, hf;
-    TENMO_CUDA_TRY(ctx, cudaIpcGetMemHandle(&hb, ctx->p2p_buf));
-    TENMO_CUDA_TRY(ctx, cudaIpcGetMemHandle(&hf, ctx->p2p_flags));
+    cudaError_t e = cudaMalloc(&ctx->p2p_buf, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->p2p_flags, P2P_FLAG_WORDS * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->p2p_buf, 0, bytes);
+    if (e == cudaSuccess) e = cudaMemset(ctx->p2p_flags, 0, P2P_FLAG_WORDS * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&hb, ctx->p2p_buf);
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&hf, ctx->p2p_flags);
+    if (e != cudaSuccess) {  // nothing half-allocated is left behind
+        if (ctx->p2p_buf) cudaFree(ctx->p2p_buf);
+        if (ctx->p2p_flags) cudaFree(ctx->p2p_flags);
+        ctx->p2p_buf = ctx->p2p_flags = nullptr;
+        cudaGetLastError();
+        return tenmo_set_error(ctx, TENMO_ERR_CUDA, "dp_p2p_alloc: %s", cudaGetErrorString(e));
+    }
     static_assert(2 * sizeof(cudaIpcMemHandle_t) == TENMO_DP_P2P_HANDLE_BYTES, "handle block size");
     memcpy(handles_out, &hb, sizeof(hb));
     memcpy(static_cast<char*>(handles_out) + sizeof(hb), &hf, sizeof(hf));
@@ -193,8 +200,18 @@ int tenmo_dp_p2p_connect(tenmo_ctx* ctx, int rank, int world, const void* all_ha
         const char* src = static_cast<const char*>(all_handles) + (size_t)p * TENMO_DP_P2P_HANDLE_BYTES;
         memcpy(&hb, src, sizeof(hb));
         memcpy(&hf, src + sizeof(hb), sizeof(hf));
-        TENMO_CUDA_TRY(ctx, cudaIpcOpenMemHandle(&ctx->p2p_peer_buf[p], hb, cudaIpcMemLazyEnablePeerAccess));
-        TENMO_CUDA_TRY(ctx, cudaIpcOpenMemHandle(&ctx->p2p_peer_flags[p], hf, cudaIpcMemLazyEnablePeerAccess));
+        cudaError_t e = cudaIpcOpenMemHandle(&ctx->p2p_peer_buf[p], hb, cudaIpcMemLazyEnablePeerAccess);
+        if (e == cudaSuccess) e = cudaIpcOpenMemHandle(&ctx->p2p_peer_flags[p], hf, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {  // unmap what was mapped so far; the bucket itself stays allocated
+            for (int q = 0; q <= p; ++q) {
+                if (q == rank) continue;
+                if (ctx->p2p_peer_buf[q]) cudaIpcCloseMemHandle(ctx->p2p_peer_buf[q]);
+                if (ctx->p2p_peer_flags[q]) cudaIpcCloseMemHandle(ctx->p2p_peer_flags[q]);
+            }
+            for (int q = 0; q < P2P_MAX_WORLD; ++q) ctx->p2p_peer_buf[q] = ctx->p2p_peer_flags[q] = nullptr;
+            cudaGetLastError();
+            return tenmo_set_error(ctx, TENMO_ERR_CUDA, "dp_p2p_connect: cannot map rank %d's bucket: %s", p, cudaGetErrorString(e));
+        }
     }
     ctx->p2p_rank = rank;
     ctx->p2p_world = world;
