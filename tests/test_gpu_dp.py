@@ -112,3 +112,27 @@ def test_two_ranks_equal_one_rank_on_the_global_batch(tmp_path, exchange):
     assert np.max(np.abs(w0 - ref)) <= 1e-5 * np.max(np.abs(ref))
     l0, l1 = np.load(tmp_path / "l0.npy"), np.load(tmp_path / "l1.npy")
     assert np.allclose((l0 + l1) / 2, losses, rtol=1e-5, atol=1e-6)  # mean of rank means == global mean
+
+
+def test_p2p_single_rank_and_argument_errors():
+    """The peer-memory exchange's entry points on one GPU: state and range errors, world = 1 as a no-op."""
+    from tenmo_b200 import TenmoCuda, TenmoError
+
+    h = TenmoCuda(0).require()
+    with pytest.raises(TenmoError):
+        h.dp_p2p_allreduce_sum(0, 10)          # nothing allocated or connected
+    ptr, handles = h.dp_p2p_alloc(1000)
+    assert ptr != 0 and len(handles) == 128
+    with pytest.raises(TenmoError):
+        h.dp_p2p_alloc(10)                     # one bucket per context
+    with pytest.raises(TenmoError):
+        h.dp_p2p_connect(0, 9, handles * 9)    # at most 8 ranks
+    with pytest.raises(TenmoError):
+        h.dp_p2p_connect(1, 1, handles)        # rank outside the world
+    h.dp_p2p_connect(0, 1, handles)
+    h.dp_p2p_allreduce_sum(0, 1000)            # a single rank: nothing to exchange
+    with pytest.raises(TenmoError):
+        h.dp_p2p_allreduce_sum(900, 200)       # range outside the bucket
+    h.check_device_status()
+    h.dp_p2p_close()
+    h.dp_p2p_close()                           # closing twice is harmless
