@@ -152,6 +152,12 @@ int tenmo_gemm_last_algo(tenmo_ctx* ctx);
  * or "gemm_simt_kernel" (strict fp32, register-staged: any strides); "" before the first call.  No reference
  * counterpart; tests and benchmarks use it to state which path was measured. */
 const char* tenmo_gemm_last_kernel(tenmo_ctx* ctx);
+/* Pieces of the stream-K tail of that launch: when the tiles of a tensor-core GEMM do not fill the last wave of CTAs,
+ * the k-range of the last tiles is cut into this many equal pieces (one per CTA) and the partial accumulators are
+ * added in ascending k by the piece that holds a tile's end; 0 = every tile was computed whole (always 0 for the
+ * strict-fp32 kernels, whose results must not depend on the machine).  TENMO_TC_STREAMK=0 in the environment turns
+ * it off.  No reference counterpart. */
+int tenmo_gemm_last_stream_k(tenmo_ctx* ctx);
 
 /* ---- elementwise neighbours of the GEMM (un-fused forms, for a host that calls op by op) ---------- */
 /* out[m,n] = x[m,n] + bias[n]; Adder.forward bias case (addition.mojo:71-112,

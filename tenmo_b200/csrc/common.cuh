@@ -14,6 +14,12 @@
 #define TENMO_DEV_TIMEOUT 1u    // a bounded mbarrier / flag wait ran out of iterations
 #define TENMO_DEV_BAD_LABEL 2u  // cross-entropy saw a label outside [0, C) that is not ignore_index
 
+// Layout of the small device scratch block (32-bit words): [0] status, [8] cross-entropy ticket, [64..127] tile counter
+// pairs of the tensor-core GEMM, [256..511] fix-up flags of its stream-K tail (one per piece).
+#define TENMO_DEV_STATUS_WORDS 512
+#define TENMO_SK_FLAG_WORD0 256
+#define TENMO_SK_MAX_UNITS 256
+
 struct tenmo_ctx {
     int device = 0;
     int sm_count = 0;
@@ -26,6 +32,7 @@ struct tenmo_ctx {
     int64_t launches = 0;
     int last_gemm_algo = -1;
     const char* last_gemm_kernel = "";
+    int last_gemm_sk_units = 0;
     // workspace (grown on demand, never shrunk): lo planes for the 3xTF32 kernel, reduction partials
     void* ws = nullptr;
     size_t ws_bytes = 0;

@@ -107,9 +107,8 @@ int tenmo_cuda_init(int device, tenmo_ctx** out) {
     cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device);
     ctx->sm_clock_khz = khz;
     e = cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking);
-    // 256 words: [0] status, [8] cross-entropy ticket, [64..127] tile counter pairs of the tensor-core GEMM
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->dev_status, 256 * sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, 256 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->dev_status, TENMO_DEV_STATUS_WORDS * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, TENMO_DEV_STATUS_WORDS * sizeof(uint32_t));
     if (e != cudaSuccess) {
         tenmo_set_error(nullptr, TENMO_ERR_CUDA, "context set-up: %s", cudaGetErrorString(e));
         tenmo_cuda_destroy(ctx);
@@ -177,7 +176,7 @@ int tenmo_cuda_check_device_status(tenmo_ctx* ctx) {
     TENMO_CUDA_TRY(ctx, cudaMemcpy(&word, ctx->dev_status, sizeof(word), cudaMemcpyDeviceToHost));
     if (word) {
         // an abandoned kernel may have left its tickets and tile counters dirty: clear the whole block
-        TENMO_CUDA_TRY(ctx, cudaMemset(ctx->dev_status, 0, 256 * sizeof(uint32_t)));
+        TENMO_CUDA_TRY(ctx, cudaMemset(ctx->dev_status, 0, TENMO_DEV_STATUS_WORDS * sizeof(uint32_t)));
         if (word & TENMO_DEV_TIMEOUT)
             return tenmo_set_error(ctx, TENMO_ERR_TIMEOUT, "a device-side bounded wait gave up (status 0x%x)", word);
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "device status 0x%x: label outside [0,C) seen by cross-entropy",

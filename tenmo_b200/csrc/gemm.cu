@@ -88,6 +88,7 @@ static int tc_split_k(tenmo_ctx* ctx, const TenmoGemmParams& p, const tenmo_gemm
 
 int tenmo_gemm_last_algo(tenmo_ctx* ctx) { return ctx ? ctx->last_gemm_algo : -1; }
 const char* tenmo_gemm_last_kernel(tenmo_ctx* ctx) { return ctx ? ctx->last_gemm_kernel : ""; }
+int tenmo_gemm_last_stream_k(tenmo_ctx* ctx) { return ctx ? ctx->last_gemm_sk_units : 0; }
 
 int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, const tenmo_mat* A, const tenmo_mat* B,
                       float* C, const tenmo_gemm_opts* o) {

@@ -395,6 +395,7 @@ int tenmo_gemm_simt_tma_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     tenmo_prof_after(ctx);
     ctx->launches++;
     ctx->last_gemm_kernel = "gemm_simt_tma_kernel";
+    ctx->last_gemm_sk_units = 0;
     if (e != cudaSuccess)
         return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_simt_tma_kernel failed: %s", cudaGetErrorString(e));
     return TENMO_OK;

@@ -73,7 +73,19 @@ struct TcParams {
     int c_vec;
     uint32_t* status;
     unsigned int* tile_counter;  // zero at launch; hands out tiles gridDim.x, gridDim.x + 1, ...
+    // stream-K tail (sk_units == 0: off).  Tiles [0, dp_tiles) are worked whole; the k-blocks of the tiles
+    // [dp_tiles, tiles) form one linear range that is cut into sk_units equal pieces.
+    int sk_units;
+    int64_t dp_tiles;
+    float* sk_partials;          // sk_units slots of BM x BN floats
+    unsigned int* sk_flags;      // sk_units words, zero between launches: epilogue warps that have stored their part of slot u
 };
+
+// What travels from the scheduler to the MMA and epilogue warps: a tile, a range of its k-blocks, and what to do with the
+// accumulator: the normal epilogue (after adding `npred` partial accumulators found in slots slot, slot + 1, ...), or
+// park it as a partial in `slot`.
+constexpr int SEG_PARTIAL = 1;
+__device__ __forceinline__ int seg_info(int kind, int npred, int slot) { return kind | (npred << 4) | (slot << 8); }
 
 // ---------------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -152,7 +164,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + Cfg::STAGES * Cfg::STAGE;
     // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], sched_full[SQ],
-    // sched_empty[SQ]; then the tile-id ring, the tmem pointer and the abort flag
+    // sched_empty[SQ]; then the segment ring (4 ints per entry), the tmem pointer and the abort flag
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::STAGES + a); };
@@ -161,7 +173,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto sempty_bar = [&](int q) { return bar_base + 8u * (2 * Cfg::STAGES + 4 + SQ + q); };
     volatile int* sched_tiles =
         reinterpret_cast<volatile int*>(smem_gen + Cfg::STAGES * Cfg::STAGE + 8 * (2 * Cfg::STAGES + 4 + 2 * SQ));
-    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(const_cast<int*>(sched_tiles) + SQ);
+    uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(const_cast<int*>(sched_tiles) + 4 * SQ);
+    static_assert(8 * (2 * Cfg::STAGES + 4 + 2 * SQ) + 16 * SQ + 8 <= 256, "barrier block overflows its 256 bytes");
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -199,20 +212,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // shared-memory ring; -1 ends the stream.
             int sq = 0;
             uint32_t sphase = 0;
-            int64_t tile = blockIdx.x;
-            while (ok) {
-                if (!mbar_wait(sempty_bar(sq), sphase ^ 1u, abort_flag)) { ok = false; break; }
-                sched_tiles[sq] = tile < num_tiles ? (int)tile : -1;
+            auto publish = [&](int tile, int kb0, int kb1, int info) -> bool {
+                if (!mbar_wait(sempty_bar(sq), sphase ^ 1u, abort_flag)) return false;
+                sched_tiles[4 * sq + 0] = tile;
+                sched_tiles[4 * sq + 1] = kb0;
+                sched_tiles[4 * sq + 2] = kb1;
+                sched_tiles[4 * sq + 3] = info;
                 mbar_arrive(sfull_bar(sq));
                 if (++sq == SQ) { sq = 0; sphase ^= 1u; }
-                if (tile >= num_tiles) break;
+                return true;
+            };
+            auto load = [&](int64_t tile, int kb0, int kb1) -> bool {
                 int64_t batch; int tm, tn;
                 tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
                 const int m0 = tm * BM, n0 = tn * BN;
                 const int ba = p.a_batched ? (int)batch : 0, bb = p.b_batched ? (int)batch : 0;
-                tile = (int64_t)gridDim.x + (int64_t)atomicAdd(p.tile_counter, 1u);  // fetched early: latency hides under the loads
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) return false;
                     const uint32_t sa = smem_base + stage * Cfg::STAGE;
                     const uint32_t sal = sa + Cfg::A_TILE, sb = sa + 2 * Cfg::A_TILE, sbl = sb + Cfg::B_TILE;
                     const uint32_t bar = full_bar(stage);
@@ -241,6 +257,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
                 }
+                return true;
+            };
+            // Work units: tiles [0, dp_tiles) whole, then sk_units pieces of the linear k-block range of the remaining
+            // tiles.  Units are drawn in ascending order and a piece only ever depends on pieces with a lower number,
+            // which some running CTA has already drawn, so the waits of the fix-up cannot form a cycle even when not all
+            // CTAs are resident.  For that the first unit must come from the counter too unless it is a whole tile.
+            const int64_t num_units = p.dp_tiles + p.sk_units;
+            const int64_t unit_base = (p.dp_tiles >= (int64_t)gridDim.x) ? (int64_t)gridDim.x : 0;
+            auto draw = [&]() -> int64_t { return unit_base + (int64_t)atomicAdd(p.tile_counter, 1u); };
+            const int64_t sk_total = (num_tiles - p.dp_tiles) * (int64_t)num_kb;
+            const int64_t sk_q = p.sk_units ? sk_total / p.sk_units : 0, sk_r = p.sk_units ? sk_total % p.sk_units : 0;
+            int64_t unit = unit_base ? (int64_t)blockIdx.x : draw();
+            while (ok) {
+                if (unit >= num_units) { if (!publish(-1, 0, 0, 0)) ok = false; break; }
+                int64_t next = -1;
+                if (unit < p.dp_tiles) {
+                    if (!publish((int)unit, 0, num_kb, 0)) { ok = false; break; }
+                    next = draw();  // fetched early: the latency hides under the loads
+                    if (!load(unit, 0, num_kb)) { ok = false; break; }
+                } else {
+                    // piece j covers [begin, end) of the linear range.  Its tiles are walked from the last to the first: the
+                    // part that does not reach its tile's end (a partial for piece j + 1 to pick up) goes first, the part
+                    // that completes a tile begun by earlier pieces goes last, when their partials have long been stored.
+                    const int64_t j = unit - p.dp_tiles;
+                    const int64_t begin = j * sk_q + (j < sk_r ? j : sk_r);
+                    int64_t hi = begin + sk_q + (j < sk_r ? 1 : 0);
+                    while (hi > begin) {
+                        const int64_t t = (hi - 1) / num_kb, base = t * (int64_t)num_kb;
+                        const int64_t lo = begin > base ? begin : base;
+                        int info = 0;
+                        if (hi - base < num_kb) {
+                            info = seg_info(SEG_PARTIAL, 0, (int)j);
+                        } else if (lo > base) {
+                            const int64_t cut = sk_r * (sk_q + 1);  // pieces below sk_r are one k-block longer
+                            const int64_t first = base < cut ? base / (sk_q + 1) : sk_r + (base - cut) / sk_q;
+                            info = seg_info(0, (int)(j - first), (int)first);
+                        }
+                        if (!publish((int)(p.dp_tiles + t), (int)(lo - base), (int)(hi - base), info)) { ok = false; break; }
+                        if (next < 0) next = draw();
+                        if (!load(p.dp_tiles + t, (int)(lo - base), (int)(hi - base))) { ok = false; break; }
+                        hi = lo;
+                    }
+                }
+                unit = next;
             }
             if (!ok) {
                 // Drain: let every copy already issued land before the CTA gives its shared memory back.
@@ -282,14 +342,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t sphase = 0;
             while (ok) {
                 if (!mbar_wait(sfull_bar(sq), sphase, abort_flag)) { ok = false; break; }
-                const int tile = sched_tiles[sq];
+                const int tile = sched_tiles[4 * sq], kb0 = sched_tiles[4 * sq + 1], kb1 = sched_tiles[4 * sq + 2];
                 mbar_arrive(sempty_bar(sq));
                 if (++sq == SQ) { sq = 0; sphase ^= 1u; }
                 if (tile < 0) break;
                 if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
                     tcgen05_fence_after();
                     const uint32_t sa = smem_base + stage * Cfg::STAGE;
@@ -300,7 +360,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const uint64_t dal = make_desc(sal + k * A_KSTEP, A_LBO, A_SBO, A_LT);
                         const uint64_t db = make_desc(sb + k * B_KSTEP, B_LBO, B_SBO, B_LT);
                         const uint64_t dbl = make_desc(sbl + k * B_KSTEP, B_LBO, B_SBO, B_LT);
-                        umma_tf32(d_tmem, dal, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);  // a_lo * b_hi
+                        umma_tf32(d_tmem, dal, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);  // a_lo * b_hi
                         umma_tf32(d_tmem, da, dbl, idesc, 1u);                             // a_hi * b_lo
                         umma_tf32(d_tmem, da, db, idesc, 1u);                              // a_hi * b_hi
                     }
@@ -335,14 +395,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         };
         while (ok) {
             if (!warp_wait(sfull_bar(sq), sphase)) { ok = false; break; }
-            int tile = 0;
+            int tile = 0, info = 0;
             if (lane == 0) {
-                tile = sched_tiles[sq];
+                tile = sched_tiles[4 * sq];
+                info = sched_tiles[4 * sq + 3];
                 mbar_arrive(sempty_bar(sq));
             }
             tile = __shfl_sync(0xffffffffu, tile, 0);
+            info = __shfl_sync(0xffffffffu, info, 0);
             if (++sq == SQ) { sq = 0; sphase ^= 1u; }
             if (tile < 0) break;
+            const bool partial = (info & SEG_PARTIAL) != 0;
+            int npred = (info >> 4) & 15;
+            const int slot = info >> 8;
             int64_t batch; int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
             if (!warp_wait(tfull_bar(acc), acc_phase[acc])) { ok = false; break; }
@@ -361,6 +426,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int64_t clo_off0 = (batch * p.M + m_warp + row_sub) * p.ld_clo;
             const bool plain = !p.bias && !p.bias_m && p.act == TENMO_ACT_NONE && !p.aux && !p.mul_mask && !p.c_lo &&
                                p.beta == 0.f && p.c_vec;
+            // Stream-K fix-up.  A partial accumulator is parked in its slot in the order the registers come out of tensor
+            // memory: float4 number (8 c + q) * 128 + row, so that a warp's store covers 512 contiguous bytes; the warp of
+            // the completing CTA that owns the same rows and columns reads it back the same way.  A slot's flag counts the
+            // epilogue warps that have stored their part.
+            float4* const part = reinterpret_cast<float4*>(p.sk_partials + (size_t)slot * (BM * BN)) + quarter * 32 + lane;
+            if (npred) {
+                int got = 1;
+                if (lane == 0) {
+                    const uint64_t t0 = globaltimer_ns();
+                    for (int s = 0; s < npred && got; ++s) {
+                        const unsigned int* f = p.sk_flags + slot + s;
+                        for (uint32_t it = 0;; ++it) {
+                            unsigned int v;
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                            if (v >= (unsigned int)EPI_WARPS) break;
+                            if (*abort_flag || ((it & 63u) == 63u && globaltimer_ns() - t0 > TENMO_WAIT_LIMIT_NS)) {
+                                *abort_flag = 1;
+                                got = 0;
+                                break;
+                            }
+                        }
+                    }
+                }
+                if (!__shfl_sync(0xffffffffu, got, 0)) npred = 0;  // gave up: finish the tile without them, the status word tells
+            }
 #pragma unroll 1
             for (int c = half; c < BN / 32; c += 2) {
                 const int64_t n0 = n_base + c * 32;
@@ -368,6 +458,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), r);
                 tmem_ld_wait();
+                if (partial) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        part[(c * 8 + q) * 128] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                              __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                    continue;
+                }
+                for (int s = 0; s < npred; ++s) {  // ascending k: own + partial of the first piece + the next ...
+                    const float4* src = part + (size_t)s * (BM * BN / 4) + (c * 8) * 128;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const float4 x = __ldcg(src + q * 128);
+                        r[4 * q] = __float_as_uint(__uint_as_float(r[4 * q]) + x.x);
+                        r[4 * q + 1] = __float_as_uint(__uint_as_float(r[4 * q + 1]) + x.y);
+                        r[4 * q + 2] = __float_as_uint(__uint_as_float(r[4 * q + 2]) + x.z);
+                        r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + x.w);
+                    }
+                }
 #pragma unroll
                 for (int q = 0; q < 32; q += 4)
                     *reinterpret_cast<float4*>(ebuf + lane * EP_LD + ((((q >> 2) ^ (lane & 7))) << 2)) =
@@ -446,7 +554,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (lane == 0) {
+                mbar_arrive(tempty_bar(acc));
+                if (partial) {
+                    __threadfence();  // the warp's stores (ordered before this by the __syncwarp) are visible before the count
+                    atomicAdd(p.sk_flags + slot, 1u);
+                }
+            }
             acc_phase[acc] ^= 1u;
             acc ^= 1;
         }
@@ -456,8 +570,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     if (threadIdx.x == 0) {
         if (*abort_flag) atomicOr(p.status, TENMO_DEV_TIMEOUT);
-        // every CTA has finished drawing tiles once it is here; the last one re-arms the counter pair
+        // every CTA has finished drawing tiles (and reading flags) once it is here; the last one re-arms the counter pair
+        // and the fix-up flags, so that no memset sits in front of the next launch and a captured graph can be replayed
+        __threadfence();
         if (atomicAdd(p.tile_counter + 1, 1u) == gridDim.x - 1) {
+            __threadfence();
+            for (int u = 0; u < p.sk_units; ++u) p.sk_flags[u] = 0;
             p.tile_counter[0] = 0;
             p.tile_counter[1] = 0;
             __threadfence();
@@ -678,13 +796,54 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     char why[160];
     if (!tenmo_make_plan(p, &a, &b, why, sizeof(why))) return tenmo_set_error(ctx, TENMO_ERR_UNSUPPORTED, "gemm_tc: %s", why);
 
+    // Tile width: 128 x 256 unless that leaves most SMs without a tile, then 128 x 128, then 128 x 64
+    // (e.g. the 1000-class output layer at batch 1024: 32 tiles -> 64 -> 128).
+    int ctas = ctx->sm_count - ctx->reserve_sms;  // SMs left free for a collective running beside the GEMM
+    if (ctas < 1) ctas = 1;
+    auto tiles_for = [&](int w) { return ((p.M + BM - 1) / BM) * ((p.N + w - 1) / w) * p.total_batch; };
+    int bn = 256;
+    if (tiles_for(256) * 4 < (int64_t)ctas * 3) bn = tiles_for(128) * 4 < (int64_t)ctas * 3 ? 64 : 128;
+    if (p.N <= 64) bn = 64;
+    else if (p.N <= 128 && bn > 128) bn = 128;
+    const char* env_bn = getenv("TENMO_TC_BN");
+    if (env_bn && (atoi(env_bn) == 64 || atoi(env_bn) == 128 || atoi(env_bn) == 256)) bn = atoi(env_bn);
+
+    // Stream-K tail.  With T tiles on P CTAs the last wave is only partly filled (128 tiles on 148 SMs: 14 % of the
+    // machine idle; 512 tiles: 3.46 waves run as 4).  When that costs more than 5 %, the last full wave and the remainder
+    // (or everything, if there is less than one wave) are handed out as P equal pieces of their linear k-block range; a
+    // piece that ends inside a tile parks its accumulator in the workspace and the piece holding the tile's end adds it.
+    // The cut depends only on the shape and the CTA count, so results are reproducible.
+    const int64_t tiles = tiles_for(bn);
+    if (tiles > 0x7fffffffLL) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_tc: %lld tiles is out of range", (long long)tiles);
+    int sk_units = 0;
+    int64_t dp_tiles = tiles;
+    {
+        const int64_t num_kb = (p.K + BK - 1) / BK;
+        const int64_t waves = (tiles + ctas - 1) / ctas;
+        const char* env_sk = getenv("TENMO_TC_STREAMK");
+        const bool allowed = !(env_sk && atoi(env_sk) == 0) && p.ws_skip == 0 && ctas <= TENMO_SK_MAX_UNITS;
+        if (allowed && tiles % ctas != 0 && (double)tiles < 0.95 * (double)(waves * ctas)) {
+            const int64_t full = tiles / ctas;
+            const char* env_mode = getenv("TENMO_TC_SK_MODE");
+            const char* env_minq = getenv("TENMO_TC_SK_MINQ");
+            const int mode = env_mode ? atoi(env_mode) : 1;
+            const int64_t minq = env_minq ? atoi(env_minq) : 64;
+            int64_t dp = full >= 1 ? (full - 1) * ctas : 0;
+            if (mode == 2 && (tiles - full * ctas) * num_kb / ctas >= minq) dp = full * ctas;
+            const int64_t q = (tiles - dp) * num_kb / ctas;
+            // pieces of at least minq k-blocks, and at most 8 partials to add into one tile
+            if (q >= 8 && q >= minq && q * 8 >= num_kb) { sk_units = ctas; dp_tiles = dp; }
+        }
+    }
+    const size_t sk_bytes = (size_t)sk_units * BM * bn * 4;
+
     // lo planes: taken from the caller when supplied (same storage geometry: outer x inner rounded up to 4,
     // batches back to back), else split here into the workspace [A_lo | B_lo]
     const size_t a_lo_bytes = p.a_lo ? 0 : (((size_t)a.bstride_lo * a.batches * 4 + 1023) & ~(size_t)1023);
     const size_t b_lo_bytes = p.b_lo ? 0 : (((size_t)b.bstride_lo * b.batches * 4 + 1023) & ~(size_t)1023);
     void* ws = nullptr;
-    if (a_lo_bytes + b_lo_bytes > 0) {
-        st = tenmo_workspace(ctx, p.ws_skip + a_lo_bytes + b_lo_bytes, &ws);
+    if (a_lo_bytes + b_lo_bytes + sk_bytes > 0) {
+        st = tenmo_workspace(ctx, p.ws_skip + a_lo_bytes + b_lo_bytes + sk_bytes, &ws);
         if (st != TENMO_OK) return st;
         ws = static_cast<char*>(ws) + p.ws_skip;
     }
@@ -703,18 +862,6 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     };
     if (!p.a_lo && (st = split(p.A, const_cast<float*>(a_lo), a)) != TENMO_OK) return st;
     if (!p.b_lo && (st = split(p.B, const_cast<float*>(b_lo), b)) != TENMO_OK) return st;
-
-    // Tile width: 128 x 256 unless that leaves most SMs without a tile, then 128 x 128, then 128 x 64
-    // (e.g. the 1000-class output layer at batch 1024: 32 tiles -> 64 -> 128).
-    int ctas = ctx->sm_count - ctx->reserve_sms;  // SMs left free for a collective running beside the GEMM
-    if (ctas < 1) ctas = 1;
-    auto tiles_for = [&](int w) { return ((p.M + BM - 1) / BM) * ((p.N + w - 1) / w) * p.total_batch; };
-    int bn = 256;
-    if (tiles_for(256) * 4 < (int64_t)ctas * 3) bn = tiles_for(128) * 4 < (int64_t)ctas * 3 ? 64 : 128;
-    if (p.N <= 64) bn = 64;
-    else if (p.N <= 128 && bn > 128) bn = 128;
-    const char* env_bn = getenv("TENMO_TC_BN");
-    if (env_bn && (atoi(env_bn) == 64 || atoi(env_bn) == 128 || atoi(env_bn) == 256)) bn = atoi(env_bn);
 
     CUtensorMap ma, mal, mb, mbl;
     const int a_box = a.mn_major ? BK : BM;
@@ -737,9 +884,11 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
                (!p.mul_mask || (reinterpret_cast<uintptr_t>(p.mul_mask) & 15u) == 0) &&
                (!p.c_lo || ((reinterpret_cast<uintptr_t>(p.c_lo) & 15u) == 0 && p.ld_clo % 4 == 0));
     tp.status = ctx->dev_status;
-    const int64_t tiles = (int64_t)tp.tiles_m * tp.tiles_n * p.total_batch;
-    if (tiles > 0x7fffffffLL) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_tc: %lld tiles is out of range", (long long)tiles);
-    const int grid = (int)(tiles < ctas ? tiles : ctas);
+    tp.sk_units = sk_units;
+    tp.dp_tiles = dp_tiles;
+    tp.sk_partials = sk_units ? reinterpret_cast<float*>(static_cast<char*>(ws) + a_lo_bytes + b_lo_bytes) : nullptr;
+    tp.sk_flags = reinterpret_cast<unsigned int*>(ctx->dev_status) + TENMO_SK_FLAG_WORD0;
+    const int grid = sk_units ? ctas : (int)(tiles < ctas ? tiles : ctas);
     // a tile counter pair for this launch (dev_status words 64..127: [next tile, CTAs finished] x 32).  Both words
     // are zero between launches: the last CTA to leave clears them, so no memset sits in front of the kernel.
     tp.tile_counter = reinterpret_cast<unsigned int*>(ctx->dev_status) + 64 + 2 * (ctx->tile_counter_next++ % TILE_COUNTERS);
@@ -750,6 +899,7 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     tenmo_prof_after(ctx);
     ctx->launches++;
     ctx->last_gemm_kernel = "gemm_tc_kernel";
+    ctx->last_gemm_sk_units = sk_units;
     if (e != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_tc_kernel failed: %s", cudaGetErrorString(e));
     return TENMO_OK;
 }

@@ -25,7 +25,7 @@ EXPORTS = [
     "tenmo_cuda_init", "tenmo_cuda_destroy", "tenmo_cuda_last_error", "tenmo_cuda_version", "tenmo_cuda_set_stream",
     "tenmo_cuda_synchronize", "tenmo_cuda_device_info", "tenmo_cuda_check_device_status", "tenmo_cuda_launch_count",
     "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end", "tenmo_cuda_reserve_sms",
-    "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_gemm_last_kernel", "tenmo_cuda_wait_probe", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
+    "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_gemm_last_kernel", "tenmo_gemm_last_stream_k", "tenmo_cuda_wait_probe", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
     "tenmo_conv_out_size", "tenmo_im2col_f32", "tenmo_col2im_f32", "tenmo_channel_sum_f32", "tenmo_maxpool2d_fwd_f32",
     "tenmo_maxpool2d_bwd_f32",
@@ -108,6 +108,7 @@ def _bind(lib):
         "tenmo_split_lo_f32": (I, [P, C.POINTER(Mat), I64, I64, P, I64]),
         "tenmo_gemm_last_algo": (I, [P]),
         "tenmo_gemm_last_kernel": (C.c_char_p, [P]),
+        "tenmo_gemm_last_stream_k": (I, [P]),
         "tenmo_cuda_wait_probe": (I, [P, C.c_int]),
         "tenmo_add_bias_f32": (I, [P, P, P, P, I64, I64]),
         "tenmo_add_inplace_f32": (I, [P, P, P, I64]),
@@ -252,6 +253,10 @@ class TenmoCuda:
 
     def gemm_last_kernel(self) -> str:
         return self.require()._lib.tenmo_gemm_last_kernel(self._ctx).decode()
+
+    def gemm_last_stream_k(self) -> int:
+        """Pieces of the stream-K tail of the last tensor-core GEMM launch (0: every tile computed whole)."""
+        return int(self.require()._lib.tenmo_gemm_last_stream_k(self._ctx))
 
     def add_bias(self, x, bias, out, M, N):
         self._call("tenmo_add_bias_f32", x, bias, out, M, N)

@@ -203,3 +203,72 @@ def test_tc_split_k_for_small_outputs_with_long_k(g, oracle, mkn, layout):
     C2, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
     assert np.array_equal(C, C2)
     g.handle().check_device_status()
+
+
+# (M, K, N): tile counts that leave the last wave of a 148-SM machine partly empty in different ways -- less than one wave
+# (pieces shorter than a tile: up to three pieces per tile), one and a bit waves, several waves
+STREAM_K_SHAPES = [(1024, 1024, 1024), (1024, 4096, 4096), (2048, 512, 2048), (4096, 1024, 4096), (1000, 2052, 1000),
+                   (3, 640, 384, 512)]
+
+
+@pytest.mark.parametrize("mkn", STREAM_K_SHAPES, ids=str)
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+def test_tc_stream_k_tail(g, oracle, mkn, layout, monkeypatch):
+    """The stream-K tail (pieces of the k-range of the last tiles, partial accumulators added by the piece that ends a
+    tile): same bar as whole tiles, epilogue options honoured by the completing piece, repeatable bit for bit, and the
+    flags are back to zero after every launch (three launches in a row with different inputs)."""
+    batch = 1
+    if len(mkn) == 4:
+        batch, M, K, N = mkn
+        if layout != "nn":
+            pytest.skip("the batched case is run once")
+    else:
+        M, K, N = mkn
+    h = g.handle()
+    if h.device_info()["sm_count"] != 148:
+        pytest.skip("shapes chosen for 148 SMs")
+    rng = np.random.default_rng(M + K + N)
+    shape_a, shape_b = ((batch, M, K), (batch, K, N)) if batch > 1 else ((M, K), (K, N))
+    A, B = rng.standard_normal(shape_a, np.float32), rng.standard_normal(shape_b, np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    if batch > 1:
+        Av, Bv = oracle.View.of(A), oracle.View.of(B)
+    else:
+        Av, Bv = layouts(oracle, A, B, layout)
+    ref64 = A.astype(np.float64) @ B.astype(np.float64)
+    absA, absB = np.abs(A), np.abs(B)
+
+    def bar(C, want):
+        scale = np.matmul(absA.astype(np.float64), absB.astype(np.float64)) + 1e-30
+        return float(np.max(np.abs(C.astype(np.float64) - want) / scale))
+
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert h.gemm_last_kernel() == "gemm_tc_kernel" and h.gemm_last_stream_k() == 148
+    assert bar(C, ref64) <= TOL
+    C2, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert np.array_equal(C, C2)
+    monkeypatch.setenv("TENMO_TC_STREAMK", "0")
+    C0, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert h.gemm_last_stream_k() == 0
+    monkeypatch.delenv("TENMO_TC_STREAMK")
+    assert bar(C0, ref64) <= TOL and bar(C, C0.astype(np.float64)) <= TOL
+    if batch == 1:
+        # bias + ReLU + mask + accumulate, applied once, by the completing piece
+        init = rng.standard_normal((M, N), np.float32)
+        C3, aux, _ = g.gpu_matmul(Av, Bv, algo=TC, bias=bias, act=1, want_aux=True, beta=1.0, c_init=init)
+        assert h.gemm_last_stream_k() == 148
+        pre = ref64 + bias
+        want = init + np.maximum(pre, 0)
+        scale = absA.astype(np.float64) @ absB.astype(np.float64) + 1e-30
+        err = np.abs(C3.astype(np.float64) - want) / scale
+        near0 = np.abs(pre) / scale < 1e-4
+        err[near0] = 0
+        assert float(err.max()) <= TOL
+        assert np.array_equal(aux[~near0], (pre > 0).astype(np.float32)[~near0])
+    # other inputs straight after: nothing of the previous launch may be picked up
+    A2 = rng.standard_normal(shape_a, np.float32)
+    absA = np.abs(A2)
+    Av2 = oracle.View.of(A2) if (batch > 1 or layout[0] == "n") else oracle.View.of(np.ascontiguousarray(A2.T)).t()
+    C4, _, _ = g.gpu_matmul(Av2, Bv, algo=TC)
+    assert bar(C4, A2.astype(np.float64) @ B.astype(np.float64)) <= TOL
+    h.check_device_status()
