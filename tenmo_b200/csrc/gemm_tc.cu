@@ -15,6 +15,11 @@
 //                           accumulator; also owns the TMEM allocation (2 accumulators, double buffered)
 //   warps 2-9 epilogue      tcgen05.ld the accumulator (one TMEM lane = one row per thread), add bias,
 //                           activation / ReLU mask / beta accumulate, store to C
+// Scheduling.  Work is handed out by the producer warp through a small shared-memory ring as segments (tile, range of
+// k-blocks, action).  Normally a segment is a whole tile.  When the tiles would leave the last wave of CTAs partly
+// empty, the k-blocks of the last tiles are cut into one equal piece per CTA (stream-K): a piece that ends inside a tile
+// parks its accumulator in the workspace, the piece that holds the tile's end adds the parked ones in ascending k and
+// runs the epilogue.  Pieces depend only on lower-numbered pieces and are drawn in ascending order.
 // Operand layouts.  "K-major" = the contraction index is the unit-stride axis (row-major A, or B given
 // as a transposed view); "MN-major" = the other axis is (A given as a transposed view, row-major B).
 // Both are native tcgen05 shared-memory layouts, so transposed stride views need no copy: only the
@@ -809,10 +814,14 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     if (env_bn && (atoi(env_bn) == 64 || atoi(env_bn) == 128 || atoi(env_bn) == 256)) bn = atoi(env_bn);
 
     // Stream-K tail.  With T tiles on P CTAs the last wave is only partly filled (128 tiles on 148 SMs: 14 % of the
-    // machine idle; 512 tiles: 3.46 waves run as 4).  When that costs more than 5 %, the last full wave and the remainder
-    // (or everything, if there is less than one wave) are handed out as P equal pieces of their linear k-block range; a
-    // piece that ends inside a tile parks its accumulator in the workspace and the piece holding the tile's end adds it.
-    // The cut depends only on the shape and the CTA count, so results are reproducible.
+    // machine idle; 512 tiles: 3.46 waves run as 4).  When that costs more than 5 %, the k-blocks of the last tiles are
+    // handed out as P equal pieces of one linear range; a piece that ends inside a tile parks its accumulator in the
+    // workspace and the piece holding the tile's end adds it.  The cut depends only on the shape and the CTA count, so
+    // results are reproducible.
+    // Which tiles: pieces run at different k positions, so they share less of the operand panels in L2 than whole tiles
+    // walking k in step; measured on 4096-wide layers, cutting the last 1.x waves pays up to x = .6 (+6 .. +14 %), above
+    // that only the last, partial wave should be cut (1.73 waves as pieces: -6 %; its last .73: +6 %).  Pieces under 48
+    // k-blocks do not repay the fix-up.
     const int64_t tiles = tiles_for(bn);
     if (tiles > 0x7fffffffLL) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_tc: %lld tiles is out of range", (long long)tiles);
     int sk_units = 0;
@@ -824,15 +833,11 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
         const bool allowed = !(env_sk && atoi(env_sk) == 0) && p.ws_skip == 0 && ctas <= TENMO_SK_MAX_UNITS;
         if (allowed && tiles % ctas != 0 && (double)tiles < 0.95 * (double)(waves * ctas)) {
             const int64_t full = tiles / ctas;
-            const char* env_mode = getenv("TENMO_TC_SK_MODE");
-            const char* env_minq = getenv("TENMO_TC_SK_MINQ");
-            const int mode = env_mode ? atoi(env_mode) : 1;
-            const int64_t minq = env_minq ? atoi(env_minq) : 64;
-            int64_t dp = full >= 1 ? (full - 1) * ctas : 0;
-            if (mode == 2 && (tiles - full * ctas) * num_kb / ctas >= minq) dp = full * ctas;
+            int64_t dp = 0;
+            if (full >= 1) dp = ((tiles - (full - 1) * ctas) * 10 <= (int64_t)ctas * 16) ? (full - 1) * ctas : full * ctas;
             const int64_t q = (tiles - dp) * num_kb / ctas;
-            // pieces of at least minq k-blocks, and at most 8 partials to add into one tile
-            if (q >= 8 && q >= minq && q * 8 >= num_kb) { sk_units = ctas; dp_tiles = dp; }
+            // and at most 8 partials to add into one tile
+            if (q >= 48 && q * 8 >= num_kb) { sk_units = ctas; dp_tiles = dp; }
         }
     }
     const size_t sk_bytes = (size_t)sk_units * BM * bn * 4;

@@ -206,9 +206,10 @@ def test_tc_split_k_for_small_outputs_with_long_k(g, oracle, mkn, layout):
 
 
 # (M, K, N): tile counts that leave the last wave of a 148-SM machine partly empty in different ways -- less than one wave
-# (pieces shorter than a tile: up to three pieces per tile), one and a bit waves, several waves
-STREAM_K_SHAPES = [(1024, 1024, 1024), (1024, 4096, 4096), (2048, 512, 2048), (4096, 1024, 4096), (1000, 2052, 1000),
-                   (3, 640, 384, 512)]
+# (pieces shorter than a tile), 3.46 waves (the last 1.46 cut into pieces), 1.73 waves (only the last .73), ragged
+# edges in m, n and k, a batch
+STREAM_K_SHAPES = [(1024, 2048, 1024), (1024, 4096, 4096), (2048, 2048, 2048), (4096, 2048, 4096), (2048, 4096, 4096),
+                   (1000, 2052, 1000), (3, 640, 2048, 512)]
 
 
 @pytest.mark.parametrize("mkn", STREAM_K_SHAPES, ids=str)
