@@ -273,3 +273,43 @@ def test_tc_stream_k_tail(g, oracle, mkn, layout, monkeypatch):
     C4, _, _ = g.gpu_matmul(Av2, Bv, algo=TC)
     assert bar(C4, A2.astype(np.float64) @ B.astype(np.float64)) <= TOL
     h.check_device_status()
+
+
+def test_tc_stream_k_replays_in_a_graph(g):
+    """A captured launch with a stream-K tail is replayed with new inputs: the kernel re-arms its own counters, so each
+    replay equals the eager call on the same inputs bit for bit."""
+    from tenmo_b200 import make_mat
+
+    h = g.handle()
+    if h.device_info()["sm_count"] != 148:
+        pytest.skip("shape chosen for 148 SMs")
+    M, K, N = 1024, 2048, 1024
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    A, B = torch.randn(M, K, generator=gen, device="cuda"), torch.randn(K, N, generator=gen, device="cuda")
+    C, Ce = g.empty(M, N), g.empty(M, N)
+    mA, mB = make_mat(A.data_ptr(), (M, K), (K, 1)), make_mat(B.data_ptr(), (K, N), (N, 1))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    try:
+        with torch.cuda.stream(side):
+            h.set_stream(side.cuda_stream)
+            h.gemm(M, N, K, mA, mB, C.data_ptr(), algo=TC)  # grows the workspace before the capture
+            assert h.gemm_last_stream_k() == 148
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                h.gemm(M, N, K, mA, mB, C.data_ptr(), algo=TC)
+        torch.cuda.current_stream().wait_stream(side)
+    finally:
+        h.set_stream(torch.cuda.current_stream().cuda_stream)
+    for _ in range(3):
+        A.copy_(torch.randn(M, K, generator=gen, device="cuda"))
+        C.fill_(float("nan"))
+        graph.replay()
+        h.gemm(M, N, K, mA, mB, Ce.data_ptr(), algo=TC)
+        torch.cuda.synchronize()
+        assert torch.equal(C, Ce)
+        ref = A.double() @ B.double()
+        scale = A.double().abs() @ B.double().abs()
+        assert float(((C.double() - ref).abs() / scale).max()) <= TOL
+    h.check_device_status()
