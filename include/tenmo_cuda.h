@@ -245,6 +245,15 @@ int tenmo_ce_fwd_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, con
 int tenmo_ce_bwd_f32(tenmo_ctx* ctx, const float* softmax, const void* labels, int label_is_i64, int64_t M,
                      int64_t C, int64_t ignore_index, float label_smoothing, int reduction,
                      const float* upstream_dev, const int32_t* valid_count_dev, float* dlogits, float beta);
+/* Forward and backward in one call, for a loss that is the root of the backward pass (loss.backward() right after
+ * criterion(pred, labels): crossentropy.mojo:1360-1391 then 664-823).  Same arguments and the same bits as
+ * tenmo_ce_fwd_f32 followed by tenmo_ce_bwd_f32 with beta = 0; softmax_out is required.  A small batch
+ * (M <= 256 and M*C <= 16384, the MNIST- and CIFAR-shaped configurations) is ONE launch: the CTA that finishes the
+ * loss and the valid count also writes dlogits.  Larger batches run the two kernels. */
+int tenmo_ce_fwd_bwd_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, const void* labels,
+                         int label_is_i64, int64_t M, int64_t C, int64_t ignore_index, float label_smoothing,
+                         int reduction, float* softmax_out, float* loss_dev, int32_t* valid_count_dev,
+                         const float* upstream_dev, float* dlogits);
 
 /* ---- optimiser ----------------------------------------------------------------------------------
  * SGD.step dense path for n_tensors parameters in ONE launch (optim.mojo:405-543,

@@ -165,10 +165,8 @@ class CNNTrainer:
         flat = make_mat(a2.data_ptr(), (B, self.feat), (self.feat, 1))            # Flatten: NCHW order, a view
         mWfc = make_mat(p["fc.weight"].data_ptr(), (self.feat, C), (C, 1))
         h.gemm_ex(B, C, self.feat, flat, mWfc, self.logits.data_ptr(), algo=_lib.ALGO_SIMT_FP32, bias=p["fc.bias"].data_ptr())
-        h.ce_fwd(self.logits.data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
-                 self.loss.data_ptr(), self.valid.data_ptr())
-        h.ce_bwd(self.softmax.data_ptr(), self.y.data_ptr(), True, B, C, -100, 0.0, 0, 0, self.valid.data_ptr(),
-                 self.dlogits.data_ptr())
+        h.ce_fwd_bwd(self.logits.data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
+                     self.loss.data_ptr(), self.valid.data_ptr(), 0, self.dlogits.data_ptr())
         mdl = make_mat(self.dlogits.data_ptr(), (B, C), (C, 1))
         h.gemm_ex(self.feat, C, B, make_mat(a2.data_ptr(), (self.feat, B), (1, self.feat)), mdl, g["fc.weight"].data_ptr(),
                   algo=_lib.ALGO_SIMT_FP32, colsum=g["fc.bias"].data_ptr())

@@ -39,9 +39,14 @@ struct CeFwdArgs {
     int vec;              // rows may be read / written as float4 (C % 4 == 0, ld % 4 == 0, 16-byte aligned bases)
     unsigned int* ticket; // one counter, zero between calls
     uint32_t* status;
+    // fused backward of a small batch (NULL: off): the CTA that finishes the loss also writes
+    // dlogits = ((softmax - (1-ls)*onehot) - ls/C) * valid * (upstream / scale), the arithmetic of ce_bwd_flat_kernel
+    float* dlogits;
+    const float* upstream;
 };
 
 constexpr int CE_SEQ_ROWS = 256;  // up to here the mean is the reference's row-ascending sequential sum
+constexpr int64_t CE_FUSED_BWD_MAX = 16384;  // logits of a batch whose backward the forward kernel's last CTA also does
 
 __device__ __forceinline__ int64_t load_label(const void* labels, int is_i64, int64_t row) {
     return is_i64 ? reinterpret_cast<const int64_t*>(labels)[row] : (int64_t) reinterpret_cast<const int32_t*>(labels)[row];
@@ -264,6 +269,31 @@ __global__ void __launch_bounds__(CE_THREADS, SMALL_C ? 2 : 3) ce_fwd_kernel(con
     __threadfence();
     ce_finalize(p, red_smem);
     if (threadIdx.x == 0) *p.ticket = 0;
+    if (p.dlogits) {
+        // every row's softmax is in memory (the other CTAs fenced before they drew their ticket) and so is the count
+        __syncthreads();
+        float scale_mul = 1.f;
+        if (p.reduction != 2) {
+            const float ug = p.upstream ? __ldg(p.upstream) : 1.f;
+            const int vc = *reinterpret_cast<volatile int32_t*>(p.valid_count);
+            const float scale = (p.reduction == 0 && vc > 0) ? (float)vc : 1.f;
+            scale_mul = ug / scale;
+        }
+        const float ls_uniform = p.ls / (float)p.C;
+        const int total = (int)(p.M * p.C), Ci = (int)p.C;
+        for (int i = threadIdx.x; i < total; i += CE_THREADS) {
+            const int row = i / Ci, c = i - row * Ci;
+            const int64_t t = load_label(p.labels, p.label_is_i64, row);
+            const bool ignored = t == p.ignore_index;
+            const float onehot = (!ignored && t == c) ? 1.f : 0.f;
+            float g = __ldcg(p.softmax + i);
+            if (p.ls > 0.f) g = (g - __fmul_rn(onehot, 1.f - p.ls)) - ls_uniform;
+            else g = g - onehot;
+            g = g * (ignored ? 0.f : 1.f);
+            const float m = p.reduction == 2 ? (p.upstream ? __ldg(p.upstream + row) : 1.f) : scale_mul;
+            p.dlogits[i] = __fmul_rn(g, m);
+        }
+    }
 }
 
 struct CeBwdArgs {
@@ -366,11 +396,11 @@ __global__ void __launch_bounds__(CE_THREADS) ce_bwd_flat_kernel(const CeBwdArgs
 
 }  // namespace
 
-extern "C" {
-
-int tenmo_ce_fwd_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, const void* labels, int label_is_i64,
-                     int64_t M, int64_t C, int64_t ignore_index, float label_smoothing, int reduction,
-                     float* softmax_out, float* loss_dev, int32_t* valid_count_dev) {
+// upstream_dev / dlogits: the fused backward of a small batch, or NULL
+static int ce_fwd_impl(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, const void* labels, int label_is_i64,
+                       int64_t M, int64_t C, int64_t ignore_index, float label_smoothing, int reduction,
+                       float* softmax_out, float* loss_dev, int32_t* valid_count_dev, const float* upstream_dev,
+                       float* dlogits) {
     TENMO_CHECK_CTX(ctx);
     if (M < 0 || C <= 0) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_fwd: bad shape (M=%lld, C=%lld)", (long long)M, (long long)C);
     if (reduction < 0 || reduction > 2) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_fwd: reduction must be 0 (mean), 1 (sum) or 2 (none)");
@@ -406,10 +436,38 @@ int tenmo_ce_fwd_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, con
     p.vec = (C % 4 == 0) && (ld_logits % 4 == 0) && aligned16(logits) && (!softmax_out || aligned16(softmax_out));
     p.ticket = reinterpret_cast<unsigned int*>(ctx->dev_status + 8);
     p.status = ctx->dev_status;
+    p.dlogits = dlogits;
+    p.upstream = upstream_dev;
     if (C <= 32) ce_fwd_kernel<true><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
     else ce_fwd_kernel<false><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
     TENMO_LAUNCH_CHECK(ctx, "ce_fwd_kernel");
     return TENMO_OK;
+}
+
+extern "C" {
+
+int tenmo_ce_fwd_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, const void* labels, int label_is_i64,
+                     int64_t M, int64_t C, int64_t ignore_index, float label_smoothing, int reduction,
+                     float* softmax_out, float* loss_dev, int32_t* valid_count_dev) {
+    return ce_fwd_impl(ctx, logits, ld_logits, labels, label_is_i64, M, C, ignore_index, label_smoothing, reduction,
+                       softmax_out, loss_dev, valid_count_dev, nullptr, nullptr);
+}
+
+int tenmo_ce_fwd_bwd_f32(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, const void* labels, int label_is_i64,
+                         int64_t M, int64_t C, int64_t ignore_index, float label_smoothing, int reduction,
+                         float* softmax_out, float* loss_dev, int32_t* valid_count_dev, const float* upstream_dev,
+                         float* dlogits) {
+    TENMO_CHECK_CTX(ctx);
+    if (!softmax_out || (M > 0 && !dlogits)) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "ce_fwd_bwd: NULL pointer");
+    // one launch while the CTA that finishes the loss can also sweep the batch; two launches beyond that
+    if (M > 0 && M <= CE_SEQ_ROWS && M * C <= CE_FUSED_BWD_MAX)
+        return ce_fwd_impl(ctx, logits, ld_logits, labels, label_is_i64, M, C, ignore_index, label_smoothing, reduction,
+                           softmax_out, loss_dev, valid_count_dev, upstream_dev, dlogits);
+    int st = ce_fwd_impl(ctx, logits, ld_logits, labels, label_is_i64, M, C, ignore_index, label_smoothing, reduction,
+                         softmax_out, loss_dev, valid_count_dev, nullptr, nullptr);
+    if (st != TENMO_OK) return st;
+    return tenmo_ce_bwd_f32(ctx, softmax_out, labels, label_is_i64, M, C, ignore_index, label_smoothing, reduction,
+                            upstream_dev, valid_count_dev, dlogits, 0.f);
 }
 
 int tenmo_ce_bwd_f32(tenmo_ctx* ctx, const float* softmax, const void* labels, int label_is_i64, int64_t M, int64_t C,

@@ -29,7 +29,7 @@ EXPORTS = [
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
     "tenmo_conv_out_size", "tenmo_im2col_f32", "tenmo_col2im_f32", "tenmo_channel_sum_f32", "tenmo_maxpool2d_fwd_f32",
     "tenmo_maxpool2d_bwd_f32",
-    "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_sgd_step_f32", "tenmo_sgd_step_lo_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
+    "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_ce_fwd_bwd_f32", "tenmo_sgd_step_f32", "tenmo_sgd_step_lo_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
     "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
     "tenmo_dp_p2p_alloc", "tenmo_dp_p2p_connect", "tenmo_dp_p2p_allreduce_sum_f32", "tenmo_dp_p2p_close",
 ]
@@ -129,6 +129,7 @@ def _bind(lib):
         "tenmo_softmax_bwd_f32": (I, [P, P, P, P, F, I64, I64]),
         "tenmo_ce_fwd_f32": (I, [P, P, I64, P, I, I64, I64, I64, F, I, P, P, P]),
         "tenmo_ce_bwd_f32": (I, [P, P, P, I, I64, I64, I64, F, I, P, P, P, F]),
+        "tenmo_ce_fwd_bwd_f32": (I, [P, P, I64, P, I, I64, I64, I64, F, I, P, P, P, P, P]),
         "tenmo_sgd_step_f32": (I, [P, I, P, P, P, P, F, F, F, F]),
         "tenmo_sgd_step_lo_f32": (I, [P, I, P, P, P, P, P, P, F, F, F, F]),
         "tenmo_accuracy_f32": (I, [P, P, I64, P, I, I64, I64, P, P]),
@@ -316,6 +317,12 @@ class TenmoCuda:
                loss, valid_count):
         self._call("tenmo_ce_fwd_f32", logits, ld, labels, 1 if label_is_i64 else 0, M, Cn, ignore_index,
                    label_smoothing, reduction, softmax or None, loss, valid_count)
+
+    def ce_fwd_bwd(self, logits, ld, labels, label_is_i64, M, Cn, ignore_index, label_smoothing, reduction, softmax,
+                   loss, valid_count, upstream, dlogits):
+        """Loss and its gradient in one call (one launch for a small batch); same bits as ce_fwd then ce_bwd."""
+        self._call("tenmo_ce_fwd_bwd_f32", logits, ld, labels, 1 if label_is_i64 else 0, M, Cn, ignore_index,
+                   label_smoothing, reduction, softmax, loss, valid_count, upstream or None, dlogits)
 
     def ce_bwd(self, softmax, labels, label_is_i64, M, Cn, ignore_index, label_smoothing, reduction, upstream,
                valid_count, dlogits, beta=0.0):

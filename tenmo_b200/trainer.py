@@ -141,8 +141,9 @@ class MLPTrainer:
                       a_lo=self.act_lo[l].data_ptr() if lo else 0, b_lo=self.W_lo[l].data_ptr() if lo else 0,
                       c_lo=self.act_lo[l + 1].data_ptr() if (lo and not last) else 0)
         C = self.dims[-1]
-        h.ce_fwd(self.act[L].data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
-                 self.loss.data_ptr(), self.valid.data_ptr())
+        # loss and dlogits together: the loss is the root of the backward pass (one launch for a small batch)
+        h.ce_fwd_bwd(self.act[L].data_ptr(), C, self.y.data_ptr(), True, B, C, -100, 0.0, 0, self.softmax.data_ptr(),
+                     self.loss.data_ptr(), self.valid.data_ptr(), 0, self.gout[L - 1].data_ptr())
 
     def _allreduce(self, start: int, count: int):
         """Sum G[start, start + count) over the ranks on the library's current stream."""
@@ -197,9 +198,7 @@ class MLPTrainer:
 
     def _backward(self, exchange: bool = False):
         h, L, B = self.h, self.L, self.batch
-        C = self.dims[-1]
-        h.ce_bwd(self.softmax.data_ptr(), self.y.data_ptr(), True, B, C, -100, 0.0, 0, 0, self.valid.data_ptr(),
-                 self.gout[L - 1].data_ptr())
+        C = self.dims[-1]  # gout[L - 1] = dlogits was written with the loss
         lo = self.fused_lo
         if lo:
             h.split_lo(self._m(self.gout[L - 1]), B, C, self.gout_lo[L - 1].data_ptr(), self.gout_lo[L - 1].numel())

@@ -299,6 +299,21 @@ def _ce_gpu(g, logits, labels, reduction, ignore_index=-100, ls=0.0, i64=True):
     h.ce_fwd(ld.data_ptr(), C, lab.data_ptr(), i64, M, C, ignore_index, ls, red, sm.data_ptr(), loss.data_ptr(),
              vc.data_ptr())
     h.ce_bwd(sm.data_ptr(), lab.data_ptr(), i64, M, C, ignore_index, ls, red, 0, vc.data_ptr(), dl.data_ptr())
+    # the one-call form (one launch when the batch is small) must give the same bits, with and without an upstream value
+    sm2, dl2, loss2 = g.empty(M, C), torch.full((M, C), float("nan"), device="cuda"), g.empty(M if red == 2 else 1)
+    vc2 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    before = h.launch_count()
+    h.ce_fwd_bwd(ld.data_ptr(), C, lab.data_ptr(), i64, M, C, ignore_index, ls, red, sm2.data_ptr(), loss2.data_ptr(),
+                 vc2.data_ptr(), 0, dl2.data_ptr())
+    assert h.launch_count() - before == (1 if (M <= 256 and M * C <= 16384) else 2)
+    assert torch.equal(sm, sm2) and torch.equal(loss, loss2) and torch.equal(vc, vc2)
+    assert torch.equal(dl, dl2)
+    up = torch.full((M if red == 2 else 1,), 0.5, device="cuda")
+    h.ce_bwd(sm.data_ptr(), lab.data_ptr(), i64, M, C, ignore_index, ls, red, up.data_ptr(), vc.data_ptr(), dl2.data_ptr())
+    dl3 = torch.full((M, C), float("nan"), device="cuda")
+    h.ce_fwd_bwd(ld.data_ptr(), C, lab.data_ptr(), i64, M, C, ignore_index, ls, red, sm2.data_ptr(), loss2.data_ptr(),
+                 vc2.data_ptr(), up.data_ptr(), dl3.data_ptr())
+    assert torch.equal(dl2, dl3)
     h.check_device_status()
     return g.host(loss), g.host(sm), int(vc.item()), g.host(dl)
 
@@ -317,7 +332,7 @@ def test_ce_reference_literals(g):
     assert np.allclose(grad, f32(c["sum_grad"]), rtol=1e-5, atol=1e-7)
 
 
-@pytest.mark.parametrize("mc", [(64, 10), (256, 10), (3, 3), (1, 1), (100, 33), (1024, 1000), (8192, 1000), (70, 2500),
+@pytest.mark.parametrize("mc", [(64, 10), (256, 10), (3, 3), (1, 1), (100, 33), (1024, 1000), (8192, 1000), (70, 2500), (16, 1000), (200, 80), (256, 64), (128, 129),
                                 (5000, 7), (300, 36), (257, 64), (999, 1002), (513, 1024), (40, 2048)], ids=str)
 @pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
 def test_ce_vs_oracle(g, oracle, mc, reduction):
