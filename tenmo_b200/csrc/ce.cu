@@ -127,6 +127,7 @@ template <bool SMALL_C>
 __global__ void __launch_bounds__(CE_THREADS, SMALL_C ? 2 : 3) ce_fwd_kernel(const CeFwdArgs p) {
     __shared__ float red_smem[2 * CE_WARPS];
     __shared__ bool is_last;
+    tenmo_grid_dependency_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const bool partials = p.M > CE_SEQ_ROWS;
     float part_loss = 0.f;  // this thread's rows, ascending
@@ -438,8 +439,10 @@ static int ce_fwd_impl(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, c
     p.status = ctx->dev_status;
     p.dlogits = dlogits;
     p.upstream = upstream_dev;
-    if (C <= 32) ce_fwd_kernel<true><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
-    else ce_fwd_kernel<false><<<grid, CE_THREADS, 0, ctx->stream>>>(p);
+    const bool pdl = tenmo_pdl_ok(ctx, grid);
+    cudaError_t le = C <= 32 ? tenmo_launch(ce_fwd_kernel<true>, (unsigned)grid, CE_THREADS, 0, ctx->stream, pdl, p)
+                             : tenmo_launch(ce_fwd_kernel<false>, (unsigned)grid, CE_THREADS, 0, ctx->stream, pdl, p);
+    if (le != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of ce_fwd_kernel failed: %s", cudaGetErrorString(le));
     TENMO_LAUNCH_CHECK(ctx, "ce_fwd_kernel");
     return TENMO_OK;
 }

@@ -33,6 +33,7 @@ struct tenmo_ctx {
     int last_gemm_algo = -1;
     const char* last_gemm_kernel = "";
     int last_gemm_sk_units = 0;
+    bool pdl = true;  // programmatic dependent launch for small kernels (TENMO_PDL=0: off)
     // workspace (grown on demand, never shrunk): lo planes for the 3xTF32 kernel, reduction partials
     void* ws = nullptr;
     size_t ws_bytes = 0;
@@ -94,6 +95,36 @@ void tenmo_prof_after(tenmo_ctx* ctx);
         if (_e != cudaSuccess)                                                                     \
             return tenmo_set_error((ctx), TENMO_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \
     } while (0)
+
+// Programmatic dependent launch for chains of small kernels (a latency-bound training step).  A kernel launched through
+// tenmo_launch with pdl = true may be scheduled while its predecessor in the stream still runs: its CTAs become resident
+// and then block in tenmo_grid_dependency_sync() until the predecessor has completed and its memory operations are
+// visible, so the launch latency overlaps the predecessor instead of following it.  The kernel must call
+// tenmo_grid_dependency_sync() before it touches global memory; launched with pdl = false the call does nothing.
+// Only for grids that are resident at once (at most one CTA per SM): early CTAs of a large grid would take SM slots from
+// the kernel they wait for.  TENMO_PDL=0 in the environment turns it off.
+#ifdef __CUDACC__
+__device__ __forceinline__ void tenmo_grid_dependency_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next kernel in the stream may start launching
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t tenmo_launch(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s,
+                                       bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+static inline bool tenmo_pdl_ok(const tenmo_ctx* ctx, int64_t grid) { return ctx->pdl && grid <= ctx->sm_count; }
 
 // Grid size for grid-stride, bandwidth-bound kernels: a multiple of the SM count.
 static inline int tenmo_stream_grid(const tenmo_ctx* ctx, int64_t work_items, int items_per_block, int ctas_per_sm) {

@@ -106,6 +106,10 @@ int tenmo_cuda_init(int device, tenmo_ctx** out) {
     int khz = 0;
     cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device);
     ctx->sm_clock_khz = khz;
+    {
+        const char* env_pdl = getenv("TENMO_PDL");
+        ctx->pdl = !(env_pdl && atoi(env_pdl) == 0);
+    }
     e = cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->dev_status, TENMO_DEV_STATUS_WORDS * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->dev_status, 0, TENMO_DEV_STATUS_WORDS * sizeof(uint32_t));

@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
     using LoaderB = TileLoader<BN, BK, B_INNER_K>;
     __shared__ __align__(16) float As[2][BK * LoaderA::LD];
     __shared__ __align__(16) float Bs[2][BK * LoaderB::LD];
+    tenmo_grid_dependency_sync();
 
     const int tid = threadIdx.x;
     // tile decode: blockIdx.x = (batch * tiles_m + tile_m) * tiles_n + tile_n
@@ -271,15 +272,16 @@ __global__ void __launch_bounds__(THREADS, BM == 128 ? 2 : 1) gemm_simt_kernel(c
 }
 
 template <int BM, int BN, int BK, int TM, int TN>
-cudaError_t launch_cfg(const TenmoGemmParams& p, bool a_inner_k, bool b_inner_k, int64_t grid, cudaStream_t s) {
+cudaError_t launch_cfg(const TenmoGemmParams& p, bool a_inner_k, bool b_inner_k, int64_t grid, cudaStream_t s, bool pdl) {
+    cudaError_t e;
     if (a_inner_k) {
-        if (b_inner_k) gemm_simt_kernel<BM, BN, BK, TM, TN, true, true><<<(unsigned)grid, THREADS, 0, s>>>(p);
-        else gemm_simt_kernel<BM, BN, BK, TM, TN, true, false><<<(unsigned)grid, THREADS, 0, s>>>(p);
+        if (b_inner_k) e = tenmo_launch(gemm_simt_kernel<BM, BN, BK, TM, TN, true, true>, (unsigned)grid, THREADS, 0, s, pdl, p);
+        else e = tenmo_launch(gemm_simt_kernel<BM, BN, BK, TM, TN, true, false>, (unsigned)grid, THREADS, 0, s, pdl, p);
     } else {
-        if (b_inner_k) gemm_simt_kernel<BM, BN, BK, TM, TN, false, true><<<(unsigned)grid, THREADS, 0, s>>>(p);
-        else gemm_simt_kernel<BM, BN, BK, TM, TN, false, false><<<(unsigned)grid, THREADS, 0, s>>>(p);
+        if (b_inner_k) e = tenmo_launch(gemm_simt_kernel<BM, BN, BK, TM, TN, false, true>, (unsigned)grid, THREADS, 0, s, pdl, p);
+        else e = tenmo_launch(gemm_simt_kernel<BM, BN, BK, TM, TN, false, false>, (unsigned)grid, THREADS, 0, s, pdl, p);
     }
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace
@@ -326,10 +328,10 @@ int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p_in, bool* co
         return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm: grid of %lld tiles is out of range", (long long)grid);
     cudaError_t e;
     tenmo_prof_before(ctx);
-    if (cfg == 128) e = launch_cfg<128, 128, 16, 8, 8>(p, a_inner_k, b_inner_k, grid, ctx->stream);
-    else if (cfg == 64) e = launch_cfg<64, 64, 16, 4, 4>(p, a_inner_k, b_inner_k, grid, ctx->stream);
-    else if (p.K <= 32) e = launch_cfg<32, 32, 32, 2, 2>(p, a_inner_k, b_inner_k, grid, ctx->stream);
-    else e = launch_cfg<32, 32, 64, 2, 2>(p, a_inner_k, b_inner_k, grid, ctx->stream);  // deep k-tiles: fewer load round trips
+    if (cfg == 128) e = launch_cfg<128, 128, 16, 8, 8>(p, a_inner_k, b_inner_k, grid, ctx->stream, tenmo_pdl_ok(ctx, grid));
+    else if (cfg == 64) e = launch_cfg<64, 64, 16, 4, 4>(p, a_inner_k, b_inner_k, grid, ctx->stream, tenmo_pdl_ok(ctx, grid));
+    else if (p.K <= 32) e = launch_cfg<32, 32, 32, 2, 2>(p, a_inner_k, b_inner_k, grid, ctx->stream, tenmo_pdl_ok(ctx, grid));
+    else e = launch_cfg<32, 32, 64, 2, 2>(p, a_inner_k, b_inner_k, grid, ctx->stream, tenmo_pdl_ok(ctx, grid));  // deep k-tiles: fewer load round trips
     if (colsum_done) *colsum_done = p.colsum != nullptr;
     tenmo_prof_after(ctx);
     ctx->launches++;

@@ -38,6 +38,7 @@ __device__ __forceinline__ void sgd_one(float& p, float g, float& v, const SgdBa
 }
 
 __global__ void __launch_bounds__(SGD_THREADS) sgd_kernel(const SgdBatch b) {
+    tenmo_grid_dependency_sync();
     const int64_t total_chunks = b.chunk_start[b.n];
     const bool has_v = b.momentum > 0.f;
     for (int64_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
@@ -127,7 +128,8 @@ static int sgd_launch(tenmo_ctx* ctx, int n_tensors, float* const* p, const floa
         b.n = n;
         const int64_t cap = (int64_t)ctx->sm_count * 8;
         const int grid = (int)(chunks < cap ? chunks : cap);
-        sgd_kernel<<<grid, SGD_THREADS, 0, ctx->stream>>>(b);
+        cudaError_t le = tenmo_launch(sgd_kernel, (unsigned)grid, SGD_THREADS, 0, ctx->stream, tenmo_pdl_ok(ctx, grid), b);
+        if (le != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of sgd_kernel failed: %s", cudaGetErrorString(le));
         TENMO_LAUNCH_CHECK(ctx, "sgd_kernel");
     }
     return TENMO_OK;

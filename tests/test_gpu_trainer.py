@@ -125,3 +125,33 @@ def test_checkpoint_round_trip(tmp_path):
     b.step(X, y)
     for wa, wb in zip(a.weights(), b.weights()):
         assert np.array_equal(wa, wb)
+
+
+def test_dependent_launch_on_and_off_give_the_same_bits(monkeypatch):
+    """The small kernels of a latency-bound step are launched as programmatic dependents of one another (their launch
+    overlaps the predecessor, their work starts after it): 300 replays of the captured step must leave exactly the
+    weights that a context created with TENMO_PDL=0 (plain stream order) leaves."""
+    from tenmo_b200.trainer import MLPTrainer
+
+    rng = np.random.default_rng(9)
+    dims = [784, 128, 32, 10]
+    Ws = xavier(rng, dims)
+    bs = [np.zeros(d, np.float32) for d in dims[1:]]
+    with_pdl = MLPTrainer(Ws, bs, batch=64, algo="simt")
+    monkeypatch.setenv("TENMO_PDL", "0")
+    plain = MLPTrainer(Ws, bs, batch=64, algo="simt")
+    monkeypatch.delenv("TENMO_PDL")
+    with_pdl.capture()
+    plain.capture()
+    pool_x = rng.uniform(0, 1, (8, 64, 784)).astype(np.float32)
+    pool_y = rng.integers(0, 10, (8, 64))
+    for step in range(300):
+        for tr in (with_pdl, plain):
+            tr.load_batch(pool_x[step % 8], pool_y[step % 8])
+            tr.replay()
+    torch.cuda.synchronize()
+    assert with_pdl.loss_value() == plain.loss_value()
+    for a, b in zip(with_pdl.weights(), plain.weights()):
+        assert np.array_equal(a, b)
+    with_pdl.h.check_device_status()
+    plain.h.check_device_status()
