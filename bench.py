@@ -733,13 +733,13 @@ def main():
     ap.add_argument("--mlp-steps", type=int, default=20)
     ap.add_argument("--dp-exchange", choices=["auto", "nccl", "p2p"], default="auto",
                     help="gradient exchange of the training legs at N > 1: NCCL all-reduce or the library's peer-memory kernel; "
-                         "auto = peer-memory from 4 ranks up (measured: 17 %% faster at 8 ranks, 3 %% slower at 2)")
+                         "auto = peer-memory from 8 ranks up (measured: 17 %% faster at 8 ranks, 6 %% slower at 4, 5 %% slower at 2)")
     ap.add_argument("--legs", default="wide_mlp,cnn,mnist_mlp", help="which training legs to run after the GEMM arm")
     ap.add_argument("--kernels", action="store_true",
                     help="time the bandwidth-bound kernels of the path against the HBM roofline (one JSON line each)")
     args = ap.parse_args()
     if args.dp_exchange == "auto":
-        args.dp_exchange = "p2p" if int(os.environ.get("WORLD_SIZE", "1")) >= 4 else "nccl"
+        args.dp_exchange = "p2p" if int(os.environ.get("WORLD_SIZE", "1")) >= 8 else "nccl"
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.kernels:
