@@ -76,6 +76,10 @@ def lib():
         L.tenmo_ref_mlp_step.argtypes = [C.c_int, P, PP, PP, PP, PP, PP, PP, P, P, I64, F, F, F, F, C.c_int, P,
                                          C.POINTER(Opts)]
         L.tenmo_ref_mlp_step.restype = F
+        L.tenmo_ref_softmax_fwd.argtypes = [P, P, I64, I64, C.c_int]
+        L.tenmo_ref_softmax_bwd.argtypes = [P, P, P, I64, I64, C.c_int]
+        L.tenmo_ref_mv.argtypes = [P, I64, I64, P, I64, P, I64, I64, C.c_int]
+        L.tenmo_ref_vm.argtypes = [P, I64, P, I64, I64, P, I64, I64, C.c_int]
         _lib = L
     return _lib
 
@@ -271,18 +275,43 @@ def maxpool2d_bwd(g, argmax, in_shape) -> np.ndarray:
     return dx
 
 
-def softmax_fwd(x) -> np.ndarray:
-    """SoftmaxNdBuffer.softmax over the last axis (softmax.mojo:30-48): exp(x - max) / sum, in fp32."""
+def softmax_fwd(x, simd_width: int = 8) -> np.ndarray:
+    """SoftmaxNdBuffer.softmax over the last axis (softmax.mojo:30-48) through the C restatement: row max, exp,
+    the chunked Buffer.sum (buffers.mojo:1304-1333) and a division, all in fp32."""
     x = _f32(x)
-    e = np.exp(x - x.max(axis=-1, keepdims=True), dtype=np.float32)
-    return (e / e.sum(axis=-1, keepdims=True, dtype=np.float32)).astype(np.float32)
+    flat = x.reshape(-1, x.shape[-1])
+    y = np.empty_like(flat)
+    lib().tenmo_ref_softmax_fwd(_ptr(flat), _ptr(y), flat.shape[0], flat.shape[1], simd_width)
+    return y.reshape(x.shape)
 
 
-def softmax_bwd(g, y) -> np.ndarray:
+def softmax_bwd(g, y, simd_width: int = 8) -> np.ndarray:
     """SoftmaxBackwardDelegate (softmax.mojo:206-213): y * (g - sum(g * y))."""
     g, y = _f32(g), _f32(y)
-    gy = (g * y).sum(axis=-1, keepdims=True, dtype=np.float32)
-    return (y * (g - gy)).astype(np.float32)
+    gf, yf = g.reshape(-1, g.shape[-1]), y.reshape(-1, y.shape[-1])
+    dx = np.empty_like(gf)
+    lib().tenmo_ref_softmax_bwd(_ptr(gf), _ptr(yf), _ptr(dx), gf.shape[0], gf.shape[1], simd_width)
+    return dx.reshape(g.shape)
+
+
+def mv(M, v, contract_scalar: int = 1) -> np.ndarray:
+    """M[..., m, k] @ v[k] (matrixvector.mojo:205-285), a 1-D vector shared by every batch of M."""
+    M, v = _f32(M), _f32(v)
+    flat = M.reshape(-1, M.shape[-2], M.shape[-1])
+    out = np.empty(flat.shape[:2], np.float32)
+    m, k = flat.shape[1:]
+    for b in range(flat.shape[0]):
+        lib().tenmo_ref_mv(_ptr(flat[b]), k, 1, _ptr(v), 1, _ptr(out[b]), m, k, contract_scalar)
+    return out.reshape(M.shape[:-1])
+
+
+def vm(v, M, contract_scalar: int = 1) -> np.ndarray:
+    """v[k] @ M[k, n] (vectormatrix.mojo:210-340)."""
+    M, v = _f32(M), _f32(v)
+    k, n = M.shape
+    out = np.empty(n, np.float32)
+    lib().tenmo_ref_vm(_ptr(v), 1, _ptr(M), n, 1, _ptr(out), k, n, contract_scalar)
+    return out
 
 
 def colsum(x) -> np.ndarray:

@@ -573,4 +573,72 @@ void tenmo_ref_maxpool2d_bwd(const float* g, const int64_t* argmax, float* dx, i
         }
 }
 
+// ---- softmax over the last axis of a contiguous (M, C) matrix -------------------------------------------------
+// SoftmaxNdBuffer.softmax (softmax.mojo:30-48) = _softmax_components (:165-178: row max, x - max, exp) then
+// SumMeanReduction.sum over the suffix axis, whose fast path is Buffer.sum (sum_mean_reduction.mojo:109-141 ->
+// buffers.mojo:1304-1333): the row is walked in chunks of simd_width lanes, each chunk collapsed by reduce_add
+// (restated as a halving tree, the order LLVM's reassociating vector reduction takes) and added to a scalar
+// accumulator, then a scalar tail; finally exp / sum (a division, not a multiply by the reciprocal).
+static float buffer_sum(const float* x, int64_t n, int simd) {
+    float accum = 0.f;
+    const int64_t vend = (n / simd) * simd;
+    float lane[64];
+    for (int64_t i = 0; i < vend; i += simd) {
+        for (int l = 0; l < simd; ++l) lane[l] = x[i + l];
+        for (int w = simd / 2; w >= 1; w /= 2)
+            for (int l = 0; l < w; ++l) lane[l] = lane[l] + lane[l + w];
+        accum += lane[0];
+    }
+    for (int64_t i = vend; i < n; ++i) accum += x[i];
+    return accum;
+}
+
+void tenmo_ref_softmax_fwd(const float* x, float* y, int64_t M, int64_t C, int simd_width) {
+    const int simd = (simd_width == 16) ? 16 : 8;
+    std::vector<float> e((size_t)C);
+    for (int64_t i = 0; i < M; ++i) {
+        const float* row = x + i * C;
+        float mx = row[0];
+        for (int64_t j = 1; j < C; ++j) mx = row[j] > mx ? row[j] : mx;
+        for (int64_t j = 0; j < C; ++j) e[(size_t)j] = std::exp(row[j] - mx);
+        const float sum = buffer_sum(e.data(), C, simd);
+        for (int64_t j = 0; j < C; ++j) y[i * C + j] = e[(size_t)j] / sum;
+    }
+}
+
+// SoftmaxBackwardDelegate (softmax.mojo:206-213): gy = g * y; s = sum(gy) over the row (same Buffer.sum path);
+// dx = y * (g - s).
+void tenmo_ref_softmax_bwd(const float* g, const float* y, float* dx, int64_t M, int64_t C, int simd_width) {
+    const int simd = (simd_width == 16) ? 16 : 8;
+    std::vector<float> gy((size_t)C);
+    for (int64_t i = 0; i < M; ++i) {
+        for (int64_t j = 0; j < C; ++j) gy[(size_t)j] = g[i * C + j] * y[i * C + j];
+        const float s = buffer_sum(gy.data(), C, simd);
+        for (int64_t j = 0; j < C; ++j) dx[i * C + j] = y[i * C + j] * (g[i * C + j] - s);
+    }
+}
+
+// ---- matrix @ vector and vector @ matrix -------------------------------------------------------------------------
+// MatrixVectorMulNd.forward (matrixvector.mojo:269-282): out[i] = sum_j M[i,j] * v[j], one scalar accumulator per
+// output, j ascending, `accumulator += m_val * v_val` (contraction is the compiler's choice, hence the option).
+void tenmo_ref_mv(const float* Mx, int64_t m_s0, int64_t m_s1, const float* v, int64_t v_s, float* out, int64_t m,
+                  int64_t k, int contract) {
+    for (int64_t i = 0; i < m; ++i) {
+        float acc = 0.f;
+        for (int64_t j = 0; j < k; ++j) acc = scalar_site(Mx[i * m_s0 + j * m_s1], v[j * v_s], acc, contract != 0);
+        out[i] = acc;
+    }
+}
+// VectorMatmulNd.forward (vectormatrix.mojo:283-340): out[j] = sum_i v[i] * M[i,j]; the contiguous-row path keeps
+// simd_width outputs in one vector accumulator and walks i ascending (`accumulator += v_val * m_vec`), the strided
+// path does the same with scalars: either way every output is one i-ascending chain.
+void tenmo_ref_vm(const float* v, int64_t v_s, const float* Mx, int64_t m_s0, int64_t m_s1, float* out, int64_t k,
+                  int64_t n, int contract) {
+    for (int64_t j = 0; j < n; ++j) {
+        float acc = 0.f;
+        for (int64_t i = 0; i < k; ++i) acc = scalar_site(v[i * v_s], Mx[i * m_s0 + j * m_s1], acc, contract != 0);
+        out[j] = acc;
+    }
+}
+
 }  // extern "C"

@@ -125,6 +125,18 @@ void tenmo_ref_maxpool2d_fwd(const float* x, float* out, int64_t* argmax, int64_
 void tenmo_ref_maxpool2d_bwd(const float* g, const int64_t* argmax, float* dx, int64_t NC, int64_t H, int64_t W, int64_t Ho,
                              int64_t Wo);
 
+/* Softmax over the last axis of a contiguous (M, C) matrix (softmax.mojo:30-48,165-178; row sums in the chunked
+ * order of buffers.mojo:1304-1333 with simd_width lanes) and its backward y * (g - sum(g * y)) (softmax.mojo:206-213). */
+void tenmo_ref_softmax_fwd(const float* x, float* y, int64_t M, int64_t C, int simd_width);
+void tenmo_ref_softmax_bwd(const float* g, const float* y, float* dx, int64_t M, int64_t C, int simd_width);
+
+/* M[m,k] @ v[k] (matrixvector.mojo:269-282) and v[k] @ M[k,n] (vectormatrix.mojo:283-340): one ascending
+ * accumulation chain per output; strides in elements; contract as in tenmo_ref_opts. */
+void tenmo_ref_mv(const float* M, int64_t m_s0, int64_t m_s1, const float* v, int64_t v_s, float* out, int64_t m,
+                  int64_t k, int contract);
+void tenmo_ref_vm(const float* v, int64_t v_s, const float* M, int64_t m_s0, int64_t m_s1, float* out, int64_t k,
+                  int64_t n, int contract);
+
 #ifdef __cplusplus
 }
 #endif

@@ -107,3 +107,154 @@ CE_IGNORE_LS = dict(
 # tests/test_cross_entropy.mojo:724-742: uniform logits give -log(1/3); :1225-1241 closed form
 CE_UNIFORM = dict(logits=[[1.0, 1.0, 1.0], [1.0, 1.0, 1.0]], targets=[0, 1])
 CE_BASIC = dict(logits=[[2.0, 1.0, 0.5], [1.0, 2.0, 0.1]], targets=[0, 1])
+
+# ---- softmax over the last axis: tests/test_softmax.mojo ----------------------------------------------
+# Forward literals (fp32 tests, atol 1e-5): :320-330, :346-355 (CPU) and :590-600 (GPU).
+SOFTMAX_FWD = [
+    dict(name="cpu_1d_basic", x=[1.0, 2.0, 3.0], y=[0.09003057, 0.24472848, 0.66524094]),        # :320-330
+    dict(name="cpu_1d_negative", x=[-1.0, -2.0, -3.0], y=[0.66524094, 0.24472848, 0.09003057]),  # :346-355
+    dict(name="cpu_1d_uniform", x=[1.0, 1.0, 1.0, 1.0], y=[0.25, 0.25, 0.25, 0.25]),             # :332-337
+]
+# Inputs whose rows must each sum to 1 and stay in [0, 1] (verify_softmax_properties_*, :290-313): :339-344 (large
+# values), :367-372, :385-399 / :636-660 (3-D, last axis).
+SOFTMAX_ROWS_SUM_TO_ONE = [
+    [[1000.0, 1001.0, 1002.0]],
+    [[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]],
+    [[1.0, 2.0, 3.0], [4.0, 5.0, 6.0], [7.0, 8.0, 9.0], [1.0, 2.0, 3.0]],
+]
+# Gradient literals of the float64 tests.  The loss there is output.mse(target) = mean((y - t)^2)
+# (tensor.mojo:3101-3121), so the gradient that reaches the softmax node is 2 (y - t) / numel; "weights" entries use
+# loss = sum(y * w), whose upstream gradient is w.
+SOFTMAX_BWD = [
+    # :40-56
+    dict(name="1d_mse", x=[[0.1, 0.2, 0.3]], mse_target=[[0.0, 1.0, 0.0]],
+         dx=[[0.05957773470833636, -0.1486374678358427, 0.08905973312750633]]),
+    # :94-126 (axis 1 of a 2-D tensor = last axis)
+    dict(name="2d_axis1_mse", x=[[1.0, 2.0], [3.0, 4.0]], mse_target=[[0.0, 1.9], [2.9, 0.0]],
+         dx=[[0.14135246274290422, -0.1413524627429042], [-0.3305161770365907, 0.3305161770365907]]),
+    # :162-212 (axis 2 of a (2,2,2) tensor, rows flattened)
+    dict(name="3d_axis2_mse", x=[[1.0, 2.0], [3.0, 4.0], [5.0, 6.0], [7.0, 8.0]],
+         mse_target=[[1.0, 1.0], [3.0, 2.0], [3.0, 4.0], [5.0, 6.0]],
+         dx=[[-0.022714436918239593, 0.0227144369182396], [-0.07186742022860364, 0.07186742022860365],
+             [0.026438546392124458, -0.026438546392124486], [0.02643854639212449, -0.026438546392124406]]),
+    # :228-250
+    dict(name="2d_weighted_sum", x=[[0.5, 1.5], [2.5, 0.5]], weights=[[1.0, 0.0], [0.0, 1.0]],
+         dx=[[0.1966119332414562, -0.19661193324145623], [-0.10499358540343878, 0.10499358540343878]]),
+    # :427-434, :449-457: loss = sum(y) => gradient 0 everywhere
+    dict(name="sum_gives_zero", x=[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], weights=[[1.0, 1.0, 1.0], [1.0, 1.0, 1.0]],
+         dx=[[0.0, 0.0, 0.0], [0.0, 0.0, 0.0]]),
+]
+# The whole-matrix softmax of :129-159 (axes [0, 1]) is a last-axis softmax of the flattened matrix.
+SOFTMAX_BWD.append(dict(name="2d_all_axes_mse", x=[[1.0, 2.0, 3.0, 4.0]], mse_target=[[0.0, 1.9, 2.9, 0.0]],
+                        dx=[[0.0064955867864787, -0.06273006370483511, -0.2712241624609286, 0.3274586393792851]]))
+
+# ---- ReLU: tests/test_relu.mojo ---------------------------------------------------------------------------
+# (x, relu(x), gradient of sum(relu(x)) = the 0/1 mask).  :9-19, :22-56, :95-100, :169-177, :179-187, :189-196
+RELU = [
+    dict(x=[-1.0, 0.0, 1.0, 2.0], y=[0.0, 0.0, 1.0, 2.0], mask=[0.0, 0.0, 1.0, 1.0]),
+    dict(x=[[-1.0, 2.0, 0.0], [3.0, -4.0, 5.0]], y=[[0.0, 2.0, 0.0], [3.0, 0.0, 5.0]], mask=[[0.0, 1.0, 0.0], [1.0, 0.0, 1.0]]),
+    dict(x=[-3.0, 0.0, 2.0, -1.0, 5.0], y=[0.0, 0.0, 2.0, 0.0, 5.0], mask=[0.0, 0.0, 1.0, 0.0, 1.0]),
+    dict(x=[-1.0, 2.0, -3.0, 4.0], y=[0.0, 2.0, 0.0, 4.0], mask=[0.0, 1.0, 0.0, 1.0]),
+    dict(x=[0.0, 1.0, -1.0], y=[0.0, 1.0, 0.0], mask=[0.0, 1.0, 0.0]),      # exactly 0: mask 0 (x > 0 is false)
+    dict(x=[[-1.0, 2.0], [3.0, -4.0]], y=[[0.0, 2.0], [3.0, 0.0]], mask=[[0.0, 1.0], [1.0, 0.0]]),
+]
+
+# ---- Sigmoid: tests/test_sigmoid.mojo ------------------------------------------------------------------------
+# Forward (atol 1e-5): :31-38, :41-46; backward of sum(y) is y (1 - y): :89-98, :101-109 (atol 1e-5)
+SIGMOID = [
+    dict(x=[0.0, 100.0, -100.0, 1.0, -1.0], y=[0.5, 1.0, 0.0, 0.7310586, 0.2689414]),
+    dict(x=[[0.0, 1.0], [-1.0, 2.0]], y=[[0.5, 0.7310586], [0.2689414, 0.8807970]]),
+    dict(x=[[0.0, 2.0], [-2.0, 0.0]], y=[[0.5, 0.8807970], [0.1192030, 0.5]]),
+]
+
+# ---- sum reductions: tests/test_sum_mean.mojo ----------------------------------------------------------------
+# :99-106 sum over axis 0 (the bias-gradient reduction); :256-265 leading-axis reduction of a 3-D tensor (mean = sum/2)
+SUM_AXIS0 = [
+    dict(x=[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], out=[5.0, 7.0, 9.0]),
+    dict(x=[[1.0, 2.0, 3.0, 4.0], [5.0, 6.0, 7.0, 8.0]], out=[6.0, 8.0, 10.0, 12.0]),   # (2,2,2) viewed as (2,4): 2 * mean
+]
+
+# ---- bias-add broadcast: tests/test_broadcast.mojo:482-505 ((4,) + (3,4), loss = sum) -------------------------
+ADD_BROADCAST = dict(bias=[1.0, 2.0, 3.0, 4.0], x=[[1.0] * 4, [2.0] * 4, [3.0] * 4],
+                     out=[[2.0, 3.0, 4.0, 5.0], [3.0, 4.0, 5.0, 6.0], [4.0, 5.0, 6.0, 7.0]],
+                     dbias=[3.0, 3.0, 3.0, 3.0])      # each bias entry receives one unit per row
+
+# ---- matrix @ vector, vector @ matrix with gradients of sum(result): tests/test_mv.mojo, tests/test_vm.mojo ----
+MV = [
+    # tests/test_mv.mojo:14-45
+    dict(name="mv_no_batch", M=[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], v=[1.0, 2.0, 3.0], out=[14.0, 32.0],
+         dM=[[1.0, 2.0, 3.0], [1.0, 2.0, 3.0]], dv=[5.0, 7.0, 9.0]),
+    # tests/test_mv.mojo:84-126: M (2,2,2) @ v (2,)
+    dict(name="mv_batch_M", M=[[[1.0, 2.0], [3.0, 4.0]], [[5.0, 6.0], [7.0, 8.0]]], v=[1.0, 1.0],
+         out=[[3.0, 7.0], [11.0, 15.0]], dM=[[[1.0, 1.0], [1.0, 1.0]], [[1.0, 1.0], [1.0, 1.0]]], dv=[16.0, 20.0]),
+]
+VM = [
+    # tests/test_vm.mojo:15-48
+    dict(name="vm_no_batch", v=[1.0, 2.0, 3.0], M=[[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]], out=[22.0, 28.0],
+         dv=[3.0, 7.0, 11.0], dM=[[1.0, 1.0], [2.0, 2.0], [3.0, 3.0]]),
+]
+
+# ---- Conv2d: tests/test_cnn.mojo ---------------------------------------------------------------------------------
+# Forward cases as (image spec, kernel spec, bias, stride, dilation, pad) -> expected values at listed positions
+# ("full" = the whole output).  "arange1" fills 1, 2, 3, ... in row-major order; a number fills with that constant.
+CONV_FWD = [
+    # :860-903 known values
+    dict(name="known_values", x_shape=(1, 1, 3, 3), x="arange1", k=[[[[1.0, 0.0], [0.0, 1.0]]]], bias=None,
+         stride=1, dilation=1, pad=0, full=[[[[6.0, 8.0], [12.0, 14.0]]]]),
+    # :149-170 bias only
+    dict(name="bias_only", x_shape=(1, 1, 3, 3), x=0.0, k_shape=(2, 1, 2, 2), k=0.0, bias=[5.0, 10.0],
+         stride=1, dilation=1, pad=0, out_shape=(1, 2, 2, 2), channel_fill=[5.0, 10.0]),
+    # :173-193 multi-channel ones: 2 channels x 2x2 = 8
+    dict(name="multi_channel", x_shape=(1, 2, 4, 4), x=1.0, k_shape=(3, 2, 2, 2), k=1.0, bias=None,
+         stride=1, dilation=1, pad=0, out_shape=(1, 3, 3, 3), fill=8.0),
+    # :1298-1318 ones + bias 10 = 14
+    dict(name="with_bias", x_shape=(1, 1, 3, 3), x=1.0, k_shape=(1, 1, 2, 2), k=1.0, bias=[10.0],
+         stride=1, dilation=1, pad=0, out_shape=(1, 1, 2, 2), fill=14.0),
+    # :1321-1344 three input channels: 12
+    dict(name="three_in_channels", x_shape=(1, 3, 4, 4), x=1.0, k_shape=(1, 3, 2, 2), k=1.0, bias=None,
+         stride=1, dilation=1, pad=0, out_shape=(1, 1, 3, 3), fill=12.0),
+    # :1347-1379 three filters filled with 1, 2, 3: 4, 8, 12
+    dict(name="three_filters", x_shape=(1, 1, 4, 4), x=1.0, k_shape=(3, 1, 2, 2), k="filter_index_plus_1", bias=None,
+         stride=1, dilation=1, pad=0, out_shape=(1, 3, 3, 3), channel_fill=[4.0, 8.0, 12.0]),
+    # :1415-1437 stride 2 on 5x5 ones
+    dict(name="stride_2", x_shape=(1, 1, 5, 5), x=1.0, k_shape=(1, 1, 2, 2), k=1.0, bias=None,
+         stride=2, dilation=1, pad=0, out_shape=(1, 1, 2, 2), fill=4.0),
+    # :1440-1462 stride 3, 2.0 x 0.5
+    dict(name="stride_3", x_shape=(1, 1, 7, 7), x=2.0, k_shape=(1, 1, 2, 2), k=0.5, bias=None,
+         stride=3, dilation=1, pad=0, out_shape=(1, 1, 2, 2), fill=4.0),
+    # :1591-1616 dilation 2
+    dict(name="dilation_2", x_shape=(1, 1, 7, 7), x=1.0, k_shape=(1, 1, 3, 3), k=1.0, bias=None,
+         stride=1, dilation=2, pad=0, out_shape=(1, 1, 3, 3), fill=9.0),
+    # :1619-1643 dilation 3 (shape only in the reference; the value follows from 4 taps of 2.0 x 0.5)
+    dict(name="dilation_3", x_shape=(1, 1, 9, 9), x=2.0, k_shape=(1, 1, 2, 2), k=0.5, bias=None,
+         stride=1, dilation=3, pad=0, out_shape=(1, 1, 6, 6), fill=4.0),
+    # :1669-1703 stride 2, dilation 2, padding 2 on 8x8 ones
+    dict(name="stride_pad_dilation", x_shape=(1, 1, 8, 8), x=1.0, k_shape=(1, 1, 3, 3), k=1.0, bias=None,
+         stride=2, dilation=2, pad=2,
+         full=[[[[4.0, 6.0, 6.0, 4.0], [6.0, 9.0, 9.0, 6.0], [6.0, 9.0, 9.0, 6.0], [4.0, 6.0, 6.0, 4.0]]]]),
+    # :1976-1994 output 1x1
+    dict(name="output_1x1", x_shape=(1, 1, 3, 3), x=1.0, k_shape=(1, 1, 3, 3), k=1.0, bias=None,
+         stride=1, dilation=1, pad=0, full=[[[[9.0]]]]),
+    # :1650-1666, :1511-1532, :1934-1952, :1955-1973 shapes only
+    dict(name="stride_and_padding", x_shape=(1, 1, 5, 5), x=1.0, k_shape=(1, 1, 3, 3), k=1.0, bias=None,
+         stride=2, dilation=1, pad=1, out_shape=(1, 1, 3, 3)),
+    dict(name="padding_int", x_shape=(1, 1, 3, 3), x=1.0, k_shape=(1, 1, 2, 2), k=1.0, bias=None,
+         stride=1, dilation=1, pad=1, out_shape=(1, 1, 4, 4)),
+    dict(name="pointwise", x_shape=(1, 3, 4, 4), x=1.0, k_shape=(2, 3, 1, 1), k=1.0, bias=None,
+         stride=1, dilation=1, pad=0, out_shape=(1, 2, 4, 4), fill=3.0),
+    dict(name="large_kernel", x_shape=(1, 1, 10, 10), x=1.0, k_shape=(1, 1, 7, 7), k=1.0, bias=None,
+         stride=1, dilation=1, pad=0, out_shape=(1, 1, 4, 4), fill=49.0),
+]
+# :196-219 and :1382-1408: image b filled with b + 1, 2x2 ones kernel => 4 (b + 1)
+CONV_BATCH = dict(x_shape=(4, 1, 3, 3), k_shape=(1, 1, 2, 2), expect_first=[4.0, 8.0, 12.0, 16.0])
+# Backward with an upstream gradient of ones.
+CONV_BWD = [
+    # :1828-1852
+    dict(name="backward_simple", x_shape=(1, 1, 3, 3), x=1.0, k_shape=(1, 1, 2, 2), k=1.0, bias=[0.0],
+         stride=1, dilation=1, pad=0, dbias=[4.0], dx=[[[[1.0, 2.0, 1.0], [2.0, 4.0, 2.0], [1.0, 2.0, 1.0]]]],
+         dk=[[[[4.0, 4.0], [4.0, 4.0]]]]),
+    # :1706-1821 batch 2, 3 -> 4 channels, stride 2, padding 1, bias 0..3: every (out, in) kernel plane has the same gradient
+    dict(name="all_parameters", x_shape=(2, 3, 8, 8), x=1.0, k_shape=(4, 3, 3, 3), k=1.0, bias=[0.0, 1.0, 2.0, 3.0],
+         stride=2, dilation=1, pad=1, out_shape=(2, 4, 4, 4), dbias=[32.0, 32.0, 32.0, 32.0],
+         dk_plane=[[18.0, 24.0, 24.0], [24.0, 32.0, 32.0], [24.0, 32.0, 32.0]]),
+]

@@ -1,0 +1,143 @@
+"""The literals the reference's own tests hold for softmax, ReLU, Sigmoid, axis-0 sums, the bias add, matrix-vector
+products and Conv2d (tests/golden/reference_kat.py gives file:line), run through the CUDA entry points of the C ABI.
+The same entries pin the CPU oracle in test_oracle_reference_literals.py."""
+import numpy as np
+import pytest
+
+from tests.golden import reference_kat as kat
+from tests.test_oracle_reference_literals import (check_conv_backward, check_conv_forward, close, conv_case_operands, f32,
+                                                  softmax_upstream)
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def g():
+    from tests import gpu_util
+
+    gpu_util.handle()
+    return gpu_util
+
+
+def gpu_softmax(g, x):
+    x = f32(x)
+    xd, yd = g.dev(x), g.empty(*x.shape)
+    g.handle().softmax_fwd(xd.data_ptr(), x.shape[1], yd.data_ptr(), x.shape[0], x.shape[1])
+    return yd
+
+
+@pytest.mark.parametrize("case", kat.SOFTMAX_FWD, ids=lambda c: c["name"])
+def test_softmax_forward_literals(g, oracle, case):
+    y = g.host(gpu_softmax(g, [case["x"]]))
+    assert close(y[0], case["y"], 1e-6)
+    assert close(y, oracle.softmax_fwd(f32([case["x"]])), 2e-7)
+
+
+@pytest.mark.parametrize("rows", kat.SOFTMAX_ROWS_SUM_TO_ONE, ids=lambda r: f"{len(r)}x{len(r[0])}")
+def test_softmax_rows_are_distributions(g, rows):
+    y = g.host(gpu_softmax(g, rows))
+    assert np.all(np.isfinite(y)) and np.all((y >= 0) & (y <= 1))
+    assert np.all(np.abs(y.sum(axis=1, dtype=np.float64) - 1) < 1e-5)
+
+
+@pytest.mark.parametrize("case", kat.SOFTMAX_BWD, ids=lambda c: c["name"])
+def test_softmax_backward_literals(g, oracle, case):
+    yd = gpu_softmax(g, case["x"])
+    y = g.host(yd)
+    up = softmax_upstream(case, y)
+    dx = g.empty(*y.shape)
+    g.handle().softmax_bwd(yd.data_ptr(), g.dev(up).data_ptr(), dx.data_ptr(), y.shape[0], y.shape[1])
+    assert close(g.host(dx), case["dx"], 2e-7)
+    assert close(g.host(dx), oracle.softmax_bwd(up, y), 1e-7)
+
+
+@pytest.mark.parametrize("case", kat.RELU, ids=lambda c: str(len(np.ravel(c["x"]))))
+def test_relu_literals(g, case):
+    x = f32(case["x"])
+    xd, out, mask, dx = g.dev(x), g.empty(*x.shape), g.empty(*x.shape), g.empty(*x.shape)
+    h = g.handle()
+    h.relu_fwd(xd.data_ptr(), out.data_ptr(), mask.data_ptr(), x.size)
+    h.relu_bwd(g.dev(np.ones_like(x)).data_ptr(), mask.data_ptr(), dx.data_ptr(), x.size)
+    assert np.array_equal(g.host(out), f32(case["y"])) and np.array_equal(g.host(mask), f32(case["mask"]))
+    assert np.array_equal(g.host(dx), f32(case["mask"]))
+    # the same ReLU as the epilogue of a GEMM with the identity: out = relu(x . I), aux = mask
+    x2 = x.reshape(-1, x.shape[-1]) if x.ndim > 1 else x.reshape(1, -1)
+    from oracle import ref
+
+    c, aux, _ = g.gpu_matmul(ref.View.of(x2), ref.View.of(np.eye(x2.shape[1], dtype=np.float32)), act=1, want_aux=True)
+    assert np.array_equal(c.reshape(x.shape), f32(case["y"])) and np.array_equal(aux.reshape(x.shape), f32(case["mask"]))
+
+
+@pytest.mark.parametrize("case", kat.SIGMOID, ids=lambda c: str(len(np.ravel(c["x"]))))
+def test_sigmoid_literals(g, oracle, case):
+    x = f32(case["x"])
+    xd, y, dx = g.dev(x), g.empty(*x.shape), g.empty(*x.shape)
+    h = g.handle()
+    h.sigmoid_fwd(xd.data_ptr(), y.data_ptr(), x.size)
+    h.sigmoid_bwd(g.dev(np.ones_like(x)).data_ptr(), y.data_ptr(), dx.data_ptr(), x.size)
+    s = f32(case["y"])
+    assert close(g.host(y), s, 1e-6) and close(g.host(dx), s * (1 - s), 1e-6)
+    assert close(g.host(y), oracle.sigmoid_fwd(x), 2e-7)
+
+
+@pytest.mark.parametrize("case", kat.SUM_AXIS0, ids=lambda c: str(len(c["out"])))
+def test_sum_axis0_literals(g, case):
+    x = f32(case["x"])
+    out = g.empty(x.shape[1])
+    g.handle().colsum(g.dev(x).data_ptr(), x.shape[0], x.shape[1], x.shape[1], out.data_ptr())
+    assert np.array_equal(g.host(out), f32(case["out"]))
+
+
+def test_bias_add_broadcast_literals(g):
+    c = kat.ADD_BROADCAST
+    x, b = f32(c["x"]), f32(c["bias"])
+    out, db = g.empty(*x.shape), g.empty(b.size)
+    h = g.handle()
+    h.add_bias(g.dev(x).data_ptr(), g.dev(b).data_ptr(), out.data_ptr(), x.shape[0], x.shape[1])
+    h.colsum(g.dev(np.ones_like(x)).data_ptr(), x.shape[0], x.shape[1], x.shape[1], db.data_ptr())
+    assert np.array_equal(g.host(out), f32(c["out"])) and np.array_equal(g.host(db), f32(c["dbias"]))
+
+
+# ---- Conv2d ------------------------------------------------------------------------------------------------------
+def gpu_conv(g, x, k, b, stride, dilation, pad, grad=None):
+    from tenmo_b200.cnn import Conv2d
+
+    N, Cin, H, W = x.shape
+    Cout, _, kh, kw = k.shape
+    assert kh == kw
+    conv = Conv2d(g.handle(), N, Cin, H, W, Cout, kh, stride, dilation, pad, relu=False)
+    bias = b if b is not None else np.zeros(Cout, np.float32)
+    xd, kd, bd = g.dev(x), g.dev(k), g.dev(bias)
+    out = g.host(conv.forward(xd, kd, bd))
+    if grad is None:
+        return out
+    dW, db = g.empty(*k.shape), g.empty(Cout)
+    dx = conv.backward(g.dev(grad(out)), kd, dW, db)
+    return out, g.host(dx), g.host(dW), g.host(db)
+
+
+@pytest.mark.parametrize("case", kat.CONV_FWD, ids=lambda c: c["name"])
+def test_conv_forward_literals(g, oracle, case):
+    x, k, b = conv_case_operands(case)
+    out = gpu_conv(g, x, k, b, case["stride"], case["dilation"], case["pad"])
+    check_conv_forward(case, out)
+    assert np.array_equal(out, oracle.conv2d_fwd(x, k, b, stride=case["stride"], dilation=case["dilation"], pad=case["pad"]))
+
+
+def test_conv_batch_literals(g):
+    c = kat.CONV_BATCH
+    x = np.empty(c["x_shape"], np.float32)
+    for b in range(x.shape[0]):
+        x[b] = b + 1
+    out = gpu_conv(g, x, np.ones(c["k_shape"], np.float32), None, 1, 1, 0)
+    assert [float(out[b, 0, 0, 0]) for b in range(4)] == c["expect_first"]
+
+
+@pytest.mark.parametrize("case", kat.CONV_BWD, ids=lambda c: c["name"])
+def test_conv_backward_literals(g, case):
+    x, k, b = conv_case_operands(case)
+    out, dx, dk, db = gpu_conv(g, x, k, b, case["stride"], case["dilation"], case["pad"], grad=np.ones_like)
+    if "out_shape" in case:
+        assert out.shape == tuple(case["out_shape"])
+    check_conv_backward(case, dx, dk, db)  # small integers: every summation order gives the same bits
