@@ -43,8 +43,7 @@ def host_cores() -> int:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one-pass ncu captures of this file's own
-# workloads (profiles/gemm_tc_kernel_8192_dram_traffic.md, profiles/hbm_kernels_colsum_relu_bwd_dram_traffic.md).
-# A number taken under a profiler is never timed here; only the byte counts are carried over.
+# workloads.  A number taken under a profiler is never timed here; only the byte counts are carried over.
 NCU_TRAFFIC_BYTES = {
     ("gemm_tc_kernel", 8192): 4.822e9,
     ("colsum_split_kernel", 8192 * 4096): 134.6e6,
@@ -94,12 +93,31 @@ def cpu_baseline(budget_s: float = 20.0):
                 sample=f"one fwd+bwd at {size}^3 ({secs:.2f} s), oracle port of matmul_cpu.mojo, {threads} threads over row tiles")
 
 
+def gemm_workload_text(S: int) -> str:
+    return (f"fp32 GEMM fwd+bwd (C=A.B, dA=dC.B^T, dB=A^T.dC) at M=N=K={S}, N(0,1) seeded, "
+            f"transposes as stride views; 3xTF32: each input split into its lo plane once per step")
+
+
 def run_reference_arm(args):
+    """The reference's own CPU path (oracle port of matmul_cpu.mojo: the Mojo reference cannot be built here) on all
+    host threads.  Each step is one fwd+bwd at the requested size when the whole run is predicted to end within
+    --ref-budget seconds, else at the largest power-of-two size that does (TFLOP/s is a rate: the sample stands in
+    for the full size and the workload text says so)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = host_cores()
-    size = args.ref_size
+    cpu_fwd_bwd(512, threads)                                   # loads the oracle
+    probe = min(2048, args.size)                                # enough row tiles to occupy every thread
+    rate = 6.0 * probe ** 3 / cpu_fwd_bwd(probe, threads)      # flop/s, to predict the time of a step
+    runs = args.steps + args.warmup
+    size = args.size
+    if args.ref_size:
+        size = args.ref_size
+    else:
+        while size > 512 and 6.0 * size ** 3 / rate * runs > args.ref_budget:
+            size //= 2
+        size = 1 << (size.bit_length() - 1) if size != args.size else size
     for _ in range(args.warmup):
         cpu_fwd_bwd(size, threads)
     t0 = time.perf_counter()
@@ -109,11 +127,14 @@ def run_reference_arm(args):
     flops = 6.0 * size ** 3 * args.steps
     value = flops / dt / 1e12
     sample = f"each step = one fwd+bwd at {size}^3 on {threads} host threads (oracle port; the Mojo reference cannot be built here)"
+    workload = gemm_workload_text(args.size)
+    if size != args.size:
+        workload += f" [CPU arm: timed at {size}^3, extrapolated to {args.size}^3 as a rate]"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"fp32 GEMM fwd+bwd, CPU sample {size}^3 of the {args.size}^3 workload", "size": size},
+        "config": {"workload": workload, "size": args.size, "sample_size": size},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -209,6 +230,7 @@ def measure_mlps(h, rank, world, local_rank, timed, args):
     if "cnn" in legs:
         out["cnn"] = measure_cnn(h, rank, world, local_rank, timed, args, rng, gen)
     if "mnist_mlp" in legs and world == 1:
+        measure_mnist_mlp.no_cpu = args.no_cpu
         out["mnist_mlp"] = measure_mnist_mlp(h, local_rank, timed, uniform_init, gen)
     return out
 
@@ -298,24 +320,38 @@ def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen)
     tr.load_batch(Xh, yh)
     for _ in range(3):
         tr.step()
+    # The same three steps from the same weights on the same global batch at every N: the loss of the third step
+    # (mean over the ranks) and a checksum of the updated parameters make the data-parallel runs comparable.
+    check = training_check(tr, world, dev)
     ms = timed(tr.step, args.mlp_steps)
+    h.check_device_status()
+
+    loss_host = torch.zeros(args.mlp_steps + 1, dtype=torch.float32).pin_memory()
+    e2e_i = [0]
 
     def e2e_step():
-        tr.load_batch(Xh, yh)   # H2D of this rank's rows from pinned memory
+        tr.load_batch(Xh, yh)   # H2D of this rank's rows from pinned memory, on the copy stream, into the idle input set
         tr.step()
-        tr.loss.cpu()            # D2H read of the step's loss
+        loss_host[e2e_i[0] % loss_host.numel():e2e_i[0] % loss_host.numel() + 1].copy_(tr.loss, non_blocking=True)  # D2H of the loss
+        e2e_i[0] += 1
 
     e2e_step()
     ms_e2e = timed(e2e_step, args.mlp_steps)
+    h.check_device_status()
     flops = sum(2.0 * gb * dims[l] * dims[l + 1] * (3 if l > 0 else 2) for l in range(4))
     res = {
         "metric": "mlp_train_samples_per_s", "value": gb * args.mlp_steps / (ms * 1e-3), "unit": "samples/s",
         "ms_per_step": ms / args.mlp_steps, "tflops": flops * args.mlp_steps / (ms * 1e-3) / 1e12, "scaling": "strong",
         "global_batch": gb, "per_rank_batch": hi - lo, "allreduce_bytes_per_step": 0 if world == 1 else tr.numel * 4,
-        "e2e_value": gb * args.mlp_steps / (ms_e2e * 1e-3), "steps": args.mlp_steps,
+        "e2e_value": gb * args.mlp_steps / (ms_e2e * 1e-3), "e2e_ms_per_step": ms_e2e / args.mlp_steps,
+        "e2e_h2d_bytes_per_step": int(Xh.numel() * 4 + yh.numel() * 8) * world, "e2e_d2h_bytes_per_step": 4 * world,
+        "steps": args.mlp_steps, "check_after_3_steps": check,
         "config": "4096-4096-4096-4096-1000 Linear+ReLU, softmax-CE, fp32 (3xTF32 GEMMs), N(0,1) inputs, U(+-sqrt(6/in)) weights",
     }
     res["exchange"] = tr.exchange
+    if rank == 0 and world == 1 and not args.no_cpu:
+        res["cpu_baseline"] = cpu_mlp_baseline(dims, Ws, bs, Xg[:512].numpy(), yg[:512].numpy(), steps=2,
+                                               note="wide MLP, a 512-row sample of the 8192-row batch")
     if world > 1:
         import torch.distributed as dist
 
@@ -356,11 +392,13 @@ def measure_cnn(h, rank, world, local_rank, timed, args, rng, gen):
     cnn.load_batch(Xc, yc)
     for _ in range(3):
         cnn.step()
+    check = training_check(cnn, world, dev)
     ms = timed(cnn.step, args.mlp_steps)
+    h.check_device_status()
     res = {
         "metric": "cnn_train_samples_per_s", "value": gbc * args.mlp_steps / (ms * 1e-3), "unit": "samples/s",
         "ms_per_step": ms / args.mlp_steps, "scaling": "strong", "global_batch": gbc, "per_rank_batch": hi - lo,
-        "steps": args.mlp_steps,
+        "steps": args.mlp_steps, "check_after_3_steps": check,
         "config": "(256,3,32,32) U[0,1): conv3x3 3->32 pad1, ReLU, maxpool2, conv3x3 32->64 pad1, ReLU, maxpool2, "
                   "Linear 4096->10, softmax-CE, SGD momentum 0.9; convolutions as im2col + strict-fp32 GEMM",
     }
@@ -411,8 +449,192 @@ def measure_mnist_mlp(h, local_rank, timed, uniform_init, gen):
                   "(938 steps) of synthetic U[0,1) pixels, step replayed as a CUDA graph; latency-bound",
     }
     h.set_stream(torch.cuda.current_stream(local_rank).cuda_stream)
+    h.check_device_status()
+    if not getattr(measure_mnist_mlp, "no_cpu", False):
+        res["cpu_baseline"] = cpu_mlp_baseline(dims, Ws, bs, pool[:64 * 100].cpu().numpy().reshape(100, 64, 784),
+                                               labels[:64 * 100].cpu().numpy().reshape(100, 64), steps=100,
+                                               note="MNIST-shaped MLP, 100 steps of batch 64", threads=1)
     torch.cuda.nvtx.range_pop()
     return res
+
+
+def training_check(tr, world, dev):
+    """Loss of the step just run (mean over the ranks) and checksums of the parameters it left, identical inputs at
+    every N.  With the NCCL exchange the figures agree with one GPU to ~1e-5; with the peer-memory exchange every
+    rank must hold the same bits (max - min of the checksum over the ranks is reported and must be 0)."""
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.synchronize()
+    loss = tr.loss.detach().double().clone()
+    p64 = tr.P.detach().double()
+    sums = torch.stack([p64.sum(), p64.abs().sum()])
+    spread = 0.0
+    if world > 1:
+        dist.all_reduce(loss)
+        loss /= world
+        hi, lo = sums.clone(), sums.clone()
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        spread = float((hi - lo).abs().max().item())
+    return {"loss": float(loss.item()), "param_sum": float(sums[0].item()), "param_abs_sum": float(sums[1].item()),
+            "checksum_spread_over_ranks": spread}
+
+
+def cpu_mlp_baseline(dims, Ws, bs, X, y, steps, note, threads=None):
+    """The oracle's restated Linear/ReLU/cross-entropy/backward/SGD step loop (net.mojo:179-216, optim.mojo:123-158)
+    timed on the host's cores for a bounded number of steps; X is (rows, in) for one repeated batch or
+    (steps, rows, in) for a sequence of batches."""
+    from oracle import ref
+
+    threads = threads or host_cores()
+    mlp = ref.MLP(Ws, bs)
+    seq = X.ndim == 3
+    rows = X.shape[-2]
+    mlp.step(X[0] if seq else X, y[0] if seq else y, threads=threads)   # warm up (loads the library)
+    t0 = time.perf_counter()
+    for i in range(steps):
+        mlp.step(X[i] if seq else X, y[i] if seq else y, threads=threads)
+    dt = time.perf_counter() - t0
+    return {"value": rows * steps / dt, "unit": "samples/s", "cores": threads, "kind": "port",
+            "sample": f"{note}: {steps} steps in {dt:.2f} s through the oracle's MLP step ({threads} threads over row tiles)"}
+
+
+def measure_tf32_yardstick(S=8192, loop=30):
+    """A ruler, not part of the path: cuBLAS TF32 GEMMs (torch.matmul with TF32 allowed) at S^3 in this process, CUDA
+    events on the current stream -- the best single launch ("burst") and a back-to-back loop of `loop` launches
+    ("sustained", the like-for-like figure for a kernel timed inside a long step).  3xTF32 spends three tensor-core
+    products per fp32 product, so the roofline of the fp32-accurate GEMM is this figure / 3."""
+    import torch
+
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a, b = torch.randn(S, S, device="cuda"), torch.randn(S, S, device="cuda")
+        c = torch.empty(S, S, device="cuda")
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(loop):
+            torch.matmul(a, b, out=c)
+        e1.record()
+        torch.cuda.synchronize()
+        sustained_ms = e0.elapsed_time(e1) / loop
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    flop = 2.0 * S ** 3
+    del a, b, c
+    torch.cuda.empty_cache()
+    return {"burst": flop / (best * 1e-3) / 1e12, "sustained": flop / (sustained_ms * 1e-3) / 1e12, "size": S, "loop": loop,
+            "how": "torch.matmul fp32 with TF32 allowed (cuBLAS), CUDA events, same process"}
+
+
+def measure_simt_fp32(h, timed, S=8192, steps=4):
+    """The strict-fp32 arm at the headline size: fwd+bwd through the plain call with the SIMT algorithm, against
+    2 x 128 lanes x SMs x the SM clock sampled while it runs (time x clock, not the maximum clock)."""
+    import torch
+
+    from tenmo_b200 import ALGO_SIMT_FP32, make_mat
+
+    A, B, dC = (torch.randn(S, S, device="cuda") for _ in range(3))
+    C, dA, dB = (torch.empty(S, S, device="cuda") for _ in range(3))
+    mA, mB, mdC = (make_mat(t.data_ptr(), (S, S), (S, 1)) for t in (A, B, dC))
+    mBt, mAt = make_mat(B.data_ptr(), (S, S), (1, S)), make_mat(A.data_ptr(), (S, S), (1, S))
+
+    def step():
+        h.gemm(S, S, S, mA, mB, C.data_ptr(), algo=ALGO_SIMT_FP32)
+        h.gemm(S, S, S, mdC, mBt, dA.data_ptr(), algo=ALGO_SIMT_FP32)
+        h.gemm(S, S, S, mAt, mdC, dB.data_ptr(), algo=ALGO_SIMT_FP32)
+
+    for _ in range(2):
+        step()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    sampler.wait_first()
+    t0 = time.time()
+    ms = timed(step, steps)
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1)
+    kernel = h.gemm_last_kernel()
+    info = h.device_info()
+    mhz = clocks.get("sm_mhz") or info["sm_clock_khz"] / 1e3
+    peak = 2.0 * 128 * info["sm_count"] * mhz * 1e6 / 1e12
+    tflops = 6.0 * S ** 3 * steps / (ms * 1e-3) / 1e12
+    del A, B, dC, C, dA, dB
+    torch.cuda.empty_cache()
+    return {"tflops": tflops, "ms_per_step": ms / steps, "kernel": kernel, "size": S,
+            "roofline": {"bound": "fp32", "achieved": tflops, "peak": peak, "unit": UNIT, "frac": tflops / peak,
+                         "peak_note": f"2 x 128 lanes x {info['sm_count']} SMs x {mhz:.0f} MHz (median SM clock sampled during the run)"},
+            "clocks": clocks}
+
+
+def measure_attention(h, timed, steps=5):
+    """Attention-shaped batched products at full size, forward + backward, device-resident, on both kernels:
+    S = Q.K^T (K^T a stride view), P.V, and their four backward products, for 384 heads of (512, 64); plus
+    (32,512,768)@(1,768,768) with its two backward products.  The (384,512,512) score matrix is 403 MB: its traffic
+    bounds the 3xTF32 numbers, so the GB/s it moves at is reported beside the TFLOP/s."""
+    import torch
+
+    from tenmo_b200 import ALGO_SIMT_FP32, ALGO_TC_3XTF32, make_mat
+
+    BH, S, D = 384, 512, 64
+    f32 = dict(dtype=torch.float32, device="cuda")
+    q, k, v, dctx = (torch.randn(BH, S, D, **f32) * 0.125 for _ in range(4))
+    sc, dsc = torch.empty(BH, S, S, **f32), torch.randn(BH, S, S, **f32)
+    ctx, dq, dk, dv = (torch.empty(BH, S, D, **f32) for _ in range(4))
+    dp = torch.empty(BH, S, S, **f32)
+    b3 = lambda t, r, c, rs, cs: make_mat(t.data_ptr(), (BH, r, c), (t.stride(0), rs, cs))
+    out = {}
+    for name, algo in (("3xtf32", ALGO_TC_3XTF32), ("simt", ALGO_SIMT_FP32)):
+        def step():
+            h.gemm(S, S, D, b3(q, S, D, D, 1), b3(k, D, S, 1, D), sc.data_ptr(), algo=algo)        # scores = Q . K^T
+            h.gemm(S, D, S, b3(sc, S, S, S, 1), b3(v, S, D, D, 1), ctx.data_ptr(), algo=algo)      # ctx = P . V
+            h.gemm(S, D, S, b3(sc, S, S, 1, S), b3(dctx, S, D, D, 1), dv.data_ptr(), algo=algo)    # dV = P^T . dctx
+            h.gemm(S, S, D, b3(dctx, S, D, D, 1), b3(v, D, S, 1, D), dp.data_ptr(), algo=algo)     # dP = dctx . V^T
+            h.gemm(S, D, S, b3(dsc, S, S, S, 1), b3(k, S, D, D, 1), dq.data_ptr(), algo=algo)      # dQ = dS . K
+            h.gemm(S, D, S, b3(dsc, S, S, 1, S), b3(q, S, D, D, 1), dk.data_ptr(), algo=algo)      # dK = dS^T . Q
+
+        for _ in range(2):
+            step()
+        ms = timed(step, steps) / steps
+        flop = 6 * 2.0 * BH * S * S * D
+        # score-sized matrices moved per step: scores written, read by P.V and by dV, dP written, dS read twice
+        score_bytes = 6 * 4.0 * BH * S * S
+        out[name] = {"ms_per_step": ms, "tflops": flop / (ms * 1e-3) / 1e12, "score_matrix_gbs": score_bytes / (ms * 1e-3) / 1e9}
+    del q, k, v, dctx, sc, dsc, ctx, dq, dk, dv, dp
+    torch.cuda.empty_cache()
+    Bb, M, K, N = 32, 512, 768, 768
+    a, w, dc = torch.randn(Bb, M, K, **f32) * 0.05, torch.randn(1, K, N, **f32) * 0.05, torch.randn(Bb, M, N, **f32)
+    c, da, dw_full, dw = torch.empty(Bb, M, N, **f32), torch.empty(Bb, M, K, **f32), torch.empty(Bb, K, N, **f32), torch.empty(K, N, **f32)
+    for name, algo in (("3xtf32", ALGO_TC_3XTF32), ("simt", ALGO_SIMT_FP32)):
+        def step():
+            h.gemm(M, N, K, make_mat(a.data_ptr(), (Bb, M, K), (M * K, K, 1)), make_mat(w.data_ptr(), (1, K, N), (K * N, N, 1)),
+                   c.data_ptr(), algo=algo)
+            h.gemm(M, K, N, make_mat(dc.data_ptr(), (Bb, M, N), (M * N, N, 1)), make_mat(w.data_ptr(), (1, N, K), (K * N, 1, N)),
+                   da.data_ptr(), algo=algo)
+            h.gemm(K, N, M, make_mat(a.data_ptr(), (Bb, K, M), (M * K, 1, K)), make_mat(dc.data_ptr(), (Bb, M, N), (M * N, N, 1)),
+                   dw_full.data_ptr(), algo=algo)
+            h.colsum(dw_full.data_ptr(), Bb, K * N, K * N, dw.data_ptr())   # sum over the broadcast batch
+
+        for _ in range(2):
+            step()
+        ms = timed(step, steps) / steps
+        out[name]["broadcast_batched_ms_per_step"] = ms
+        out[name]["broadcast_batched_tflops"] = 6.0 * Bb * M * K * N / (ms * 1e-3) / 1e12
+    out["config"] = ("384 x (512,64).(64,512)-view then .(512,64) and the four backward products; "
+                     "(32,512,768)@(1,768,768) with dA and dB summed over the batch; N(0, 1/sqrt(64)) / N(0, 0.05^2) inputs")
+    h.check_device_status()
+    return out
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -597,6 +819,17 @@ def run_gpu_arm(args):
     del A, B, dC, C, dA, dB, host_in, host_out, sets, planes0
     torch.cuda.empty_cache()
     sweep = None if (args.no_sweep or world > 1) else measure_other_sizes(h, algo, timed)
+    extras = {}
+    if world == 1 and not args.no_extras:
+        yard = measure_tf32_yardstick(S)
+        extras["simt_fp32"] = measure_simt_fp32(h, timed, S)
+        extras["attention"] = measure_attention(h, timed)
+        hbm = {}
+        run_kernel_rooflines(args, h=h, collect=hbm)
+        extras["hbm_kernels"] = hbm
+        h.set_stream(stream.cuda_stream)
+    else:
+        yard = None
     mlp = None if args.no_mlp else measure_mlps(h, rank, world, local_rank, timed, args)
 
     flop_step = 6.0 * M * N * K
@@ -609,9 +842,17 @@ def run_gpu_arm(args):
         peak_note = "strict-FP32 SIMT peak = 2 x 128 lanes x SMs x max SM clock"
         kernel = last_kernel or "gemm_simt_kernel"
     else:
-        peak = peaks["bf16_sustained"] / 2.0 / 3.0
-        peak_note = (f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']:.1f} TFLOP/s / 2 (TF32 rate) / 3 "
-                     f"(three products per fp32 product); burst-based figure {peaks['bf16_burst'] / 6.0:.1f}")
+        peak_bf16 = peaks["bf16_sustained"] / 2.0 / 3.0
+        if yard:
+            peak = yard["sustained"] / 3.0
+            peak_note = (f"TF32 GEMM measured in this run (cuBLAS, {yard['loop']} back-to-back {yard['size']}^3 launches): "
+                         f"{yard['sustained']:.1f} TFLOP/s / 3 (three tensor-core products per fp32 product); best single launch "
+                         f"{yard['burst']:.1f} / 3 = {yard['burst'] / 3.0:.1f}; derived from the {peaks['source']} bf16 peak: "
+                         f"{peaks['bf16_sustained']:.1f} / 2 / 3 = {peak_bf16:.1f} sustained, {peaks['bf16_burst'] / 6.0:.1f} burst")
+        else:
+            peak = peak_bf16
+            peak_note = (f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']:.1f} TFLOP/s / 2 (TF32 rate) / 3 "
+                         f"(three products per fp32 product); burst-based figure {peaks['bf16_burst'] / 6.0:.1f}")
         kernel = last_kernel or "gemm_tc_kernel"
     achieved = (2.0 * M * N * K) / ((kernel_ms / max(n_kernel, 1)) * 1e-3) / 1e12 if n_kernel else None
 
@@ -621,8 +862,7 @@ def run_gpu_arm(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"fp32 GEMM fwd+bwd (C=A.B, dA=dC.B^T, dB=A^T.dC) at M=N=K={S}, N(0,1) seeded, "
-                                   f"transposes as stride views; 3xTF32: each input split into its lo plane once per step", "size": S, "algo": "3xtf32-tcgen05" if algo == 1 else "simt-fp32",
+            "config": {"workload": gemm_workload_text(S), "size": S, "algo": "3xtf32-tcgen05" if algo == 1 else "simt-fp32",
                        "parallelism": f"replicas x{world}", "l2": "inputs (3 x %.0f MB) exceed the 126 MB L2" % (S * S * 4 / 1e6)},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": 3 * S * S * 4, "d2h_bytes_per_step": 3 * S * S * 4,
@@ -635,6 +875,14 @@ def run_gpu_arm(args):
                          "traffic": NCU_TRAFFIC_BYTES.get((kernel, S)), "traffic_unit": "bytes per launch (ncu, dram read+write)",
                          "launches_timed": n_kernel, "avg_launch_ms": kernel_ms / max(n_kernel, 1), "peak_note": peak_note},
         }
+        if yard and algo == 1:
+            out["roofline"]["tf32_measured"] = yard["sustained"]
+            out["roofline"]["tf32_measured_burst"] = yard["burst"]
+            out["roofline"]["frac_of_bf16_derived_sustained"] = achieved / peak_bf16 if achieved else None
+            out["roofline"]["frac_of_bf16_derived_burst"] = achieved / (peaks["bf16_burst"] / 6.0) if achieved else None
+        out["e2e"]["pcie_note"] = ("805 MB each way per step and rank: the end-to-end figure is bound by the host link, and at N > 1 "
+                                   "all ranks share the host's memory and PCIe paths")
+        out.update(extras)
         if sweep:
             out["other_sizes"] = sweep
         if mlp:
@@ -650,16 +898,17 @@ def run_gpu_arm(args):
 # ---------------------------------------------------------------------------------------------------
 # HBM-bound kernels of the path against the bandwidth roofline
 # ---------------------------------------------------------------------------------------------------
-def run_kernel_rooflines(args):
-    """One JSON line per kernel: algorithmic bytes per launch / CUDA-event time, against the measured copy
-    bandwidth.  Shapes are the wide-MLP ones (per-rank batch 8192).  Every kernel cycles through enough
-    distinct buffers that the working set exceeds the 126 MB L2."""
+def run_kernel_rooflines(args, h=None, collect=None):
+    """One JSON line per kernel (or one entry of ``collect``): algorithmic bytes per launch / CUDA-event time, against
+    the measured copy bandwidth.  Shapes are the wide-MLP ones (per-rank batch 8192).  Every kernel cycles through
+    enough distinct buffers that the working set exceeds the 126 MB L2."""
     import torch
 
-    from tenmo_b200 import TenmoCuda
+    from tenmo_b200 import TenmoCuda, make_mat
 
-    torch.cuda.set_device(0)
-    h = TenmoCuda(0).require()
+    if h is None:
+        torch.cuda.set_device(0)
+        h = TenmoCuda(0).require()
     stream = torch.cuda.current_stream()
     h.set_stream(stream.cuda_stream)
     peaks = load_peaks()
@@ -677,11 +926,16 @@ def run_kernel_rooflines(args):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / iters
         gbs = alg_bytes / (ms * 1e-3) / 1e9
-        print(json.dumps({"kernel": name, "avg_launch_ms": ms, "roofline": {
+        entry = {"kernel": name, "avg_launch_ms": ms, "roofline": {
             "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
             "traffic": NCU_TRAFFIC_BYTES.get((name, 8192 * 4096)), "peak_note": f"{peaks['source']} copy bandwidth"},
             "algorithmic_bytes": alg_bytes,
-            "note": note}), flush=True)
+            "note": note}
+        if collect is not None:
+            collect[name] = {"gbs": gbs, "frac": gbs / peaks["hbm_gbs"], "avg_launch_ms": ms, "algorithmic_bytes": alg_bytes,
+                             "note": note}
+        else:
+            print(json.dumps(entry), flush=True)
 
     M, N, C = 8192, 4096, 1000
     R = 4  # rotating buffers: 4 x 134 MB
@@ -714,6 +968,19 @@ def run_kernel_rooflines(args):
     report("ce_bwd_kernel", 8.0 * M * C + 8.0 * M,
            lambda i: h.ce_bwd(sm[i % R].data_ptr(), labels.data_ptr(), True, M, C, -100, 0.0, 0, 0, valid.data_ptr(),
                               logits[i % R].data_ptr()))
+    del logits, sm
+    # matrix @ vector and vector @ matrix on a (65536, 4096) matrix (1 GB: larger than the L2 by itself)
+    Mr, Kc = 65536, 4096
+    A = torch.randn(Mr, Kc, **f32)
+    xv, yv = torch.randn(Kc, **f32), torch.empty(Mr, **f32)
+    xr, yc = torch.randn(Mr, **f32), torch.empty(Kc, **f32)
+    mA = make_mat(A.data_ptr(), (Mr, Kc), (Kc, 1))
+    report("gemv_kernel", 4.0 * Mr * Kc + 4.0 * (Mr + Kc), lambda i: h.gemv(Mr, Kc, mA, xv.data_ptr(), 1, yv.data_ptr()),
+           iters=20, note="y = A . x, A (65536, 4096) row-major")
+    report("vecmat_kernel", 4.0 * Mr * Kc + 4.0 * (Mr + Kc), lambda i: h.vecmat(Mr, Kc, xr.data_ptr(), 1, mA, yc.data_ptr()),
+           iters=20, note="y = x . A, A (65536, 4096) row-major")
+    del A
+    torch.cuda.empty_cache()
     h.check_device_status()
 
 
@@ -725,11 +992,14 @@ def main():
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--algo", choices=["tc", "simt"], default="tc")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--ref-size", type=int, default=2048, help="CPU sample size for --impl reference")
+    ap.add_argument("--ref-size", type=int, default=0, help="force the CPU sample size of --impl reference (0 = --size if it fits --ref-budget)")
+    ap.add_argument("--ref-budget", type=float, default=150.0, help="seconds the whole --impl reference run may take")
     ap.add_argument("--cpu-budget", type=float, default=20.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-mlp", action="store_true", help="skip the MLP training legs")
     ap.add_argument("--no-sweep", action="store_true", help="skip the smaller / skinny GEMM sizes of the same configuration")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the TF32 yardstick, the strict-fp32 arm, the attention shapes and the HBM-bound kernels")
     ap.add_argument("--mlp-steps", type=int, default=20)
     ap.add_argument("--dp-exchange", choices=["auto", "nccl", "p2p"], default="auto",
                     help="gradient exchange of the training legs at N > 1: NCCL all-reduce or the library's peer-memory kernel; "

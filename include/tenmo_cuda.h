@@ -159,6 +159,20 @@ const char* tenmo_gemm_last_kernel(tenmo_ctx* ctx);
  * it off.  No reference counterpart. */
 int tenmo_gemm_last_stream_k(tenmo_ctx* ctx);
 
+/* ---- matrix @ vector, vector @ matrix ---------------------------------------------------------------
+ * y[i] = sum_k A[i,k] x[k] (+ y[i] when beta == 1): MatrixVectorMulNd.forward (matrixvector.mojo:205-285), and
+ * y[j] = sum_k x[k] A[k,j]: VectorMatmulNd.forward (vectormatrix.mojo:210-340); with g in place of x they are also the
+ * vector gradients of the two backward passes (matrixvector.mojo:15-201, vectormatrix.mojo:14-206).  A is one
+ * (M,K) / (K,N) matrix view (batch_rank 0; a batched caller loops, as the reference's forward does) with a unit
+ * stride on at least one axis; x has element stride incx >= 1; y is contiguous.  HBM-bound kernels that read A once;
+ * sums are not in the reference's k-ascending order, so results agree with it to rounding (the bit-identical form is
+ * tenmo_gemm_f32 with a unit dimension and the strict-fp32 algorithm, which also serves a matrix without a
+ * unit-stride axis: these two return TENMO_ERR_UNSUPPORTED for it). */
+int tenmo_gemv_f32(tenmo_ctx* ctx, int64_t M, int64_t K, const tenmo_mat* A, const float* x, int64_t incx, float* y,
+                   float beta);
+int tenmo_vecmat_f32(tenmo_ctx* ctx, int64_t K, int64_t N, const float* x, int64_t incx, const tenmo_mat* A, float* y,
+                     float beta);
+
 /* ---- elementwise neighbours of the GEMM (un-fused forms, for a host that calls op by op) ---------- */
 /* out[m,n] = x[m,n] + bias[n]; Adder.forward bias case (addition.mojo:71-112,
  * binary_ops_kernel.mojo:778-807).  out may alias x. */
@@ -301,6 +315,20 @@ int tenmo_dp_finalize(tenmo_ctx* ctx);
 int tenmo_dp_p2p_alloc(tenmo_ctx* ctx, int64_t count, float** buf_out, void* handles_out, size_t handles_bytes);
 int tenmo_dp_p2p_connect(tenmo_ctx* ctx, int rank, int world, const void* all_handles, size_t handles_bytes);
 int tenmo_dp_p2p_allreduce_sum_f32(tenmo_ctx* ctx, int64_t offset, int64_t count);
+/* The exchange and SGD.step (optim.mojo:405-543) as one kernel with the optimiser sharded over the ranks.  The bucket
+ * holds the gradients of the range at [grad_offset, +count) and the parameters at [param_offset, +count) (disjoint
+ * ranges of the same allocation, so that the peers can read both).  Per call: every rank adds the W gradient copies of
+ * its shard in rank order, applies g' = g*grad_scale (+ p*wd); v = momentum*v + g'; p -= lr*v to its shard of the
+ * parameters -- the arithmetic of tenmo_sgd_step_f32, bit for bit -- and then copies the other ranks' updated shards,
+ * so every rank ends with identical parameters.  v: this rank's velocities for the range (count floats, device
+ * memory of the caller; only the own shard is read and written, so a rank holds the momentum of 1/W of the
+ * parameters).  p_lo / lo_count: optional 3xTF32 lo plane of the first lo_count updated parameters of the range,
+ * written as the parameters land (see tenmo_sgd_step_lo_f32).  The gradient range is left as it was.  Same rules as
+ * the all-reduce: same calls in the same order on every rank, one call in flight per context, bounded waits.
+ * Both kernels keep their call counter on the device, so a captured CUDA graph that contains them can be replayed. */
+int tenmo_dp_p2p_sgd_step_f32(tenmo_ctx* ctx, int64_t grad_offset, int64_t param_offset, int64_t count, float* v,
+                              float* p_lo, int64_t lo_count, float lr, float momentum, float weight_decay,
+                              float grad_scale);
 int tenmo_dp_p2p_close(tenmo_ctx* ctx);
 
 #ifdef __cplusplus

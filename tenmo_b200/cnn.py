@@ -16,6 +16,7 @@ import torch
 
 from . import lib as _lib
 from .lib import TenmoCuda, make_mat
+from .trainer import BatchFeed
 
 
 def out_size(n: int, k: int, stride: int, dilation: int, pad: int) -> int:
@@ -89,7 +90,7 @@ class MaxPool2d:
         return self.dx
 
 
-class CNNTrainer:
+class CNNTrainer(BatchFeed):
     """The CIFAR-shaped CNN of the reference's examples as one planned step: conv3x3(3->32, pad 1) + ReLU,
     maxpool 2, conv3x3(32->64, pad 1) + ReLU, maxpool 2, flatten (NCHW order), Linear 4096->10, softmax
     cross-entropy, SGD momentum.  Parameters, gradients and velocities live in flat buffers so that the
@@ -133,8 +134,7 @@ class CNNTrainer:
         self.feat = C2 * (hw // 4) * (hw // 4)
         self.classes = shapes[4][1]
         assert shapes[4][0] == self.feat, "fc.weight rows must equal the flattened feature count"
-        self.X = torch.zeros(B, shapes[0][1], hw, hw, **f32)
-        self.y = torch.zeros(B, dtype=torch.int64, device=f"cuda:{self.dev}")
+        self._feed_init((B, shapes[0][1], hw, hw), self.dev)   # two sets of input buffers (BatchFeed)
         self.logits = torch.empty(B, self.classes, **f32)
         self.softmax = torch.empty(B, self.classes, **f32)
         self.dlogits = torch.empty(B, self.classes, **f32)
@@ -146,19 +146,9 @@ class CNNTrainer:
             self.h.dp_init(rank, world, unique_id)
         torch.cuda.synchronize(self.dev)
 
-    def load_batch(self, X, y):
-        if not torch.is_tensor(X):
-            X = torch.from_numpy(np.ascontiguousarray(X, np.float32))
-        if not torch.is_tensor(y):
-            y = torch.from_numpy(np.ascontiguousarray(y, np.int64))
-        self.X.copy_(X, non_blocking=True)
-        self.y.copy_(y, non_blocking=True)
-
     def step(self, X=None, y=None, update: bool = True):
         h, B, C = self.h, self.batch, self.classes
-        h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
-        if X is not None:
-            self.load_batch(X, y)
+        self._begin_step(X, y)
         p, g = self.p, self.g
         a1 = self.pool1.forward(self.conv1.forward(self.X, p["conv1.weight"], p["conv1.bias"]))
         a2 = self.pool2.forward(self.conv2.forward(a1, p["conv2.weight"], p["conv2.bias"]))
@@ -183,6 +173,7 @@ class CNNTrainer:
                 h.dp_allreduce_sum(self.G.data_ptr(), self.numel)
             h.sgd_step([self.P.data_ptr()], [self.G.data_ptr()], [self.V.data_ptr()], [self.numel], self.lr, self.momentum,
                        0.0, 1.0 / self.world)
+        self._end_step()
 
     def close(self):
         """Release the data-parallel resources (every rank, after a host barrier)."""

@@ -65,7 +65,6 @@ struct tenmo_ctx {
     void* p2p_peer_buf[8] = {nullptr};
     void* p2p_peer_flags[8] = {nullptr};
     int64_t p2p_count = 0;
-    uint32_t p2p_epoch = 0;
     int p2p_rank = 0, p2p_world = 0;
 };
 

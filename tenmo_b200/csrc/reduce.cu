@@ -141,6 +141,28 @@ int tenmo_colsum_launch(tenmo_ctx* ctx, const float* x, int64_t M, int64_t N, in
     return TENMO_OK;
 }
 
+// Scratch of the split kernels: slabs*N partial sums (workspace) and one ticket counter per strip (kept at zero between calls).
+int tenmo_colsum_scratch(tenmo_ctx* ctx, int slabs, int64_t N, int strips, float** partials, unsigned int** tickets) {
+    void* ws = nullptr;
+    int st = tenmo_workspace(ctx, (size_t)slabs * (size_t)N * sizeof(float), &ws);
+    if (st != TENMO_OK) return st;
+    if (strips > ctx->tickets_cap) {
+        if (ctx->tickets) {
+            TENMO_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            cudaFree(ctx->tickets);
+            ctx->tickets = nullptr;
+            ctx->tickets_cap = 0;
+        }
+        const int cap = strips < 1024 ? 1024 : strips;
+        TENMO_CUDA_TRY(ctx, cudaMalloc(&ctx->tickets, (size_t)cap * sizeof(unsigned int)));
+        TENMO_CUDA_TRY(ctx, cudaMemset(ctx->tickets, 0, (size_t)cap * sizeof(unsigned int)));
+        ctx->tickets_cap = cap;
+    }
+    *partials = static_cast<float*>(ws);
+    *tickets = ctx->tickets;
+    return TENMO_OK;
+}
+
 extern "C" int tenmo_colsum_f32(tenmo_ctx* ctx, const float* x, int64_t M, int64_t N, int64_t ldx, float* out,
                                 float beta) {
     TENMO_CHECK_CTX(ctx);
@@ -159,24 +181,11 @@ extern "C" int tenmo_colsum_f32(tenmo_ctx* ctx, const float* x, int64_t M, int64
     const bool vec = (N % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
     int strips, slabs, rps;
     tenmo_colsum_plan(ctx->sm_count, M, N, vec, &strips, &slabs, &rps);
-    // scratch: slabs*N partial sums (workspace) and one ticket counter per strip (kept at zero between calls)
-    void* ws = nullptr;
-    int st = tenmo_workspace(ctx, (size_t)slabs * (size_t)N * sizeof(float), &ws);
+    float* partials = nullptr;
+    unsigned int* tickets = nullptr;
+    int st = tenmo_colsum_scratch(ctx, slabs, N, strips, &partials, &tickets);
     if (st != TENMO_OK) return st;
-    if (strips > ctx->tickets_cap) {
-        if (ctx->tickets) {
-            TENMO_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-            cudaFree(ctx->tickets);
-            ctx->tickets = nullptr;
-            ctx->tickets_cap = 0;
-        }
-        const int cap = strips < 1024 ? 1024 : strips;
-        TENMO_CUDA_TRY(ctx, cudaMalloc(&ctx->tickets, (size_t)cap * sizeof(unsigned int)));
-        TENMO_CUDA_TRY(ctx, cudaMemset(ctx->tickets, 0, (size_t)cap * sizeof(unsigned int)));
-        ctx->tickets_cap = cap;
-    }
-    unsigned int* tickets = ctx->tickets;
-    return tenmo_colsum_launch(ctx, x, M, N, ldx, out, beta, static_cast<float*>(ws), tickets, strips, slabs, rps, vec);
+    return tenmo_colsum_launch(ctx, x, M, N, ldx, out, beta, partials, tickets, strips, slabs, rps, vec);
 }
 
 // ---------------------------------------------------------------------------------------------------

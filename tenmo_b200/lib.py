@@ -25,13 +25,13 @@ EXPORTS = [
     "tenmo_cuda_init", "tenmo_cuda_destroy", "tenmo_cuda_last_error", "tenmo_cuda_version", "tenmo_cuda_set_stream",
     "tenmo_cuda_synchronize", "tenmo_cuda_device_info", "tenmo_cuda_check_device_status", "tenmo_cuda_launch_count",
     "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end", "tenmo_cuda_reserve_sms",
-    "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_gemm_last_kernel", "tenmo_gemm_last_stream_k", "tenmo_cuda_wait_probe", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
+    "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_gemv_f32", "tenmo_vecmat_f32", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_gemm_last_kernel", "tenmo_gemm_last_stream_k", "tenmo_cuda_wait_probe", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
     "tenmo_conv_out_size", "tenmo_im2col_f32", "tenmo_col2im_f32", "tenmo_channel_sum_f32", "tenmo_maxpool2d_fwd_f32",
     "tenmo_maxpool2d_bwd_f32",
     "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_ce_fwd_bwd_f32", "tenmo_sgd_step_f32", "tenmo_sgd_step_lo_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
     "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
-    "tenmo_dp_p2p_alloc", "tenmo_dp_p2p_connect", "tenmo_dp_p2p_allreduce_sum_f32", "tenmo_dp_p2p_close",
+    "tenmo_dp_p2p_alloc", "tenmo_dp_p2p_connect", "tenmo_dp_p2p_allreduce_sum_f32", "tenmo_dp_p2p_sgd_step_f32", "tenmo_dp_p2p_close",
 ]
 
 
@@ -105,6 +105,8 @@ def _bind(lib):
         "tenmo_cuda_profile_end": (I, [P, C.POINTER(I64), C.POINTER(C.c_double)]),
         "tenmo_gemm_f32": (I, [P, I, I64, I64, I64, C.POINTER(Mat), C.POINTER(Mat), P, F, P, I, P, P]),
         "tenmo_gemm_f32_ex": (I, [P, I, I64, I64, I64, C.POINTER(Mat), C.POINTER(Mat), P, C.POINTER(GemmOpts)]),
+        "tenmo_gemv_f32": (I, [P, I64, I64, C.POINTER(Mat), P, I64, P, F]),
+        "tenmo_vecmat_f32": (I, [P, I64, I64, P, I64, C.POINTER(Mat), P, F]),
         "tenmo_split_lo_f32": (I, [P, C.POINTER(Mat), I64, I64, P, I64]),
         "tenmo_gemm_last_algo": (I, [P]),
         "tenmo_gemm_last_kernel": (C.c_char_p, [P]),
@@ -140,6 +142,7 @@ def _bind(lib):
         "tenmo_dp_p2p_alloc": (I, [P, I64, C.POINTER(C.c_void_p), P, C.c_size_t]),
         "tenmo_dp_p2p_connect": (I, [P, I, I, P, C.c_size_t]),
         "tenmo_dp_p2p_allreduce_sum_f32": (I, [P, I64, I64]),
+        "tenmo_dp_p2p_sgd_step_f32": (I, [P, I64, I64, I64, P, P, I64, F, F, F, F]),
         "tenmo_dp_p2p_close": (I, [P]),
     }
     for name, (res, args) in sig.items():
@@ -241,6 +244,14 @@ class TenmoCuda:
         o = GemmOpts(beta, bias or None, act, aux or None, colsum or None, a_lo or None, b_lo or None, c_lo or None,
                      mul_mask or None, bias_m or None)
         self._call("tenmo_gemm_f32_ex", algo, M, N, K, C.byref(A), C.byref(B), c_ptr, C.byref(o))
+
+    def gemv(self, M, K, A: Mat, x, incx, y, beta=0.0):
+        """y[i] = sum_k A[i,k] x[k]: the HBM-bound matrix @ vector kernel (one matrix per call)."""
+        self._call("tenmo_gemv_f32", M, K, C.byref(A), x, incx, y, beta)
+
+    def vecmat(self, K, N, x, incx, A: Mat, y, beta=0.0):
+        """y[j] = sum_k x[k] A[k,j]: the HBM-bound vector @ matrix kernel (one matrix per call)."""
+        self._call("tenmo_vecmat_f32", K, N, x, incx, C.byref(A), y, beta)
 
     def split_lo(self, X: Mat, rows, cols, lo_out, capacity):
         self._call("tenmo_split_lo_f32", C.byref(X), rows, cols, lo_out, capacity)
@@ -382,6 +393,12 @@ class TenmoCuda:
 
     def dp_p2p_allreduce_sum(self, offset: int, count: int):
         self._call("tenmo_dp_p2p_allreduce_sum_f32", offset, count)
+
+    def dp_p2p_sgd_step(self, grad_offset: int, param_offset: int, count: int, v, p_lo, lo_count: int, lr, momentum=0.0,
+                        weight_decay=0.0, grad_scale=1.0):
+        """Exchange + SGD with the optimiser sharded over the ranks (gradients and parameters both live in the bucket)."""
+        self._call("tenmo_dp_p2p_sgd_step_f32", grad_offset, param_offset, count, v or None, p_lo or None, lo_count, lr,
+                   momentum, weight_decay, grad_scale)
 
     def dp_p2p_close(self):
         self._call("tenmo_dp_p2p_close")

@@ -330,6 +330,14 @@ class Tensor:
             code, la, lb, drop = BACKWARD_MATRIX_VECTOR_MUL, self.buffer, other.buffer.unsqueeze(len(b)), (-1,)
         if la.shape[-1] != lb.shape[-2]:
             panic("Matmul: incompatible shapes", a, b)
+        fast = self._rank1_hbm_kernel(other, kind)
+        if fast is not None:
+            out = Tensor(fast)
+            if track_grad and (self.requires_grad or other.requires_grad):
+                out.requires_grad = True
+                full_shape = tuple(la.shape[:-1]) + (lb.shape[-1],)
+                out.ancestry = Ancestry(code, [self, other], arg=dict(la=la, lb=lb, full_shape=full_shape))
+            return out
         full = la.matmul_nd(lb)
         shape = list(full.shape)
         for d in sorted((ax % len(shape) for ax in drop), reverse=True):
@@ -338,6 +346,27 @@ class Tensor:
         if track_grad and (self.requires_grad or other.requires_grad):
             out.requires_grad = True
             out.ancestry = Ancestry(code, [self, other], arg=dict(la=la, lb=lb, full_shape=full.shape))
+        return out
+
+    def _rank1_hbm_kernel(self, other: "Tensor", kind: str):
+        """Large unbatched matrix @ vector / vector @ matrix products go to the bandwidth-bound kernels
+        (tenmo_gemv_f32 / tenmo_vecmat_f32); small ones, batched ones and matrices without a unit-stride axis keep the
+        GEMM with a unit dimension, whose k-ascending chain is bit-identical to the reference's loops."""
+        if kind == "mv":
+            M, v = self.buffer, other.buffer
+        elif kind == "vm":
+            v, M = self.buffer, other.buffer
+        else:
+            return None
+        if len(M.shape) != 2 or len(v.shape) != 1 or M.numels() < (1 << 20) or 1 not in M.strides or v.strides[0] < 1:
+            return None
+        out = NDBuffer.empty((M.shape[0] if kind == "mv" else M.shape[1],))
+        mat = make_mat(M.storage.data_ptr(), M.shape, M.strides, M.offset)
+        vptr = v.storage.data_ptr() + 4 * v.offset
+        if kind == "mv":
+            handle().gemv(M.shape[0], M.shape[1], mat, vptr, v.strides[0], out.data_ptr())
+        else:
+            handle().vecmat(M.shape[0], M.shape[1], vptr, v.strides[0], mat, out.data_ptr())
         return out
 
     def __matmul__(self, other):

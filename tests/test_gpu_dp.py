@@ -32,7 +32,7 @@ def _problem():
     return Ws, bs, X, y
 
 
-def _worker(rank, world, port, out_dir, exchange):
+def _worker(rank, world, port, out_dir, mode):
     import sys
 
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -47,13 +47,17 @@ def _worker(rank, world, port, out_dir, exchange):
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
+        # mode = exchange[+tc][+graph]: "+tc" runs the 3xTF32 kernel (the sharded optimiser then also writes the weights'
+        # lo planes), "+graph" replays the captured step instead of enqueueing it
+        exchange, *flags = mode.split("+")
+        algo = "3xtf32" if "tc" in flags else "simt"
         h = TenmoCuda(rank).require()
         uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes()) if exchange == "nccl" else None
         Ws, bs, X, y = _problem()
         lo, hi = shard_rows(128, rank, world)
-        tr = MLPTrainer(Ws, bs, batch=hi - lo, lr=0.05, momentum=0.9, algo="simt", handle=h, rank=rank, world=world,
+        tr = MLPTrainer(Ws, bs, batch=hi - lo, lr=0.05, momentum=0.9, algo=algo, handle=h, rank=rank, world=world,
                         unique_id=uid, device=rank, exchange=exchange, all_gather_bytes=torch_all_gather_bytes())
-        if exchange == "p2p":
+        if exchange.startswith("p2p") and not flags:
             # the collective on its own: ragged ranges, every rank ends with the same bits = the sum in rank order
             g = torch.Generator(device="cpu").manual_seed(5 + rank)
             mine = torch.randn(tr.numel, generator=g)
@@ -76,11 +80,23 @@ def _worker(rank, world, port, out_dir, exchange):
             torch.cuda.synchronize()
             dist.barrier()
         losses = []
+        if "graph" in flags:
+            tr.load_batch(X[0, lo:hi], y[0, lo:hi])
+            dist.barrier()
+            tr.capture()     # two warm-up steps and the capture itself: every rank makes the same calls
+            torch.cuda.synchronize()
+            dist.barrier()
         for s in range(4):
-            tr.step(X[s, lo:hi], y[s, lo:hi])
+            if "graph" in flags:
+                tr.load_batch(X[s, lo:hi], y[s, lo:hi])
+                tr.replay()
+            else:
+                tr.step(X[s, lo:hi], y[s, lo:hi])
             losses.append(tr.loss_value())
         torch.cuda.synchronize()
         h.check_device_status()
+        vel = tr.state_dict()["__velocity__"]   # gathers the sharded momentum: every rank calls it
+        np.save(os.path.join(out_dir, f"v{rank}.npy"), vel)
         np.save(os.path.join(out_dir, f"w{rank}.npy"), np.concatenate([w.reshape(-1) for w in tr.weights() + tr.biases()]))
         np.save(os.path.join(out_dir, f"l{rank}.npy"), np.array(losses))
         dist.barrier()  # leave only between steps, with nothing in flight
@@ -90,17 +106,17 @@ def _worker(rank, world, port, out_dir, exchange):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
-def test_two_ranks_equal_one_rank_on_the_global_batch(tmp_path, exchange):
+@pytest.mark.parametrize("mode", ["nccl", "p2p", "p2p_allreduce", "p2p+tc", "p2p+graph", "nccl+graph"])
+def test_two_ranks_equal_one_rank_on_the_global_batch(tmp_path, mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
 
     from tenmo_b200.trainer import MLPTrainer
 
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), exchange), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), mode), nprocs=2, join=True)
     Ws, bs, X, y = _problem()
-    single = MLPTrainer(Ws, bs, batch=128, lr=0.05, momentum=0.9, algo="simt")
+    single = MLPTrainer(Ws, bs, batch=128, lr=0.05, momentum=0.9, algo="3xtf32" if "+tc" in mode else "simt")
     losses = []
     for s in range(4):
         single.step(X[s], y[s])
@@ -112,6 +128,47 @@ def test_two_ranks_equal_one_rank_on_the_global_batch(tmp_path, exchange):
     assert np.max(np.abs(w0 - ref)) <= 1e-5 * np.max(np.abs(ref))
     l0, l1 = np.load(tmp_path / "l0.npy"), np.load(tmp_path / "l1.npy")
     assert np.allclose((l0 + l1) / 2, losses, rtol=1e-5, atol=1e-6)  # mean of rank means == global mean
+    # the momentum buffers, gathered from the ranks that own them, are the single rank's
+    v0, v1 = np.load(tmp_path / "v0.npy"), np.load(tmp_path / "v1.npy")
+    vref = single.state_dict()["__velocity__"]
+    assert np.array_equal(v0, v1) and np.max(np.abs(v0 - vref)) <= 1e-5 * np.max(np.abs(vref))
+
+
+def test_sharded_optimiser_kernel_single_rank_matches_sgd_kernel():
+    """tenmo_dp_p2p_sgd_step_f32 with a world of one is SGD-momentum on the whole range: the parameters, velocities and
+    lo plane it leaves equal tenmo_sgd_step_lo_f32's bit for bit, on aligned and ragged ranges, over two steps."""
+    from tenmo_b200 import TenmoCuda
+    from tenmo_b200.parallel import DeviceFloats
+
+    h = TenmoCuda(0).require()
+    h.set_stream(torch.cuda.current_stream().cuda_stream)
+    n = 300_000
+    ptr, handles = h.dp_p2p_alloc(2 * n)
+    try:
+        h.dp_p2p_connect(0, 1, handles)
+        bucket = torch.as_tensor(DeviceFloats(ptr, 2 * n), device="cuda:0")
+        G, P = bucket[:n], bucket[n:]
+        gen = torch.Generator(device="cuda").manual_seed(3)
+        for off, cnt, lo_cnt in ((0, n, n), (1024, 70_001, 40_000), (4, 3, 3), (8, 100_003, 0)):
+            p0 = torch.randn(n, generator=gen, device="cuda")
+            v0 = torch.randn(n, generator=gen, device="cuda") * 0.1
+            P.copy_(p0)
+            V, lo = v0.clone(), torch.zeros(n, device="cuda")
+            rp, rv, rlo = p0.clone(), v0.clone(), torch.zeros(n, device="cuda")
+            for step in range(2):
+                g = torch.randn(n, generator=gen, device="cuda")
+                G.copy_(g)
+                h.dp_p2p_sgd_step(off, n + off, cnt, V.data_ptr() + 4 * off, lo.data_ptr() + 4 * off, lo_cnt, 0.05, 0.9, 0.01, 0.5)
+                h.sgd_step([rp.data_ptr() + 4 * off], [g.data_ptr() + 4 * off], [rv.data_ptr() + 4 * off], [cnt], 0.05, 0.9, 0.01, 0.5,
+                           lo_ptrs=[rlo.data_ptr() + 4 * off], lo_numels=[lo_cnt])
+                torch.cuda.synchronize()
+                assert torch.equal(P, rp) and torch.equal(V, rv) and torch.equal(lo, rlo), (off, cnt, step)
+                assert torch.equal(G, g)   # the gradient range is left alone
+        with pytest.raises(Exception):
+            h.dp_p2p_sgd_step(0, 10, 100, V.data_ptr(), 0, 0, 0.1, 0.9)   # overlapping ranges
+        h.check_device_status()
+    finally:
+        h.dp_p2p_close()
 
 
 def test_p2p_single_rank_and_argument_errors():

@@ -141,3 +141,88 @@ def test_conv_backward_literals(g, case):
     if "out_shape" in case:
         assert out.shape == tuple(case["out_shape"])
     check_conv_backward(case, dx, dk, db)  # small integers: every summation order gives the same bits
+
+
+# ---- matrix @ vector, vector @ matrix through the HBM-bound kernels -------------------------------------------------
+def gpu_gemv(g, M, v, beta=0.0, y0=None, transposed_storage=False):
+    """y = M . v through tenmo_gemv_f32; with transposed_storage the matrix is handed over as a stride view of its
+    transpose (column-major), which takes the other kernel."""
+    from tenmo_b200 import make_mat
+
+    M, v = f32(M), f32(v)
+    m, k = M.shape
+    if transposed_storage:
+        Md = g.dev(np.ascontiguousarray(M.T))
+        mat = make_mat(Md.data_ptr(), (m, k), (1, m))
+    else:
+        Md = g.dev(M)
+        mat = make_mat(Md.data_ptr(), (m, k), (k, 1))
+    y = g.dev(y0) if y0 is not None else g.empty(m)
+    g.handle().gemv(m, k, mat, g.dev(v).data_ptr(), 1, y.data_ptr(), beta)
+    return g.host(y)
+
+
+def gpu_vecmat(g, v, M, transposed_storage=False):
+    from tenmo_b200 import make_mat
+
+    M, v = f32(M), f32(v)
+    k, n = M.shape
+    if transposed_storage:
+        Md = g.dev(np.ascontiguousarray(M.T))
+        mat = make_mat(Md.data_ptr(), (k, n), (1, k))
+    else:
+        Md = g.dev(M)
+        mat = make_mat(Md.data_ptr(), (k, n), (n, 1))
+    y = g.empty(n)
+    g.handle().vecmat(k, n, g.dev(v).data_ptr(), 1, mat, y.data_ptr())
+    return g.host(y)
+
+
+@pytest.mark.parametrize("case", kat.MV, ids=lambda c: c["name"])
+@pytest.mark.parametrize("tr", [False, True], ids=["row_major", "col_major"])
+def test_mv_literals(g, case, tr):
+    M, v = f32(case["M"]), f32(case["v"])
+    flat = M.reshape(-1, *M.shape[-2:])
+    out = np.stack([gpu_gemv(g, Mb, v, transposed_storage=tr) for Mb in flat]).reshape(np.shape(case["out"]))
+    assert np.array_equal(out, f32(case["out"]))
+    # dv = sum over the batch of M_b^T . ones (matrixvector.mojo:15-201): the vecmat kernel with beta = 1 semantics
+    dv = sum(gpu_vecmat(g, np.ones(Mb.shape[0], np.float32), Mb, transposed_storage=tr) for Mb in flat)
+    assert np.array_equal(dv, f32(case["dv"]))
+
+
+@pytest.mark.parametrize("case", kat.VM, ids=lambda c: c["name"])
+@pytest.mark.parametrize("tr", [False, True], ids=["row_major", "col_major"])
+def test_vm_literals(g, case, tr):
+    v, M = f32(case["v"]), f32(case["M"])
+    assert np.array_equal(gpu_vecmat(g, v, M, transposed_storage=tr), f32(case["out"]))
+    assert np.array_equal(gpu_gemv(g, M, np.ones(M.shape[1], np.float32), transposed_storage=tr), f32(case["dv"]))
+
+
+@pytest.mark.parametrize("mk", [(1, 1), (3, 5), (37, 301), (513, 64), (1000, 1027), (4096, 4096), (130, 70000)], ids=str)
+@pytest.mark.parametrize("tr", [False, True], ids=["row_major", "col_major"])
+def test_gemv_vecmat_vs_oracle(g, oracle, mk, tr):
+    m, k = mk
+    rng = np.random.default_rng(m * 7 + k)
+    M = rng.standard_normal((m, k)).astype(np.float32)
+    v, u = rng.standard_normal(k).astype(np.float32), rng.standard_normal(m).astype(np.float32)
+    y0 = rng.standard_normal(m).astype(np.float32)
+    # the oracle's chain is k-ascending, the kernels' is not: same sum to rounding, bar 1e-5 of sum |a||x|
+    want = oracle.mv(M, v).astype(np.float64)
+    bound = np.abs(M).astype(np.float64) @ np.abs(v).astype(np.float64) + 1e-30
+    assert np.max(np.abs(gpu_gemv(g, M, v, transposed_storage=tr) - want) / bound) <= 1e-5
+    acc = gpu_gemv(g, M, v, beta=1.0, y0=y0, transposed_storage=tr)
+    assert np.max(np.abs(acc - (want + y0)) / (bound + np.abs(y0))) <= 1e-5
+    want_t = oracle.vm(u, M).astype(np.float64)
+    bound_t = np.abs(u).astype(np.float64) @ np.abs(M).astype(np.float64) + 1e-30
+    assert np.max(np.abs(gpu_vecmat(g, u, M, transposed_storage=tr) - want_t) / bound_t) <= 1e-5
+    # run to run the bits are the same (slab order, not arrival order)
+    assert np.array_equal(gpu_vecmat(g, u, M, transposed_storage=tr), gpu_vecmat(g, u, M, transposed_storage=tr))
+    g.handle().check_device_status()
+
+
+def test_gemv_rejects_a_matrix_without_a_unit_stride(g):
+    from tenmo_b200 import TenmoError, make_mat
+
+    A = g.dev(np.zeros((8, 16), np.float32))
+    with pytest.raises(TenmoError):
+        g.handle().gemv(4, 4, make_mat(A.data_ptr(), (4, 4), (32, 2)), g.empty(4).data_ptr(), 1, g.empty(4).data_ptr())
