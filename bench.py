@@ -278,7 +278,7 @@ def build_with_fallback(build, exchange, uid, h, rank, world, dev):
         return build(exchange, uid)
     tr, ok = None, 1
     try:
-        tr = build("p2p", None)
+        tr = build(exchange, None)
     except TenmoError as e:
         ok = 0
         print(f"rank {rank}: peer-memory exchange unavailable ({e}); using NCCL", file=sys.stderr, flush=True)
@@ -1001,7 +1001,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the TF32 yardstick, the strict-fp32 arm, the attention shapes and the HBM-bound kernels")
     ap.add_argument("--mlp-steps", type=int, default=20)
-    ap.add_argument("--dp-exchange", choices=["auto", "nccl", "p2p"], default="auto",
+    ap.add_argument("--dp-exchange", choices=["auto", "nccl", "p2p", "p2p_allreduce"], default="auto",
                     help="gradient exchange of the training legs at N > 1: NCCL all-reduce or the library's peer-memory kernel; "
                          "auto = peer-memory from 8 ranks up (measured: 17 %% faster at 8 ranks, 6 %% slower at 4, 5 %% slower at 2)")
     ap.add_argument("--legs", default="wide_mlp,cnn,mnist_mlp", help="which training legs to run after the GEMM arm")

@@ -15,7 +15,13 @@
  *   - Return value: TENMO_OK (0) or a negative tenmo_status; tenmo_cuda_last_error gives the message.
  *     Bad shapes / strides / alignment are rejected on the host before any launch.  Nothing aborts.
  *   - There is no CPU fallback: a layout the tensor-core kernel cannot take runs on the SIMT GPU kernel.
- *   - One host thread per context.
+ *   - One host thread per context, and one stream at a time: a context owns ONE workspace, one status / ticket block
+ *     and one set of stream-K fix-up flags, so calls that use them (the GEMMs, the column sums, cross-entropy) must
+ *     not be in flight on two streams of the same context at once.  Rebinding the context to another stream between
+ *     calls is fine when the streams are ordered by events (a side stream that only runs the gradient exchange and
+ *     the optimiser, as the trainers do); the library waits for the eight most recently bound streams before it
+ *     frees and regrows the workspace and before it reads the status word.  A call that must grow the workspace while
+ *     its stream is being captured into a CUDA graph returns TENMO_ERR_STATE: run it once outside the capture first.
  */
 #ifndef TENMO_CUDA_H
 #define TENMO_CUDA_H
@@ -44,7 +50,7 @@ typedef enum {
  * Replaces tenmo's GPU/DeviceContext wrapper (device.mojo:87-90) for the purposes of this path. */
 int tenmo_cuda_init(int device, tenmo_ctx** out);
 void tenmo_cuda_destroy(tenmo_ctx* ctx);
-const char* tenmo_cuda_last_error(tenmo_ctx* ctx); /* ctx may be NULL: returns the last init error */
+const char* tenmo_cuda_last_error(tenmo_ctx* ctx); /* ctx may be NULL: the calling thread's last error from a call without a context */
 const char* tenmo_cuda_version(void);
 /* Stream handle of the caller's DeviceContext (a cudaStream_t, taken verbatim: NULL is CUDA's default
  * stream).  A new context runs on a stream of its own; TENMO_STREAM_OWN selects that one again. */
@@ -206,8 +212,11 @@ int tenmo_colsum_f32(tenmo_ctx* ctx, const float* x, int64_t M, int64_t N, int64
  *   - Limit: N <= 16384 columns (any M, any ldx >= N); beyond that it returns TENMO_ERR_UNSUPPORTED and
  *     tenmo_cuda_last_error(NULL) says so.
  *   - Runs on the CURRENT device, on `cuda_stream` (a cudaStream_t; NULL = default stream).
- *   - The first call on each device resolves the array's device address; make that first call outside
- *     any stream capture.
+ *   - The first call on each device is the set-up call: it resolves the array's device address
+ *     (cudaGetSymbolAddress), which under CUDA's lazy module loading is also the moment the module is loaded
+ *     and the array comes into existence on that device, so that one call may synchronise the device.  Make it
+ *     during start-up, outside any stream capture; every later call allocates and synchronises nothing.  The
+ *     set-up is safe to race from several host threads.
  *   - All calls share the one array.  What must start at zero is cleared on the stream before each
  *     launch, but two calls whose kernels overlap on the GPU (different streams) race on it. */
 int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int64_t ldx, float* out, float beta,

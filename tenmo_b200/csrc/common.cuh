@@ -19,6 +19,7 @@
 #define TENMO_DEV_STATUS_WORDS 512
 #define TENMO_SK_FLAG_WORD0 256
 #define TENMO_SK_MAX_UNITS 256
+#define TENMO_MAX_BOUND_STREAMS 8
 
 struct tenmo_ctx {
     int device = 0;
@@ -28,6 +29,8 @@ struct tenmo_ctx {
     size_t smem_optin = 0;
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
+    cudaStream_t bound[8] = {nullptr};  // streams the context has been bound to, most recent first (tenmo_cuda_set_stream)
+    int n_bound = 0;
     char err[512] = {0};
     int64_t launches = 0;
     int last_gemm_algo = -1;

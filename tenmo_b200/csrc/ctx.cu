@@ -1,7 +1,8 @@
 // Context lifetime, error strings, stream binding, workspace.
 #include "common.cuh"
 
-static char g_init_error[512] = {0};
+// errors of calls that have no context (tenmo_cuda_init, tenmo_colsum_f32_static): one buffer per host thread
+static thread_local char g_init_error[512] = {0};
 
 int tenmo_set_error(tenmo_ctx* ctx, int status, const char* fmt, ...) {
     char* dst = ctx ? ctx->err : g_init_error;
@@ -12,11 +13,26 @@ int tenmo_set_error(tenmo_ctx* ctx, int status, const char* fmt, ...) {
     return status;
 }
 
+// Waits for every stream this context has been bound to (work that uses the workspace, the status block or the
+// tickets may be queued on any of them).
+static cudaError_t sync_bound_streams(tenmo_ctx* ctx) {
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    for (int i = 0; i < ctx->n_bound && e == cudaSuccess; ++i)
+        if (ctx->bound[i] != ctx->stream) e = cudaStreamSynchronize(ctx->bound[i]);
+    return e;
+}
+
 int tenmo_workspace(tenmo_ctx* ctx, size_t bytes, void** out) {
     if (bytes > ctx->ws_bytes) {
-        // Grow: the old block may still be in use by work queued on the stream.
+        // Growing frees the old block and allocates: neither is allowed while the stream records a CUDA graph.
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(ctx->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return tenmo_set_error(ctx, TENMO_ERR_STATE,
+                                   "the workspace must grow to %zu bytes but the stream is capturing: run the call once outside the capture first",
+                                   bytes);
+        // The old block may still be in use by work queued on any stream the context was bound to.
         if (ctx->ws) {
-            cudaError_t e = cudaStreamSynchronize(ctx->stream);
+            cudaError_t e = sync_bound_streams(ctx);
             if (e != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "workspace sync: %s", cudaGetErrorString(e));
             cudaFree(ctx->ws);
             ctx->ws = nullptr;
@@ -147,6 +163,16 @@ const char* tenmo_cuda_last_error(tenmo_ctx* ctx) { return ctx ? ctx->err : g_in
 int tenmo_cuda_set_stream(tenmo_ctx* ctx, void* cuda_stream) {
     TENMO_CHECK_CTX(ctx);
     ctx->stream = cuda_stream == TENMO_STREAM_OWN ? ctx->own_stream : (cudaStream_t)cuda_stream;
+    // remember the streams the context has run on (most recent first): a workspace growth and the status check wait for them
+    int at = -1;
+    for (int i = 0; i < ctx->n_bound; ++i)
+        if (ctx->bound[i] == ctx->stream) at = i;
+    if (at < 0) {
+        if (ctx->n_bound < TENMO_MAX_BOUND_STREAMS) ++ctx->n_bound;
+        at = ctx->n_bound - 1;
+    }
+    for (int i = at; i > 0; --i) ctx->bound[i] = ctx->bound[i - 1];
+    ctx->bound[0] = ctx->stream;
     return TENMO_OK;
 }
 
@@ -176,7 +202,7 @@ int tenmo_cuda_device_info(tenmo_ctx* ctx, int* sm_count, int* cc_major, int* cc
 int tenmo_cuda_check_device_status(tenmo_ctx* ctx) {
     TENMO_CHECK_CTX(ctx);
     uint32_t word = 0;
-    TENMO_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    TENMO_CUDA_TRY(ctx, sync_bound_streams(ctx));
     TENMO_CUDA_TRY(ctx, cudaMemcpy(&word, ctx->dev_status, sizeof(word), cudaMemcpyDeviceToHost));
     if (word) {
         // an abandoned kernel may have left its tickets and tile counters dirty: clear the whole block

@@ -32,7 +32,15 @@ __device__ __forceinline__ void ew_apply(float a, float b, float old, float old2
     else { o = __fmul_rn(__fmul_rn(a, b), 1.f - b); if (p.beta != 0.f) o += old; }  // (g*y)*(1-y)
 }
 
-template <int OP>
+// NC: the inputs may be read through the non-coherent path (ld.global.nc).  That is only defined for memory the
+// kernel does not write, so an in-place call (an input aliasing an output, e.g. relu_bwd(g, mask, g)) takes the
+// instantiation with plain loads.
+template <bool NC, typename T>
+__device__ __forceinline__ T ew_load(const T* p) {
+    return NC ? __ldg(p) : *p;
+}
+
+template <int OP, bool NC>
 __global__ void __launch_bounds__(EW_THREADS) ew_kernel(const EwArgs p, const int vec_ok) {
     constexpr bool READ_A = OP != EW_FILL;
     constexpr bool READ_B = OP == EW_RELU_BWD || OP == EW_SIGMOID_BWD;
@@ -42,8 +50,8 @@ __global__ void __launch_bounds__(EW_THREADS) ew_kernel(const EwArgs p, const in
     const int64_t n4 = vec_ok ? p.n / 4 : 0;
     for (int64_t i = tid; i < n4; i += stride) {
         float4 a = make_float4(0, 0, 0, 0), b = a, old = a, o, o2;
-        if (READ_A) a = __ldg(reinterpret_cast<const float4*>(p.a) + i);
-        if (READ_B) b = __ldg(reinterpret_cast<const float4*>(p.b) + i);
+        if (READ_A) a = ew_load<NC>(reinterpret_cast<const float4*>(p.a) + i);
+        if (READ_B) b = ew_load<NC>(reinterpret_cast<const float4*>(p.b) + i);
         if (read_old) old = reinterpret_cast<const float4*>(p.out)[i];
         ew_apply<OP>(a.x, b.x, old.x, 0.f, p, o.x, o2.x);
         ew_apply<OP>(a.y, b.y, old.y, 0.f, p, o.y, o2.y);
@@ -54,8 +62,8 @@ __global__ void __launch_bounds__(EW_THREADS) ew_kernel(const EwArgs p, const in
     }
     for (int64_t i = n4 * 4 + tid; i < p.n; i += stride) {
         float a = 0.f, b = 0.f, old = 0.f, o, o2;
-        if (READ_A) a = __ldg(p.a + i);
-        if (READ_B) b = __ldg(p.b + i);
+        if (READ_A) a = ew_load<NC>(p.a + i);
+        if (READ_B) b = ew_load<NC>(p.b + i);
         if (read_old) old = p.out[i];
         ew_apply<OP>(a, b, old, 0.f, p, o, o2);
         p.out[i] = o;
@@ -64,21 +72,23 @@ __global__ void __launch_bounds__(EW_THREADS) ew_kernel(const EwArgs p, const in
 }
 
 // out[m,n] = x[m,n] + bias[n]
-__global__ void __launch_bounds__(EW_THREADS) add_bias_kernel(const float* __restrict__ x, const float* __restrict__ bias,
-                                                             float* __restrict__ out, int64_t M, int64_t N, int vec_ok) {
+// x and out may be the same buffer (each element is read and then written by the same thread), so x is read with
+// plain loads and neither pointer is declared restrict.
+__global__ void __launch_bounds__(EW_THREADS) add_bias_kernel(const float* x, const float* __restrict__ bias,
+                                                             float* out, int64_t M, int64_t N, int vec_ok) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t total = M * N;
     if (vec_ok) {  // N % 4 == 0: a float4 never straddles a row
         const int64_t n4 = total / 4, row4 = N / 4;
         for (int64_t i = tid; i < n4; i += stride) {
-            float4 v = __ldg(reinterpret_cast<const float4*>(x) + i);
+            float4 v = reinterpret_cast<const float4*>(x)[i];
             const float4 b = __ldg(reinterpret_cast<const float4*>(bias) + (i % row4));
             v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
             reinterpret_cast<float4*>(out)[i] = v;
         }
     } else {
-        for (int64_t i = tid; i < total; i += stride) out[i] = __ldg(x + i) + __ldg(bias + (i % N));
+        for (int64_t i = tid; i < total; i += stride) out[i] = x[i] + __ldg(bias + (i % N));
     }
 }
 
@@ -93,7 +103,13 @@ int launch_ew(tenmo_ctx* ctx, const EwArgs& p, const char* name) {
     const int vec_ok = al16(p.a) && al16(p.b) && al16(p.out) && al16(p.out2);
     const int grid = tenmo_stream_grid(ctx, p.n, EW_THREADS * 4 * 4, 8);
     TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    ew_kernel<OP><<<grid, EW_THREADS, 0, ctx->stream>>>(p, vec_ok);
+    // inputs that overlap an output anywhere are read coherently (exact aliasing is the supported in-place form)
+    auto overlaps = [&](const float* in, const float* out) {
+        return in && out && in < out + p.n && out < in + p.n;
+    };
+    const bool aliased = overlaps(p.a, p.out) || overlaps(p.b, p.out) || overlaps(p.a, p.out2) || overlaps(p.b, p.out2);
+    if (aliased) ew_kernel<OP, false><<<grid, EW_THREADS, 0, ctx->stream>>>(p, vec_ok);
+    else ew_kernel<OP, true><<<grid, EW_THREADS, 0, ctx->stream>>>(p, vec_ok);
     TENMO_LAUNCH_CHECK(ctx, name);
     return TENMO_OK;
 }

@@ -8,6 +8,8 @@
 //   * many rows: the rows are split over CTAs; each CTA reduces its slab of a 128-column strip and
 //     parks a partial in scratch memory, and the last CTA of a strip to finish (ticket counter) adds
 //     the partials in slab order, so the result does not depend on scheduling.
+#include <atomic>
+
 #include "common.cuh"
 #include "reduce.cuh"
 
@@ -211,8 +213,11 @@ static __device__ __align__(256) unsigned int tenmo_static_scratch[TENMO_STATIC_
 
 namespace {
 constexpr int STATIC_MAX_DEVICES = 64;
-void* g_static_scratch_addr[STATIC_MAX_DEVICES] = {nullptr};  // per device, filled on its first call
-int g_static_sm_count[STATIC_MAX_DEVICES] = {0};
+// Per device, published by its first call: the SM count is written first and the address is stored with release
+// order, so a thread that reads a non-null address (acquire) also sees the SM count.  Two threads that race through
+// the set-up both resolve the same address and store the same values.
+std::atomic<void*> g_static_scratch_addr[STATIC_MAX_DEVICES];
+std::atomic<int> g_static_sm_count[STATIC_MAX_DEVICES];
 }  // namespace
 
 extern "C" int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int64_t ldx, float* out, float beta,
@@ -233,7 +238,8 @@ extern "C" int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int
     if (e != cudaSuccess) return tenmo_set_error(nullptr, TENMO_ERR_CUDA, "colsum_static: cudaGetDevice: %s", cudaGetErrorString(e));
     if (dev < 0 || dev >= STATIC_MAX_DEVICES)
         return tenmo_set_error(nullptr, TENMO_ERR_UNSUPPORTED, "colsum_static: device ordinal %d is beyond %d", dev, STATIC_MAX_DEVICES);
-    if (!g_static_scratch_addr[dev]) {
+    void* scratch = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!scratch) {
         // Set-up, once per device, with that device current: resolve the module's array to a device address.
         void* addr = nullptr;
         e = cudaGetSymbolAddress(&addr, tenmo_static_scratch);
@@ -243,8 +249,9 @@ extern "C" int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int
         e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess || sms <= 0)
             return tenmo_set_error(nullptr, TENMO_ERR_CUDA, "colsum_static: SM count query: %s", cudaGetErrorString(e));
-        g_static_sm_count[dev] = sms;
-        g_static_scratch_addr[dev] = addr;
+        g_static_sm_count[dev].store(sms, std::memory_order_relaxed);
+        g_static_scratch_addr[dev].store(addr, std::memory_order_release);
+        scratch = addr;
     }
     if (M <= TENMO_COLSUM_SEQ_ROWS) {  // few rows: one thread per column, no scratch at all
         const int grid = (int)((N + CS_THREADS - 1) / CS_THREADS);
@@ -255,7 +262,7 @@ extern "C" int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int
     }
     const bool vec = (N % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
     int strips, slabs, rps;
-    tenmo_colsum_plan(g_static_sm_count[dev], M, N, vec, &strips, &slabs, &rps);
+    tenmo_colsum_plan(g_static_sm_count[dev].load(std::memory_order_relaxed), M, N, vec, &strips, &slabs, &rps);
     if (slabs > TENMO_STATIC_MAX_SLABS) {  // fewer, taller slabs so that the partials fit
         const int64_t rows = (M + TENMO_STATIC_MAX_SLABS - 1) / TENMO_STATIC_MAX_SLABS;
         rps = (int)((rows + CS_WARPS - 1) / CS_WARPS * CS_WARPS);
@@ -263,8 +270,8 @@ extern "C" int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int
     }
     if (strips > TENMO_STATIC_MAX_STRIPS || (int64_t)slabs * N > TENMO_STATIC_PARTIAL_FLOATS)
         return tenmo_set_error(nullptr, TENMO_ERR_UNSUPPORTED, "colsum_static: %d strips x %d slabs do not fit the fixed scratch", strips, slabs);
-    float* partials = static_cast<float*>(g_static_scratch_addr[dev]);
-    unsigned int* tickets = static_cast<unsigned int*>(g_static_scratch_addr[dev]) + TENMO_STATIC_PARTIAL_FLOATS;
+    float* partials = static_cast<float*>(scratch);
+    unsigned int* tickets = static_cast<unsigned int*>(scratch) + TENMO_STATIC_PARTIAL_FLOATS;
     // The array keeps whatever the previous call left.  The partials are rewritten before they are read;
     // the tickets must start at zero, so they are cleared on the stream ahead of the kernel.
     e = cudaMemsetAsync(tickets, 0, (size_t)strips * sizeof(unsigned int), stream);

@@ -195,20 +195,28 @@ class NDBuffer:
         handle().fill(self.data_ptr(), value, self.numels())
 
     def sum_leading(self, target_shape) -> "NDBuffer":
-        """sum_over_broadcasted_axes (sum_mean_reduction.mojo:184-211) for the cases the path produces:
-        extra or size-1 LEADING dims (bias gradient, broadcast batch)."""
-        if tuple(self.shape) == tuple(target_shape):
+        """sum_over_broadcasted_axes (sum_mean_reduction.mojo:184-211): sum the axes along which ``target_shape`` was
+        broadcast -- extra leading dims and dims where the target has size 1 -- back to the target's shape.  Leading
+        axes (bias gradient, broadcast batch) reduce in place as a column sum; interior size-1 axes (a batch such as
+        (2,1,m,k) against (1,3,k,n)) are first moved to the front by a strided copy, then take the same kernel."""
+        target_shape = tuple(int(d) for d in target_shape)
+        if tuple(self.shape) == target_shape:
             return self
-        x = self.contiguous()
-        cols = int(np.prod(target_shape)) if len(target_shape) else 1
-        total = x.numels()
-        lead = total // cols
-        # the target must equal the trailing dims of x, up to leading 1s
-        t_core = tuple(target_shape)
-        while t_core and t_core[0] == 1:
-            t_core = t_core[1:]
-        if tuple(x.shape[len(x.shape) - len(t_core):]) != t_core or lead * cols != total:
-            panic("sum_over_broadcasted_axes: only leading axes are summed here:", self.shape, "->", target_shape)
+        rank = len(self.shape)
+        if len(target_shape) > rank:
+            panic("sum_over_broadcasted_axes: the target has more dims than the gradient:", self.shape, "->", target_shape)
+        padded = (1,) * (rank - len(target_shape)) + target_shape
+        summed = [d for d in range(rank) if padded[d] != self.shape[d]]
+        if any(padded[d] != 1 for d in summed):
+            panic("sum_over_broadcasted_axes: shapes are not a broadcast of one another:", self.shape, "->", target_shape)
+        kept = [d for d in range(rank) if d not in summed]
+        x = self
+        if summed != list(range(len(summed))):  # an interior axis: bring the summed axes to the front
+            order = summed + kept
+            x = NDBuffer(self.storage, [self.shape[d] for d in order], [self.strides[d] for d in order], self.offset)
+        x = x.contiguous()
+        lead = int(np.prod([self.shape[d] for d in summed])) if summed else 1
+        cols = x.numels() // lead if lead else 0
         out = NDBuffer.empty(target_shape)
         handle().colsum(x.data_ptr(), lead, cols, cols, out.data_ptr())
         return out
@@ -620,9 +628,15 @@ class Backward:
 
     @staticmethod
     def sum(output: Tensor, retain_graph: bool):
+        """The upstream scalar spread over the parent's shape, without a host round trip: a (numel, 1) column of ones
+        times the (1, 1) upstream gradient, accumulated by the GEMM's epilogue."""
         (parent,) = output.ancestry.parents
-        g = float(output.gradbox.numpy().reshape(-1)[0])
+        n = int(np.prod(parent.shape())) if parent.shape() else 1
+        ones = NDBuffer(torch.ones(max(n, 1), dtype=torch.float32, device="cuda"), (n, 1))
         inc = NDBuffer.empty(parent.shape())
-        inc.fill(g)
+        g = output.gradbox.reshape((1, 1))
+        handle().gemm(n, 1, 1, ones.mat(), g.mat(), inc.data_ptr(), algo=_lib.ALGO_SIMT_FP32)  # exact: 1.0 * g
         parent.update_grad(inc)
+        if not retain_graph:
+            output.gradbox.fill(0.0)
         return [parent]

@@ -238,3 +238,28 @@ def test_sigmoid_mlp_and_3xtf32_path(tm, oracle):
     dz = oracle.sigmoid_bwd(np.ones_like(yref), yref)
     assert np.allclose(ws.grad().numpy(), oracle.matmul(oracle.View.of(X).t(), oracle.View.of(dz)), rtol=1e-4, atol=1e-3)
     assert np.allclose(xs.grad().numpy(), oracle.matmul(oracle.View.of(dz), oracle.View.of(W).t()), rtol=1e-4, atol=1e-3)
+
+
+def test_interior_broadcast_batch_gradients(tm):
+    """(2,1,m,k) @ (1,3,k,n): each operand is broadcast along an INTERIOR batch axis; the backward pass sums the batched
+    gradients back over that axis (sum_over_broadcasted_axes, sum_mean_reduction.mojo:184-211)."""
+    rng = np.random.default_rng(17)
+    a = rng.standard_normal((2, 1, 5, 4)).astype(np.float32)
+    b = rng.standard_normal((1, 3, 4, 6)).astype(np.float32)
+    A, B = tm.Tensor.from_numpy(a, requires_grad=True), tm.Tensor.from_numpy(b, requires_grad=True)
+    C = A.matmul(B)
+    assert C.shape() == (2, 3, 5, 6) and C.all_close(a @ b, rtol=1e-5, atol=1e-6)
+    up = rng.standard_normal((2, 3, 5, 6)).astype(np.float32)
+    C.backward(tm.Tensor.from_numpy(up))
+    dA = (up @ np.swapaxes(b, -1, -2)).sum(axis=1, keepdims=True)
+    dB = (np.swapaxes(a, -1, -2) @ up).sum(axis=0, keepdims=True)
+    assert A.grad().shape() == a.shape and A.grad().all_close(dA, rtol=1e-5, atol=1e-5)
+    assert B.grad().shape() == b.shape and B.grad().all_close(dB, rtol=1e-5, atol=1e-5)
+
+
+def test_sum_backward_keeps_the_upstream_on_the_device(tm):
+    A = tm.Tensor.d2([[1, 2], [3, 4]], requires_grad=True)
+    s = A.sum()
+    s.backward(3.0)
+    assert A.grad().all_close(np.full((2, 2), 3.0, np.float32))
+    assert s.gradbox is None or not s.gradbox.numpy().any()   # zeroed like every other backward (retain_graph=False)

@@ -245,6 +245,17 @@ def test_elementwise(g, oracle, n):
     sd = g.dev(sg)
     h.sigmoid_bwd(yd.data_ptr(), sd.data_ptr(), od.data_ptr(), n)
     assert np.array_equal(g.host(od), oracle.sigmoid_bwd(y, sg))
+    # in place: the gradient buffer is also the output (what the convolution layers do with the ReLU mask), and the
+    # activation is overwritten by its own sigmoid / its own backward
+    gd = g.dev(y)
+    h.relu_bwd(gd.data_ptr(), md.data_ptr(), gd.data_ptr(), n)
+    assert np.array_equal(g.host(gd), oracle.relu_bwd(y, mask))
+    gd = g.dev(y)
+    h.sigmoid_bwd(gd.data_ptr(), sd.data_ptr(), gd.data_ptr(), n)
+    assert np.array_equal(g.host(gd), oracle.sigmoid_bwd(y, sg))
+    xi = g.dev(x)
+    h.relu_fwd(xi.data_ptr(), xi.data_ptr(), 0, n)
+    assert np.array_equal(g.host(xi), out)
     h.add_inplace(xd.data_ptr(), yd.data_ptr(), n)
     assert np.array_equal(g.host(xd), x + y)
     h.fill(xd.data_ptr(), 0.0, n)
