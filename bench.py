@@ -962,7 +962,7 @@ def run_kernel_rooflines(args, h=None, collect=None):
     sm = [torch.empty(M, C, **f32) for _ in range(R)]
     labels = torch.randint(0, C, (M,), device="cuda")
     loss, valid = torch.zeros(1, **f32), torch.zeros(1, dtype=torch.int32, device="cuda")
-    report("ce_fwd_kernel", 8.0 * M * C + 8.0 * M,
+    report("ce_fwd_stream_kernel", 8.0 * M * C + 8.0 * M,
            lambda i: h.ce_fwd(logits[i % R].data_ptr(), C, labels.data_ptr(), True, M, C, -100, 0.0, 0, sm[i % R].data_ptr(),
                               loss.data_ptr(), valid.data_ptr()), note="softmax kept for backward, loss finished on the device")
     report("ce_bwd_kernel", 8.0 * M * C + 8.0 * M,

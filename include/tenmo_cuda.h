@@ -154,8 +154,9 @@ int tenmo_gemm_f32_ex(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K,
 int tenmo_split_lo_f32(tenmo_ctx* ctx, const tenmo_mat* X, int64_t rows, int64_t cols, float* lo_out, int64_t capacity);
 /* Which kernel the last tenmo_gemm_f32 call on this context ran: TENMO_ALGO_SIMT_FP32 or _TC_3XTF32. */
 int tenmo_gemm_last_algo(tenmo_ctx* ctx);
-/* Name of the kernel that call launched: "gemm_tc_kernel", "gemm_simt_tma_kernel" (strict fp32, TMA-staged tiles)
- * or "gemm_simt_kernel" (strict fp32, register-staged: any strides); "" before the first call.  No reference
+/* Name of the kernel that call launched: "gemm_tc_kernel", "gemm_simt_tma_kernel" (strict fp32, TMA-staged tiles),
+ * "gemm_simt_kernel" (strict fp32, register-staged: any strides) or "gemm_skinny_kernel" (strict fp32, a result of at
+ * most 32 columns over a contraction of 512 or more); "" before the first call.  No reference
  * counterpart; tests and benchmarks use it to state which path was measured. */
 const char* tenmo_gemm_last_kernel(tenmo_ctx* ctx);
 /* Pieces of the stream-K tail of that launch: when the tiles of a tensor-core GEMM do not fill the last wave of CTAs,
@@ -235,6 +236,27 @@ int tenmo_colsum_f32_static(const float* x, int64_t M, int64_t N, int64_t ldx, f
  *   maxpool2d fwd  k x k window, first maximum wins (strict >), argmax = y*W + x inside the (n,c) plane or -1
  *            (pooling.mojo:301-402); bwd  dx = 0 then dx[argmax] += g (pooling.mojo:25-107). */
 int tenmo_conv_out_size(int64_t in, int k, int stride, int dilation, int pad, int64_t* out);
+/* The convolution as an implicit GEMM: the patch matrix is never written, the image region a tile of outputs reads is
+ * staged in shared memory and the multiplies gather from there (3x3 / stride 1 / dilation 1 kernels; other geometries
+ * run plain gather kernels).  Strict fp32.
+ *   fwd         out[n,co,oy,ox] = act(bias[co] + sum over (ci,ky,kx) ascending of x * weight): Conv2dFused.forward
+ *               (cnn.mojo:404-507), the accumulator starting at the bias (cnn.mojo:435) -- bit-identical to that chain.
+ *               act: TENMO_ACT_NONE or TENMO_ACT_RELU; mask (optional, shape of out) receives the 0/1 ReLU mask
+ *               (relu.mojo:97-141).  bias may be NULL.
+ *   bwd_input   dx (+)= the input gradient (compute_input_gradient, cnn.mojo:812-950), gathered instead of scattered.
+ *   bwd_weight  dW (+)= grad . patches and db (+)= per-channel sum of grad (compute_kernel_gradient / compute_bias_gradient,
+ *               cnn.mojo:716-809, 664-714); per-slab partial sums are added in slab order, so results repeat run to run.
+ *   g_mask (optional, shape of g): the 0/1 ReLU mask of the layer's output; the kernels use g * g_mask, which fuses
+ *               ReLUBackward (relu.mojo:19-46) into the load.  beta: 0 or 1 (accumulate into the outputs). */
+int tenmo_conv2d_fwd_f32(tenmo_ctx* ctx, const float* x, int64_t N, int64_t C, int64_t H, int64_t W, const float* weight,
+                         const float* bias, int64_t Cout, int KH, int KW, int stride, int dilation, int pad, int act,
+                         float* out, float* mask);
+int tenmo_conv2d_bwd_input_f32(tenmo_ctx* ctx, const float* g, const float* g_mask, const float* weight, int64_t N, int64_t C,
+                               int64_t H, int64_t W, int64_t Cout, int KH, int KW, int stride, int dilation, int pad,
+                               float* dx, float beta);
+int tenmo_conv2d_bwd_weight_f32(tenmo_ctx* ctx, const float* x, const float* g, const float* g_mask, int64_t N, int64_t C,
+                                int64_t H, int64_t W, int64_t Cout, int KH, int KW, int stride, int dilation, int pad,
+                                float* dW, float* db, float beta);
 int tenmo_im2col_f32(tenmo_ctx* ctx, const float* x, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW,
                      int stride, int dilation, int pad, float* patches);
 int tenmo_col2im_f32(tenmo_ctx* ctx, const float* dpatches, int64_t N, int64_t C, int64_t H, int64_t W, int KH, int KW,

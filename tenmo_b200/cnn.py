@@ -1,13 +1,13 @@
-"""Conv2d (as GEMM) and MaxPool2d over the C ABI, NCHW, plus the CIFAR-shaped CNN training step.
+"""Conv2d (as an implicit GEMM) and MaxPool2d over the C ABI, NCHW, plus the CIFAR-shaped CNN training step.
 
-The reference's Conv2D (tenmo/cnn.mojo:18-271, net.mojo) pads, then runs a direct convolution; its backward
-uses an explicit im2col + matmul for the kernel gradient and a scatter for the input gradient.  Here the
-same arithmetic is four calls per direction:
+The reference's Conv2D (tenmo/cnn.mojo:18-271, net.mojo) pads, then runs a direct convolution; its backward uses an
+explicit im2col + matmul for the kernel gradient and a scatter for the input gradient.  Here each direction is one
+call whose kernel gathers the patch operand from a shared-memory copy of the image region it needs, so no patch
+matrix ever exists in device memory:
 
-  forward   patches = im2col(x);  out[n] = W(C_out, K) . patches[n]^T + bias  (one batched GEMM whose output
-            is NCHW as it stands, bias per row, ReLU and its mask in the epilogue)
-  backward  db = channel_sum(g);  dW = sum_n g[n] . patches[n]  (batched GEMM + sum over the batch);
-            dpatches[n] = g[n]^T . W  (batched GEMM);  dx = col2im(dpatches)
+  forward   out = relu(conv(x, W) + b) with the bias as the accumulators' start value and the 0/1 mask from the epilogue
+  backward  dW, db = conv2d_bwd_weight(x, g * mask);  dx = conv2d_bwd_input(g * mask, W)   (the mask multiply rides in
+            the kernels' loads)
 """
 from __future__ import annotations
 
@@ -31,42 +31,32 @@ class Conv2d:
         self.h, self.N, self.Cin, self.H, self.W, self.Cout, self.k = h, N, Cin, H, W, Cout, k
         self.stride, self.dil, self.pad, self.relu, self.need_dx = stride, dilation, pad, relu, need_dx
         self.Ho, self.Wo = out_size(H, k, stride, dilation, pad), out_size(W, k, stride, dilation, pad)
-        self.K = Cin * k * k
         f32 = dict(dtype=torch.float32, device=f"cuda:{device}")
-        S = self.Ho * self.Wo
-        self.patches = torch.empty(N * S, self.K, **f32)
         self.out = torch.empty(N, Cout, self.Ho, self.Wo, **f32)
         self.mask = torch.empty(N, Cout, self.Ho, self.Wo, **f32) if relu else None
-        self.dW_full = torch.empty(N, Cout, self.K, **f32)
-        self.dpatches = torch.empty(N * S, self.K, **f32) if need_dx else None
         self.dx = torch.empty(N, Cin, H, W, **f32) if need_dx else None
+        self.x = None
+
+    def _geom(self):
+        return (self.N, self.Cin, self.H, self.W), (self.Cout, self.k, self.k, self.stride, self.dil, self.pad)
 
     def forward(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
-        h, N, S, K = self.h, self.N, self.Ho * self.Wo, self.K
-        h.im2col(x.data_ptr(), N, self.Cin, self.H, self.W, self.k, self.k, self.stride, self.dil, self.pad,
-                 self.patches.data_ptr())
-        mW = make_mat(weight.data_ptr(), (self.Cout, K), (K, 1))                 # broadcast over the batch
-        mPt = make_mat(self.patches.data_ptr(), (N, K, S), (S * K, 1, K))         # patches[n]^T as a stride view
-        h.gemm_ex(self.Cout, S, K, mW, mPt, self.out.data_ptr(), algo=_lib.ALGO_SIMT_FP32, bias_m=bias.data_ptr(),
-                  act=_lib.ACT_RELU if self.relu else _lib.ACT_NONE, aux=self.mask.data_ptr() if self.relu else 0)
+        (N, Cin, H, W), (Cout, kh, kw, stride, dil, pad) = self._geom()
+        self.x = x  # the kernel gradient reads the layer input again
+        self.h.conv2d_fwd(x.data_ptr(), N, Cin, H, W, weight.data_ptr(), bias.data_ptr() if bias is not None else 0, Cout, kh, kw,
+                          stride, dil, pad, _lib.ACT_RELU if self.relu else _lib.ACT_NONE, self.out.data_ptr(),
+                          self.mask.data_ptr() if self.relu else 0)
         return self.out
 
     def backward(self, g: torch.Tensor, weight: torch.Tensor, dW: torch.Tensor, db: torch.Tensor):
-        """g is dL/d(out) AFTER the activation; with relu=True it is multiplied by the mask first (in place)."""
-        h, N, S, K, Cout = self.h, self.N, self.Ho * self.Wo, self.K, self.Cout
-        if self.relu:
-            h.relu_bwd(g.data_ptr(), self.mask.data_ptr(), g.data_ptr(), g.numel())
-        h.channel_sum(g.data_ptr(), N, Cout, S, db.data_ptr())
-        mG = make_mat(g.data_ptr(), (N, Cout, S), (Cout * S, S, 1))
-        mP = make_mat(self.patches.data_ptr(), (N, S, K), (S * K, K, 1))
-        h.gemm_ex(Cout, K, S, mG, mP, self.dW_full.data_ptr(), algo=_lib.ALGO_SIMT_FP32)
-        h.colsum(self.dW_full.data_ptr(), N, Cout * K, Cout * K, dW.data_ptr())   # sum over the batch
+        """g is dL/d(out) AFTER the activation; with relu=True the kernels multiply it by the mask as they load it."""
+        (N, Cin, H, W), (Cout, kh, kw, stride, dil, pad) = self._geom()
+        mask = self.mask.data_ptr() if self.relu else 0
+        self.h.conv2d_bwd_weight(self.x.data_ptr(), g.data_ptr(), mask, N, Cin, H, W, Cout, kh, kw, stride, dil, pad,
+                                 dW.data_ptr(), db.data_ptr())
         if self.need_dx:
-            mGt = make_mat(g.data_ptr(), (N, S, Cout), (Cout * S, 1, S))
-            mW = make_mat(weight.data_ptr(), (Cout, K), (K, 1))
-            h.gemm_ex(S, K, Cout, mGt, mW, self.dpatches.data_ptr(), algo=_lib.ALGO_SIMT_FP32)
-            h.col2im(self.dpatches.data_ptr(), N, self.Cin, self.H, self.W, self.k, self.k, self.stride, self.dil, self.pad,
-                     self.dx.data_ptr())
+            self.h.conv2d_bwd_input(g.data_ptr(), mask, weight.data_ptr(), N, Cin, H, W, Cout, kh, kw, stride, dil, pad,
+                                    self.dx.data_ptr())
         return self.dx
 
 

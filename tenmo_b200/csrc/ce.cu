@@ -297,6 +297,97 @@ __global__ void __launch_bounds__(CE_THREADS, SMALL_C ? 2 : 3) ce_fwd_kernel(con
     }
 }
 
+// The forward pass for a large batch of wide, 16-byte aligned rows (33 <= C <= 1024, more rows than CE_SEQ_ROWS): the
+// arithmetic of ce_fwd_kernel's row-in-registers path, bit for bit, with the NEXT row of a warp already on its way from
+// HBM while the current one is reduced, exponentiated and written back.  A warp of the plain kernel alternates between
+// a load phase and a compute phase and only the three CTAs of an SM overlap them; here every warp keeps 4 KB of loads in
+// flight all the time (two CTAs of eight warps per SM, 64 row registers per lane).
+__global__ void __launch_bounds__(CE_THREADS, 2) ce_fwd_stream_kernel(const CeFwdArgs p) {
+    __shared__ float red_smem[2 * CE_WARPS];
+    __shared__ bool is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float NEG = -3.4028234663852886e38f;
+    float part_loss = 0.f;
+    int part_cnt = 0;
+    const int64_t stride = (int64_t)gridDim.x * CE_WARPS;
+    auto load_row = [&](int64_t row, float (&v)[CE_REG]) {
+        const float4* x4 = reinterpret_cast<const float4*>(p.logits + row * p.ld);
+#pragma unroll
+        for (int i = 0; i < CE_REG / 4; ++i) {
+            const int c = (lane + 32 * i) * 4;
+            float4 t = make_float4(NEG, NEG, NEG, NEG);
+            if (c < p.C) t = __ldcs(x4 + lane + 32 * i);
+            v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+    };
+    auto finish_row = [&](int64_t row, float (&v)[CE_REG]) {
+        const int64_t t = load_label(p.labels, p.label_is_i64, row);
+        const float logit_t = (t >= 0 && t < p.C) ? __ldg(p.logits + row * p.ld + t) : 0.f;
+        float mx = NEG;
+#pragma unroll
+        for (int i = 0; i < CE_REG; ++i) mx = fmaxf(mx, v[i]);
+        mx = tenmo_warp_max(mx);
+        float sum_exp = 0.f, sum_logits = 0.f;
+#pragma unroll
+        for (int i = 0; i < CE_REG; ++i) {
+            const int c = (lane + 32 * (i / 4)) * 4;
+            if (c < p.C) { sum_logits += v[i]; v[i] = expf(v[i] - mx); sum_exp += v[i]; }
+        }
+        sum_exp = tenmo_warp_sum(sum_exp);
+        sum_logits = tenmo_warp_sum(sum_logits);
+        if (p.softmax) {
+            const float inv = 1.f / sum_exp;
+            float4* sm4 = reinterpret_cast<float4*>(p.softmax + row * p.C);
+#pragma unroll
+            for (int i = 0; i < CE_REG / 4; ++i) {
+                const int c = (lane + 32 * i) * 4;
+                if (c < p.C) sm4[lane + 32 * i] = make_float4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
+            }
+        }
+        if (lane == 0) {
+            int counted;
+            const float loss = row_loss_from_stats(p, t, logit_t, mx, sum_exp, sum_logits, &counted);
+            if (p.reduction == 2) p.loss[row] = loss;
+            part_loss += loss;
+            part_cnt += counted;
+        }
+    };
+    float va[CE_REG], vb[CE_REG];
+    int64_t row = (int64_t)blockIdx.x * CE_WARPS + warp;
+    if (row < p.M) load_row(row, va);
+    while (row < p.M) {                       // two rows per turn, so that the buffers never have to be copied
+        if (row + stride < p.M) load_row(row + stride, vb);
+        finish_row(row, va);
+        row += stride;
+        if (row >= p.M) break;
+        if (row + stride < p.M) load_row(row + stride, va);
+        finish_row(row, vb);
+        row += stride;
+    }
+    // this CTA's partial: lanes, then warps, in a fixed order (as in ce_fwd_kernel)
+    part_loss = tenmo_warp_sum(part_loss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part_cnt += __shfl_xor_sync(0xffffffffu, part_cnt, o);
+    int* cnt_smem = reinterpret_cast<int*>(red_smem + CE_WARPS);
+    if (lane == 0) { red_smem[warp] = part_loss; cnt_smem[warp] = part_cnt; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        int c = 0;
+        for (int w = 0; w < CE_WARPS; ++w) { t += red_smem[w]; c += cnt_smem[w]; }
+        p.part_loss[blockIdx.x] = t;
+        p.part_cnt[blockIdx.x] = c;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(p.ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    ce_finalize(p, red_smem);
+    if (threadIdx.x == 0) *p.ticket = 0;
+}
+
 struct CeBwdArgs {
     const float* softmax;
     const void* labels;
@@ -333,36 +424,63 @@ __global__ void __launch_bounds__(CE_THREADS) ce_bwd_kernel(const CeBwdArgs p) {
         scale_mul = ug / scale;
     }
     const float ls_uniform = p.ls / (float)p.C;
-    for (int64_t row = (int64_t)blockIdx.x * CE_WARPS + warp; row < p.M; row += (int64_t)gridDim.x * CE_WARPS) {
-        const int64_t t = load_label(p.labels, p.label_is_i64, row);
-        const bool ignored = t == p.ignore_index;
-        const int64_t hit = ignored ? -1 : t;
-        const float m = p.reduction == 2 ? (p.upstream ? __ldg(p.upstream + row) : 1.f) : scale_mul;
-        const float* sm = p.softmax + row * p.C;
-        float* dl = p.dlogits + row * p.C;
+    const int64_t stride = (int64_t)gridDim.x * CE_WARPS;
+    // two rows of a warp travel together (row and row + stride): twice the loads in flight per lane
+    for (int64_t row = (int64_t)blockIdx.x * CE_WARPS + warp; row < p.M; row += 2 * stride) {
+        const int64_t row_b = row + stride;
+        const bool has_b = row_b < p.M;
+        const int64_t ta = load_label(p.labels, p.label_is_i64, row);
+        const int64_t tb = has_b ? load_label(p.labels, p.label_is_i64, row_b) : p.ignore_index;
+        const bool ign_a = ta == p.ignore_index, ign_b = tb == p.ignore_index;
+        const int64_t hit_a = ign_a ? -1 : ta, hit_b = ign_b ? -1 : tb;
+        const float ma = p.reduction == 2 ? (p.upstream ? __ldg(p.upstream + row) : 1.f) : scale_mul;
+        const float mb = p.reduction == 2 ? ((p.upstream && has_b) ? __ldg(p.upstream + row_b) : 1.f) : scale_mul;
+        const float* sm_a = p.softmax + row * p.C;
+        const float* sm_b = p.softmax + (has_b ? row_b : row) * p.C;
+        float* dl_a = p.dlogits + row * p.C;
+        float* dl_b = p.dlogits + (has_b ? row_b : row) * p.C;
         if (p.vec) {
-            const float4* sm4 = reinterpret_cast<const float4*>(sm);
-            float4* dl4 = reinterpret_cast<float4*>(dl);
+            const float4* sa4 = reinterpret_cast<const float4*>(sm_a);
+            const float4* sb4 = reinterpret_cast<const float4*>(sm_b);
+            float4* da4 = reinterpret_cast<float4*>(dl_a);
+            float4* db4 = reinterpret_cast<float4*>(dl_b);
             const int n4 = (int)(p.C >> 2);
 #pragma unroll 4
             for (int q = lane; q < n4; q += 32) {
-                const float4 s = __ldg(sm4 + q);
+                const float4 s = __ldcs(sa4 + q);
+                float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (has_b) u = __ldcs(sb4 + q);
                 const int64_t c = (int64_t)q * 4;
-                float4 g;
-                g.x = ce_bwd_value(p, s.x, c == hit, ignored, ls_uniform, m);
-                g.y = ce_bwd_value(p, s.y, c + 1 == hit, ignored, ls_uniform, m);
-                g.z = ce_bwd_value(p, s.z, c + 2 == hit, ignored, ls_uniform, m);
-                g.w = ce_bwd_value(p, s.w, c + 3 == hit, ignored, ls_uniform, m);
+                float4 g, h;
+                g.x = ce_bwd_value(p, s.x, c == hit_a, ign_a, ls_uniform, ma);
+                g.y = ce_bwd_value(p, s.y, c + 1 == hit_a, ign_a, ls_uniform, ma);
+                g.z = ce_bwd_value(p, s.z, c + 2 == hit_a, ign_a, ls_uniform, ma);
+                g.w = ce_bwd_value(p, s.w, c + 3 == hit_a, ign_a, ls_uniform, ma);
                 if (p.beta != 0.f) {
-                    const float4 o = dl4[q];
+                    const float4 o = da4[q];
                     g.x += o.x; g.y += o.y; g.z += o.z; g.w += o.w;
                 }
-                dl4[q] = g;
+                da4[q] = g;
+                if (has_b) {
+                    h.x = ce_bwd_value(p, u.x, c == hit_b, ign_b, ls_uniform, mb);
+                    h.y = ce_bwd_value(p, u.y, c + 1 == hit_b, ign_b, ls_uniform, mb);
+                    h.z = ce_bwd_value(p, u.z, c + 2 == hit_b, ign_b, ls_uniform, mb);
+                    h.w = ce_bwd_value(p, u.w, c + 3 == hit_b, ign_b, ls_uniform, mb);
+                    if (p.beta != 0.f) {
+                        const float4 o = db4[q];
+                        h.x += o.x; h.y += o.y; h.z += o.z; h.w += o.w;
+                    }
+                    db4[q] = h;
+                }
             }
         } else {
             for (int64_t c = lane; c < p.C; c += 32) {
-                const float g = ce_bwd_value(p, __ldg(sm + c), c == hit, ignored, ls_uniform, m);
-                dl[c] = p.beta != 0.f ? dl[c] + g : g;
+                const float g = ce_bwd_value(p, __ldg(sm_a + c), c == hit_a, ign_a, ls_uniform, ma);
+                dl_a[c] = p.beta != 0.f ? dl_a[c] + g : g;
+                if (has_b) {
+                    const float h = ce_bwd_value(p, __ldg(sm_b + c), c == hit_b, ign_b, ls_uniform, mb);
+                    dl_b[c] = p.beta != 0.f ? dl_b[c] + h : h;
+                }
             }
         }
     }
@@ -419,7 +537,12 @@ static int ce_fwd_impl(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, c
     p.logits = logits; p.ld = ld_logits; p.labels = labels; p.label_is_i64 = label_is_i64;
     p.M = M; p.C = C; p.ignore_index = ignore_index; p.ls = label_smoothing; p.reduction = reduction;
     p.softmax = softmax_out; p.loss = loss_dev; p.valid_count = valid_count_dev;
-    const int grid = C <= 32 ? tenmo_stream_grid(ctx, M, CE_THREADS, 4) : tenmo_stream_grid(ctx, M, CE_WARPS, 8);
+    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+    p.vec = (C % 4 == 0) && (ld_logits % 4 == 0) && aligned16(logits) && (!softmax_out || aligned16(softmax_out));
+    // large batches of wide aligned rows: the kernel that keeps the next row of every warp in flight (two CTAs per SM)
+    const bool stream = C > 32 && C <= 32 * CE_REG && p.vec && M > 4 * (int64_t)ctx->sm_count * CE_WARPS && !dlogits;
+    const int grid = C <= 32 ? tenmo_stream_grid(ctx, M, CE_THREADS, 4)
+                             : (stream ? tenmo_stream_grid(ctx, M, CE_WARPS, 2) : tenmo_stream_grid(ctx, M, CE_WARPS, 8));
     // scratch: per-row losses for the sequential mean of a small batch, one (sum, count) pair per CTA beyond it
     p.row_loss = nullptr;
     p.part_loss = nullptr;
@@ -433,15 +556,15 @@ static int ce_fwd_impl(tenmo_ctx* ctx, const float* logits, int64_t ld_logits, c
         p.part_loss = p.row_loss + rows;
         p.part_cnt = reinterpret_cast<int32_t*>(p.part_loss + grid);
     }
-    auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
-    p.vec = (C % 4 == 0) && (ld_logits % 4 == 0) && aligned16(logits) && (!softmax_out || aligned16(softmax_out));
     p.ticket = reinterpret_cast<unsigned int*>(ctx->dev_status + 8);
     p.status = ctx->dev_status;
     p.dlogits = dlogits;
     p.upstream = upstream_dev;
     const bool pdl = tenmo_pdl_ok(ctx, grid);
-    cudaError_t le = C <= 32 ? tenmo_launch(ce_fwd_kernel<true>, (unsigned)grid, CE_THREADS, 0, ctx->stream, pdl, p)
-                             : tenmo_launch(ce_fwd_kernel<false>, (unsigned)grid, CE_THREADS, 0, ctx->stream, pdl, p);
+    cudaError_t le;
+    if (stream) le = tenmo_launch(ce_fwd_stream_kernel, (unsigned)grid, CE_THREADS, 0, ctx->stream, false, p);
+    else le = C <= 32 ? tenmo_launch(ce_fwd_kernel<true>, (unsigned)grid, CE_THREADS, 0, ctx->stream, pdl, p)
+                      : tenmo_launch(ce_fwd_kernel<false>, (unsigned)grid, CE_THREADS, 0, ctx->stream, pdl, p);
     if (le != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of ce_fwd_kernel failed: %s", cudaGetErrorString(le));
     TENMO_LAUNCH_CHECK(ctx, "ce_fwd_kernel");
     return TENMO_OK;
@@ -491,7 +614,7 @@ int tenmo_ce_bwd_f32(tenmo_ctx* ctx, const float* softmax, const void* labels, i
         const int grid = tenmo_stream_grid(ctx, M * C, CE_THREADS * 4, 8);
         ce_bwd_flat_kernel<<<grid, CE_THREADS, 0, ctx->stream>>>(p);
     } else {
-        const int grid = tenmo_stream_grid(ctx, M, CE_WARPS, 8);
+        const int grid = tenmo_stream_grid(ctx, (M + 1) / 2, CE_WARPS, 8);  // a warp takes two rows at a time
         ce_bwd_kernel<<<grid, CE_THREADS, 0, ctx->stream>>>(p);
     }
     TENMO_LAUNCH_CHECK(ctx, "ce_bwd_kernel");

@@ -306,6 +306,7 @@ int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p_in, bool* co
     p.b_vec = p.b_vec && aligned16(p.B) && batch_ok(p.batch.b_stride);
     p.c_vec = (p.N % 4 == 0) && aligned16(p.C) && (!p.aux || aligned16(p.aux));
 
+    if (tenmo_gemm_skinny_supported(p)) return tenmo_gemm_skinny_launch(ctx, p);
     auto tiles = [&](int bm, int bn) {
         return ((p.M + bm - 1) / bm) * ((p.N + bn - 1) / bn) * p.total_batch;
     };

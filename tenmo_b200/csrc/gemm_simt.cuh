@@ -49,3 +49,6 @@ struct TenmoGemmParams {
 int tenmo_gemm_simt_launch(tenmo_ctx* ctx, const TenmoGemmParams& p, bool* colsum_done = nullptr);
 bool tenmo_gemm_simt_tma_supported(tenmo_ctx* ctx, const TenmoGemmParams& p);
 int tenmo_gemm_simt_tma_launch(tenmo_ctx* ctx, const TenmoGemmParams& p);
+// Narrow results (N <= 32) over a long contraction (K >= 512), one matrix: gemm_skinny.cu, same bits.
+bool tenmo_gemm_skinny_supported(const TenmoGemmParams& p);
+int tenmo_gemm_skinny_launch(tenmo_ctx* ctx, const TenmoGemmParams& p);

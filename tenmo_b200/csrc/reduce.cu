@@ -54,8 +54,24 @@ colsum_split_kernel(const float* __restrict__ x, int64_t M, int64_t N, int64_t l
 #pragma unroll
     for (int q = 0; q < VEC; ++q) acc[q] = 0.f;
     if (n0 < N) {
-        // 4 rows in flight per warp step to cover HBM latency
+        // 8 rows in flight per warp step (4 KB per warp with 16-byte loads) to cover HBM latency
         int64_t m = m_begin + warp;
+        for (; m + 7 * CS_WARPS < m_end; m += 8 * CS_WARPS) {
+            if (VEC == 4) {
+                float4 r[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) r[u] = __ldcs(reinterpret_cast<const float4*>(x + (m + u * CS_WARPS) * ldx + n0));
+                acc[0] += ((r[0].x + r[1].x) + (r[2].x + r[3].x)) + ((r[4].x + r[5].x) + (r[6].x + r[7].x));
+                acc[1 % VEC] += ((r[0].y + r[1].y) + (r[2].y + r[3].y)) + ((r[4].y + r[5].y) + (r[6].y + r[7].y));
+                acc[2 % VEC] += ((r[0].z + r[1].z) + (r[2].z + r[3].z)) + ((r[4].z + r[5].z) + (r[6].z + r[7].z));
+                acc[3 % VEC] += ((r[0].w + r[1].w) + (r[2].w + r[3].w)) + ((r[4].w + r[5].w) + (r[6].w + r[7].w));
+            } else {
+                float r[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) r[u] = __ldg(x + (m + u * CS_WARPS) * ldx + n0);
+                acc[0] += ((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7]));
+            }
+        }
         for (; m + 3 * CS_WARPS < m_end; m += 4 * CS_WARPS) {
             if (VEC == 4) {
                 const float4 a = __ldg(reinterpret_cast<const float4*>(x + m * ldx + n0));
@@ -117,8 +133,8 @@ colsum_split_kernel(const float* __restrict__ x, int64_t M, int64_t N, int64_t l
 void tenmo_colsum_plan(int sm_count, int64_t M, int64_t N, bool vec, int* strips, int* slabs, int* rows_per_slab) {
     const int strip_w = vec ? 128 : 32;
     const int64_t ns = (N + strip_w - 1) / strip_w;
-    // aim for ~4 CTAs per SM in total, at least 64 rows per slab
-    int64_t want = ((int64_t)sm_count * 4 + ns - 1) / ns;
+    // aim for ~6 CTAs per SM in total, at least 64 rows per slab
+    int64_t want = ((int64_t)sm_count * 6 + ns - 1) / ns;
     int64_t max_slabs = (M + 63) / 64;
     if (want > max_slabs) want = max_slabs;
     if (want < 1) want = 1;

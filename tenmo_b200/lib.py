@@ -27,7 +27,7 @@ EXPORTS = [
     "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end", "tenmo_cuda_reserve_sms",
     "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_gemv_f32", "tenmo_vecmat_f32", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_gemm_last_kernel", "tenmo_gemm_last_stream_k", "tenmo_cuda_wait_probe", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
-    "tenmo_conv_out_size", "tenmo_im2col_f32", "tenmo_col2im_f32", "tenmo_channel_sum_f32", "tenmo_maxpool2d_fwd_f32",
+    "tenmo_conv_out_size", "tenmo_conv2d_fwd_f32", "tenmo_conv2d_bwd_input_f32", "tenmo_conv2d_bwd_weight_f32", "tenmo_im2col_f32", "tenmo_col2im_f32", "tenmo_channel_sum_f32", "tenmo_maxpool2d_fwd_f32",
     "tenmo_maxpool2d_bwd_f32",
     "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_ce_fwd_bwd_f32", "tenmo_sgd_step_f32", "tenmo_sgd_step_lo_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
     "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
@@ -122,6 +122,9 @@ def _bind(lib):
         "tenmo_colsum_f32": (I, [P, P, I64, I64, I64, P, F]),
         "tenmo_colsum_f32_static": (I, [P, I64, I64, I64, P, F, P]),
         "tenmo_conv_out_size": (I, [I64, I, I, I, I, C.POINTER(I64)]),
+        "tenmo_conv2d_fwd_f32": (I, [P, P, I64, I64, I64, I64, P, P, I64, I, I, I, I, I, I, P, P]),
+        "tenmo_conv2d_bwd_input_f32": (I, [P, P, P, P, I64, I64, I64, I64, I64, I, I, I, I, I, P, F]),
+        "tenmo_conv2d_bwd_weight_f32": (I, [P, P, P, P, I64, I64, I64, I64, I64, I, I, I, I, I, P, P, F]),
         "tenmo_im2col_f32": (I, [P, P, I64, I64, I64, I64, I, I, I, I, I, P]),
         "tenmo_col2im_f32": (I, [P, P, I64, I64, I64, I64, I, I, I, I, I, P, F]),
         "tenmo_channel_sum_f32": (I, [P, P, I64, I64, I64, P, F]),
@@ -302,6 +305,19 @@ class TenmoCuda:
         st = self._lib.tenmo_colsum_f32_static(x, M, N, ldx, out, beta, C.c_void_p(stream))
         if st != 0:
             raise TenmoError(st, self._lib.tenmo_cuda_last_error(None).decode())
+
+    def conv2d_fwd(self, x, N, Cn, H, W, weight, bias, Cout, KH, KW, stride, dilation, pad, act, out, mask=0):
+        """Convolution forward as an implicit GEMM (bias-initialised accumulators, optional ReLU + mask)."""
+        self._call("tenmo_conv2d_fwd_f32", x, N, Cn, H, W, weight, bias or None, Cout, KH, KW, stride, dilation, pad, act, out,
+                   mask or None)
+
+    def conv2d_bwd_input(self, g, g_mask, weight, N, Cn, H, W, Cout, KH, KW, stride, dilation, pad, dx, beta=0.0):
+        self._call("tenmo_conv2d_bwd_input_f32", g, g_mask or None, weight, N, Cn, H, W, Cout, KH, KW, stride, dilation, pad, dx,
+                   beta)
+
+    def conv2d_bwd_weight(self, x, g, g_mask, N, Cn, H, W, Cout, KH, KW, stride, dilation, pad, dW, db, beta=0.0):
+        self._call("tenmo_conv2d_bwd_weight_f32", x, g, g_mask or None, N, Cn, H, W, Cout, KH, KW, stride, dilation, pad, dW, db,
+                   beta)
 
     def im2col(self, x, N, Cn, H, W, KH, KW, stride, dilation, pad, patches):
         self._call("tenmo_im2col_f32", x, N, Cn, H, W, KH, KW, stride, dilation, pad, patches)

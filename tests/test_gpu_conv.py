@@ -1,4 +1,5 @@
-"""Conv2d-as-GEMM, MaxPool2d and the CIFAR-shaped CNN step (BASELINE config 5) against the CPU oracle."""
+"""Conv2d as an implicit GEMM, MaxPool2d and the CIFAR-shaped CNN step ((256,3,32,32) images, two 3x3 convolutions with
+ReLU and 2x2 max pooling, Linear 4096 -> 10) against the CPU oracle."""
 import numpy as np
 import pytest
 
@@ -16,10 +17,13 @@ def g():
 
 GEOMS = [  # N, Cin, H, W, Cout, k, stride, dilation, pad
     (2, 3, 8, 8, 5, 3, 1, 1, 1),
-    (3, 4, 9, 7, 6, 2, 2, 1, 0),
-    (2, 2, 11, 10, 3, 3, 1, 2, 2),
+    (3, 4, 9, 7, 6, 2, 2, 1, 0),      # gather kernels: 2x2 kernel, stride 2
+    (2, 2, 11, 10, 3, 3, 1, 2, 2),    # gather kernels: dilation 2
+    (2, 5, 13, 19, 7, 3, 2, 1, 1),    # gather kernels: 3x3 with stride 2
     (4, 3, 32, 32, 32, 3, 1, 1, 1),   # conv1 of the CNN
     (2, 32, 16, 16, 64, 3, 1, 1, 1),  # conv2 of the CNN
+    (3, 40, 19, 21, 70, 3, 1, 1, 0),  # staged kernels with ragged tiles, two input-channel chunks, three channel blocks, no padding
+    (5, 9, 35, 33, 33, 3, 1, 1, 2),   # staged kernels, padding 2, image larger than one tile in both directions
 ]
 
 
@@ -39,12 +43,6 @@ def test_conv2d_forward_backward_vs_oracle(g, oracle, geom):
     ref = oracle.conv2d_fwd(x, w, b, stride=stride, dilation=dil, pad=pad, contract=1)
     # the strict-fp32 GEMM starts its accumulators at the bias and runs the same (c, ky, kx) fma chain
     assert np.array_equal(out, ref)
-    # im2col itself: every patch entry is an image entry or a padding zero
-    patches = g.host(conv.patches).reshape(N, conv.Ho, conv.Wo, Cin, k, k)
-    xp = np.pad(x, ((0, 0), (0, 0), (pad, pad), (pad, pad)))
-    oy, ox = conv.Ho - 1, conv.Wo // 2
-    assert np.array_equal(patches[:, oy, ox], xp[:, :, oy * stride:oy * stride + (k - 1) * dil + 1:dil,
-                                                 ox * stride:ox * stride + (k - 1) * dil + 1:dil])
     gr = rng.standard_normal(ref.shape).astype(np.float32)
     dW, db = g.empty(Cout, Cin, k, k), g.empty(Cout)
     dx = conv.backward(g.dev(gr), wd, dW, db)
@@ -53,6 +51,33 @@ def test_conv2d_forward_backward_vs_oracle(g, oracle, geom):
     assert np.allclose(g.host(db), rdb, **tol)
     assert np.allclose(g.host(dW), rdw, **tol)
     assert np.allclose(g.host(dx), rdx, **tol)
+    # the same layer with ReLU: output and 0/1 mask from the epilogue, the mask multiplied into g by the backward kernels
+    convr = Conv2d(h, N, Cin, H, W, Cout, k, stride, dil, pad, relu=True)
+    outr = g.host(convr.forward(xd, wd, bd))
+    r_out, r_mask = oracle.relu_fwd(ref)
+    assert np.array_equal(outr, r_out) and np.array_equal(g.host(convr.mask), r_mask)
+    dxr = convr.backward(g.dev(gr), wd, dW, db)
+    rdx, rdw, rdb = oracle.conv2d_bwd(oracle.relu_bwd(gr, r_mask), x, w, stride=stride, dilation=dil, pad=pad)
+    assert np.allclose(g.host(db), rdb, **tol) and np.allclose(g.host(dW), rdw, **tol) and np.allclose(g.host(dxr), rdx, **tol)
+    # run to run the gradients are the same bits (slab order, not arrival order)
+    dW2, db2 = g.empty(Cout, Cin, k, k), g.empty(Cout)
+    convr.backward(g.dev(gr), wd, dW2, db2)
+    assert torch.equal(dW, dW2) and torch.equal(db, db2)
+    h.check_device_status()
+
+
+def test_im2col_matches_the_padded_image(g):
+    N, Cin, H, W, k, stride, dil, pad = 2, 3, 9, 8, 3, 2, 1, 1
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((N, Cin, H, W)).astype(np.float32)
+    Ho, Wo = (H + 2 * pad - 3) // stride + 1, (W + 2 * pad - 3) // stride + 1
+    pat = g.empty(N * Ho * Wo, Cin * k * k)
+    g.handle().im2col(g.dev(x).data_ptr(), N, Cin, H, W, k, k, stride, dil, pad, pat.data_ptr())
+    patches = g.host(pat).reshape(N, Ho, Wo, Cin, k, k)
+    xp = np.pad(x, ((0, 0), (0, 0), (pad, pad), (pad, pad)))
+    for oy, ox in ((0, 0), (Ho - 1, Wo // 2), (Ho - 1, Wo - 1)):
+        assert np.array_equal(patches[:, oy, ox], xp[:, :, oy * stride:oy * stride + (k - 1) * dil + 1:dil,
+                                                     ox * stride:ox * stride + (k - 1) * dil + 1:dil])
 
 
 @pytest.mark.parametrize("shape_k", [((2, 3, 8, 8), 2, 2, 0), ((3, 5, 9, 7), 3, 2, 1), ((256, 32, 32, 32), 2, 2, 0)], ids=str)

@@ -137,6 +137,28 @@ def test_gemm_simt_bit_exact(g, oracle, mkn, layout):
     assert np.allclose(C, oracle.matmul_naive(Av, Bv), rtol=1e-5, atol=1e-4 * max(1, K // 32))
 
 
+@pytest.mark.parametrize("mkn", [(256, 4096, 10), (5, 700, 1), (33, 513, 32), (4, 512, 7), (1000, 1555, 3)], ids=str)
+@pytest.mark.parametrize("layout", ["nn", "a_t", "b_t", "strided"])
+def test_gemm_narrow_result_kernel_bit_exact(g, oracle, mkn, layout):
+    """A result of at most 32 columns over a long contraction runs on its own strict-fp32 kernel: same chain, same bits,
+    with the Linear epilogue (bias, ReLU + mask) and the accumulate."""
+    M, K, N = mkn
+    rng = np.random.default_rng(M + 3 * K + 7 * N)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32) * 0.05
+    bias = rng.standard_normal(N).astype(np.float32)
+    Av, Bv = _layout_views(oracle, A, B, layout, rng)
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=SIMT)
+    assert g.handle().gemm_last_kernel() == "gemm_skinny_kernel"
+    ref = oracle.matmul(Av, Bv, contract_scalar=1, threads=4)
+    assert np.array_equal(C, ref)
+    C, aux, _ = g.gpu_matmul(Av, Bv, algo=SIMT, bias=bias, act=1, want_aux=True)
+    out, mask = oracle.relu_fwd(oracle.add_bias(ref, bias))
+    assert np.array_equal(C, out) and np.array_equal(aux, mask)
+    init = rng.standard_normal((M, N), np.float32)
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=SIMT, beta=1.0, c_init=init)
+    assert np.array_equal(C, init + ref)
+
+
 def test_gemm_small_exhaustive(g, oracle):
     """Every M, N, K in a small box on the scalar-tail-heavy sizes: one launch each, all bit-exact."""
     rng = np.random.default_rng(5)

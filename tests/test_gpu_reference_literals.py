@@ -47,7 +47,8 @@ def test_softmax_backward_literals(g, oracle, case):
     y = g.host(yd)
     up = softmax_upstream(case, y)
     dx = g.empty(*y.shape)
-    g.handle().softmax_bwd(yd.data_ptr(), g.dev(up).data_ptr(), dx.data_ptr(), y.shape[0], y.shape[1])
+    upd = g.dev(up)
+    g.handle().softmax_bwd(yd.data_ptr(), upd.data_ptr(), dx.data_ptr(), y.shape[0], y.shape[1])
     assert close(g.host(dx), case["dx"], 2e-7)
     assert close(g.host(dx), oracle.softmax_bwd(up, y), 1e-7)
 
@@ -58,7 +59,8 @@ def test_relu_literals(g, case):
     xd, out, mask, dx = g.dev(x), g.empty(*x.shape), g.empty(*x.shape), g.empty(*x.shape)
     h = g.handle()
     h.relu_fwd(xd.data_ptr(), out.data_ptr(), mask.data_ptr(), x.size)
-    h.relu_bwd(g.dev(np.ones_like(x)).data_ptr(), mask.data_ptr(), dx.data_ptr(), x.size)
+    ones = g.dev(np.ones_like(x))
+    h.relu_bwd(ones.data_ptr(), mask.data_ptr(), dx.data_ptr(), x.size)
     assert np.array_equal(g.host(out), f32(case["y"])) and np.array_equal(g.host(mask), f32(case["mask"]))
     assert np.array_equal(g.host(dx), f32(case["mask"]))
     # the same ReLU as the epilogue of a GEMM with the identity: out = relu(x . I), aux = mask
@@ -75,7 +77,8 @@ def test_sigmoid_literals(g, oracle, case):
     xd, y, dx = g.dev(x), g.empty(*x.shape), g.empty(*x.shape)
     h = g.handle()
     h.sigmoid_fwd(xd.data_ptr(), y.data_ptr(), x.size)
-    h.sigmoid_bwd(g.dev(np.ones_like(x)).data_ptr(), y.data_ptr(), dx.data_ptr(), x.size)
+    ones = g.dev(np.ones_like(x))
+    h.sigmoid_bwd(ones.data_ptr(), y.data_ptr(), dx.data_ptr(), x.size)
     s = f32(case["y"])
     assert close(g.host(y), s, 1e-6) and close(g.host(dx), s * (1 - s), 1e-6)
     assert close(g.host(y), oracle.sigmoid_fwd(x), 2e-7)
@@ -85,7 +88,8 @@ def test_sigmoid_literals(g, oracle, case):
 def test_sum_axis0_literals(g, case):
     x = f32(case["x"])
     out = g.empty(x.shape[1])
-    g.handle().colsum(g.dev(x).data_ptr(), x.shape[0], x.shape[1], x.shape[1], out.data_ptr())
+    xd = g.dev(x)
+    g.handle().colsum(xd.data_ptr(), x.shape[0], x.shape[1], x.shape[1], out.data_ptr())
     assert np.array_equal(g.host(out), f32(case["out"]))
 
 
@@ -94,8 +98,9 @@ def test_bias_add_broadcast_literals(g):
     x, b = f32(c["x"]), f32(c["bias"])
     out, db = g.empty(*x.shape), g.empty(b.size)
     h = g.handle()
-    h.add_bias(g.dev(x).data_ptr(), g.dev(b).data_ptr(), out.data_ptr(), x.shape[0], x.shape[1])
-    h.colsum(g.dev(np.ones_like(x)).data_ptr(), x.shape[0], x.shape[1], x.shape[1], db.data_ptr())
+    xd, bd, ones = g.dev(x), g.dev(b), g.dev(np.ones_like(x))   # named: a temporary's memory may be reused by the next one
+    h.add_bias(xd.data_ptr(), bd.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1])
+    h.colsum(ones.data_ptr(), x.shape[0], x.shape[1], x.shape[1], db.data_ptr())
     assert np.array_equal(g.host(out), f32(c["out"])) and np.array_equal(g.host(db), f32(c["dbias"]))
 
 
@@ -158,7 +163,8 @@ def gpu_gemv(g, M, v, beta=0.0, y0=None, transposed_storage=False):
         Md = g.dev(M)
         mat = make_mat(Md.data_ptr(), (m, k), (k, 1))
     y = g.dev(y0) if y0 is not None else g.empty(m)
-    g.handle().gemv(m, k, mat, g.dev(v).data_ptr(), 1, y.data_ptr(), beta)
+    vd = g.dev(v)
+    g.handle().gemv(m, k, mat, vd.data_ptr(), 1, y.data_ptr(), beta)
     return g.host(y)
 
 
@@ -174,7 +180,8 @@ def gpu_vecmat(g, v, M, transposed_storage=False):
         Md = g.dev(M)
         mat = make_mat(Md.data_ptr(), (k, n), (n, 1))
     y = g.empty(n)
-    g.handle().vecmat(k, n, g.dev(v).data_ptr(), 1, mat, y.data_ptr())
+    vd = g.dev(v)
+    g.handle().vecmat(k, n, vd.data_ptr(), 1, mat, y.data_ptr())
     return g.host(y)
 
 
@@ -225,4 +232,5 @@ def test_gemv_rejects_a_matrix_without_a_unit_stride(g):
 
     A = g.dev(np.zeros((8, 16), np.float32))
     with pytest.raises(TenmoError):
-        g.handle().gemv(4, 4, make_mat(A.data_ptr(), (4, 4), (32, 2)), g.empty(4).data_ptr(), 1, g.empty(4).data_ptr())
+        xv, yv = g.empty(4), g.empty(4)
+        g.handle().gemv(4, 4, make_mat(A.data_ptr(), (4, 4), (32, 2)), xv.data_ptr(), 1, yv.data_ptr())
