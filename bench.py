@@ -311,7 +311,8 @@ def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen)
     uid = exchange_unique_id(h.dp_get_unique_id, rank, world, torch_broadcast_bytes(dev)) if args.dp_exchange == "nccl" else None
     def build(exchange, unique_id):
         return MLPTrainer(Ws, bs, batch=hi - lo, lr=0.01, momentum=0.9, algo="3xtf32", handle=h, rank=rank, world=world,
-                          unique_id=unique_id, device=local_rank, exchange=exchange, all_gather_bytes=torch_all_gather_bytes(dev))
+                          unique_id=unique_id, device=local_rank, exchange=exchange, all_gather_bytes=torch_all_gather_bytes(dev),
+                          overlap=False if args.dp_no_overlap else (True if args.dp_overlap else None))
 
     tr = build_with_fallback(build, args.dp_exchange, uid, h, rank, world, dev)
     Xg = torch.randn(gb, dims[0], generator=gen)
@@ -349,6 +350,9 @@ def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen)
         "config": "4096-4096-4096-4096-1000 Linear+ReLU, softmax-CE, fp32 (3xTF32 GEMMs), N(0,1) inputs, U(+-sqrt(6/in)) weights",
     }
     res["exchange"] = tr.exchange
+    res["overlap"] = tr.overlap
+    if world > 1 and tr.exchange in ("p2p", "p2p_allreduce"):
+        res["exchange_kernel"] = measure_exchange_kernel(tr, h, timed, world)
     if rank == 0 and world == 1 and not args.no_cpu:
         res["cpu_baseline"] = cpu_mlp_baseline(dims, Ws, bs, Xg[:512].numpy(), yg[:512].numpy(), steps=2,
                                                note="wide MLP, a 512-row sample of the 8192-row batch")
@@ -363,6 +367,35 @@ def measure_wide_mlp(h, rank, world, local_rank, timed, args, uniform_init, gen)
     torch.cuda.empty_cache()
     torch.cuda.nvtx.range_pop()
     return res
+
+
+def measure_exchange_kernel(tr, h, timed, world):
+    """The peer-memory exchange kernel alone on the largest layer (nothing else running), against NVLink: per call a rank
+    receives (W-1)/W of the range twice -- the peers' gradient copies it reads for its shard and the finished elements the
+    peers push into its bucket -- so the inbound traffic per rank is 2 (W-1)/W 4 count bytes (and as much goes out); the
+    measured peer-copy bandwidth of this pool is 770 GB/s per direction."""
+    import torch
+
+    start, count = max(tr.layer_span, key=lambda sc: sc[1])
+    h.set_stream(torch.cuda.current_stream().cuda_stream)
+
+    def call():
+        if tr.sharded:   # lr = 0, momentum = 0: parameters and velocities come out as they went in
+            h.dp_p2p_sgd_step(start, tr.numel + start, count, tr.V.data_ptr() + 4 * start, 0, 0, 0.0, 0.0, 0.0, 1.0 / world)
+        else:
+            h.dp_p2p_allreduce_sum(start, count)
+
+    tr.G.zero_()
+    for _ in range(3):
+        call()
+    iters = 10
+    ms = timed(call, iters) / iters
+    inbound = 2.0 * (world - 1) / world * 4.0 * count
+    gbs = inbound / (ms * 1e-3) / 1e9
+    return {"kernel": "dp_p2p_kernel<W, sharded optimiser>" if tr.sharded else "dp_p2p_kernel<W, all-reduce>", "floats": count, "ms": ms,
+            "nvlink_inbound_bytes": inbound,
+            "roofline": {"bound": "nvlink", "achieved": gbs, "peak": 770.0, "unit": "GB/s", "frac": gbs / 770.0,
+                         "peak_note": "measured peer-copy bandwidth per direction on this pool (nominal 900)"}}
 
 
 def measure_cnn(h, rank, world, local_rank, timed, args, rng, gen):
@@ -1004,6 +1037,9 @@ def main():
     ap.add_argument("--dp-exchange", choices=["auto", "nccl", "p2p", "p2p_allreduce"], default="auto",
                     help="gradient exchange of the training legs at N > 1: NCCL all-reduce or the library's peer-memory kernel; "
                          "auto = peer-memory from 8 ranks up (measured: 17 %% faster at 8 ranks, 6 %% slower at 4, 5 %% slower at 2)")
+    ap.add_argument("--dp-overlap", action="store_true", help="force the per-layer exchange onto a side stream beside the backward GEMMs")
+    ap.add_argument("--dp-no-overlap", action="store_true",
+                    help="run the gradient exchange after the backward pass on the compute stream (for measuring what the overlap hides)")
     ap.add_argument("--legs", default="wide_mlp,cnn,mnist_mlp", help="which training legs to run after the GEMM arm")
     ap.add_argument("--kernels", action="store_true",
                     help="time the bandwidth-bound kernels of the path against the HBM roofline (one JSON line each)")

@@ -165,6 +165,11 @@ const char* tenmo_gemm_last_kernel(tenmo_ctx* ctx);
  * strict-fp32 kernels, whose results must not depend on the machine).  TENMO_TC_STREAMK=0 in the environment turns
  * it off.  No reference counterpart. */
 int tenmo_gemm_last_stream_k(tenmo_ctx* ctx);
+/* 1 when that launch ran as CTA pairs: two CTAs on neighbouring SMs share a 256 x 256 tile (tcgen05.mma.cta_group::2,
+ * each staging half of the right-hand tile; three shared-memory stages instead of two).  Chosen when the product has at
+ * least two such tiles per pair of SMs; TENMO_TC_PAIR=0 / 1 in the environment forces it off / on.  No reference
+ * counterpart. */
+int tenmo_gemm_last_pair(tenmo_ctx* ctx);
 
 /* ---- matrix @ vector, vector @ matrix ---------------------------------------------------------------
  * y[i] = sum_k A[i,k] x[k] (+ y[i] when beta == 1): MatrixVectorMulNd.forward (matrixvector.mojo:205-285), and
@@ -360,6 +365,10 @@ int tenmo_dp_p2p_allreduce_sum_f32(tenmo_ctx* ctx, int64_t offset, int64_t count
 int tenmo_dp_p2p_sgd_step_f32(tenmo_ctx* ctx, int64_t grad_offset, int64_t param_offset, int64_t count, float* v,
                               float* p_lo, int64_t lo_count, float lr, float momentum, float weight_decay,
                               float grad_scale);
+/* Form of the exchange kernels.  Off (default): 128 CTAs x 512 threads, for an exchange that runs with nothing beside it
+ * (fastest by itself).  On: 128 CTAs x 128 threads at no more than 85 registers, small enough to share an SM with the
+ * persistent GEMM CTA, for a host that overlaps the exchange with the backward GEMMs.  Every rank must choose the same. */
+int tenmo_dp_p2p_set_coresident(tenmo_ctx* ctx, int on);
 int tenmo_dp_p2p_close(tenmo_ctx* ctx);
 
 #ifdef __cplusplus

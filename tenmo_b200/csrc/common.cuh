@@ -36,6 +36,7 @@ struct tenmo_ctx {
     int last_gemm_algo = -1;
     const char* last_gemm_kernel = "";
     int last_gemm_sk_units = 0;
+    bool last_gemm_pair = false;  // the last tensor-core GEMM ran as CTA pairs (tcgen05 cta_group::2)
     bool pdl = true;  // programmatic dependent launch for small kernels (TENMO_PDL=0: off)
     // workspace (grown on demand, never shrunk): lo planes for the 3xTF32 kernel, reduction partials
     void* ws = nullptr;
@@ -69,6 +70,7 @@ struct tenmo_ctx {
     void* p2p_peer_flags[8] = {nullptr};
     int64_t p2p_count = 0;
     int p2p_rank = 0, p2p_world = 0;
+    bool p2p_small = false;  // launch the exchange in its co-resident form (tenmo_dp_p2p_set_coresident)
 };
 
 int tenmo_set_error(tenmo_ctx* ctx, int status, const char* fmt, ...);

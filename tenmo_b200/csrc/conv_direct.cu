@@ -472,6 +472,28 @@ __global__ void __launch_bounds__(CD_THREADS) conv_dw_gather_kernel(const DwGath
     }
 }
 
+// The per-slab partial rows [dW | db] added in slab order (one thread per column, sixteen loads in flight): one launch
+// finishes both gradients.
+__global__ void __launch_bounds__(CD_THREADS) conv_reduce_partials_kernel(const float* __restrict__ partials, int slabs, int n_w,
+                                                                         int n_b, float* __restrict__ dw, float* __restrict__ db,
+                                                                         float beta) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int row_len = n_w + n_b;
+    if (c >= row_len) return;
+    float acc = 0.f;
+    int s = 0;
+    for (; s + 16 <= slabs; s += 16) {
+        float v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) v[u] = __ldcs(partials + (int64_t)(s + u) * row_len + c);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) acc += v[u];
+    }
+    for (; s < slabs; ++s) acc += __ldcs(partials + (int64_t)s * row_len + c);
+    float* dst = c < n_w ? dw + c : db + (c - n_w);
+    *dst = beta != 0.f ? *dst + acc : acc;
+}
+
 int conv_check(tenmo_ctx* ctx, const char* who, int64_t N, int64_t C, int64_t H, int64_t W, int64_t Cout, int KH, int KW, int stride,
                int dil, int pad, int64_t* Ho, int64_t* Wo) {
     if (N < 0 || C <= 0 || H <= 0 || W <= 0 || Cout <= 0 || KH <= 0 || KW <= 0 || stride <= 0 || dil <= 0 || pad < 0)
@@ -492,6 +514,9 @@ int launch_fwd3x3(tenmo_ctx* ctx, ConvArgs& a) {
     static bool attr_set[64] = {false};
     if (!attr_set[ctx->device & 63]) {
         TENMO_CUDA_TRY(ctx, cudaFuncSetAttribute(conv3x3_fwd_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+        // two CTAs per SM need the large shared-memory split of the L1
+        TENMO_CUDA_TRY(ctx, cudaFuncSetAttribute(conv3x3_fwd_kernel<TH, TW>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                 cudaSharedmemCarveoutMaxShared));
         attr_set[ctx->device & 63] = true;
     }
     a.tiles_x = (a.Wo + TW - 1) / TW;
@@ -532,6 +557,8 @@ int launch_dw3x3(tenmo_ctx* ctx, const DwArgs& a, int slabs) {
     static bool attr_set[64] = {false};
     if (!attr_set[ctx->device & 63]) {
         TENMO_CUDA_TRY(ctx, cudaFuncSetAttribute(conv3x3_dw_kernel<CI_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        TENMO_CUDA_TRY(ctx, cudaFuncSetAttribute(conv3x3_dw_kernel<CI_T>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                 cudaSharedmemCarveoutMaxShared));
         attr_set[ctx->device & 63] = true;
     }
     dim3 grid((unsigned)slabs, (unsigned)((a.Cout + CO_T - 1) / CO_T));
@@ -611,7 +638,7 @@ int tenmo_conv2d_bwd_weight_f32(tenmo_ctx* ctx, const float* x, const float* g, 
     }
     if (fast3x3(KH, KW, stride, dilation)) {
         const int co_blocks = (int)((Cout + CO_T - 1) / CO_T);
-        // about two CTAs per SM in total, at most TENMO_COLSUM_SEQ_ROWS slabs (their sum is the sequential column sum)
+        // about two CTAs per SM in total, at most TENMO_COLSUM_SEQ_ROWS slabs
         int64_t slabs = (2 * (int64_t)ctx->sm_count + co_blocks - 1) / co_blocks;
         if (slabs > N) slabs = N;
         if (slabs > TENMO_COLSUM_SEQ_ROWS) slabs = TENMO_COLSUM_SEQ_ROWS;
@@ -632,11 +659,11 @@ int tenmo_conv2d_bwd_weight_f32(tenmo_ctx* ctx, const float* x, const float* g, 
         else if (C <= 16) st = launch_dw3x3<16>(ctx, a, (int)slabs);
         else st = launch_dw3x3<32>(ctx, a, (int)slabs);
         if (st != TENMO_OK) return st;
-        // the slabs in ascending order: dW, then db, out of the same partial rows (the column sum does not touch the workspace
-        // for so few rows)
-        st = tenmo_colsum_f32(ctx, a.partials, slabs, n_w, row_len, dW, beta);
-        if (st != TENMO_OK) return st;
-        return tenmo_colsum_f32(ctx, a.partials + n_w, slabs, Cout, row_len, db, beta);
+        // the slabs in ascending order, dW and db out of the same partial rows
+        conv_reduce_partials_kernel<<<(unsigned)((row_len + CD_THREADS - 1) / CD_THREADS), CD_THREADS, 0, ctx->stream>>>(
+            a.partials, (int)slabs, (int)n_w, (int)Cout, dW, db, beta);
+        TENMO_LAUNCH_CHECK(ctx, "conv_reduce_partials_kernel");
+        return TENMO_OK;
     }
     DwGatherArgs a;
     a.x = x; a.g = g; a.g_mask = g_mask; a.dw = dW; a.db = db;

@@ -3,7 +3,10 @@
 // Why not only NCCL: the exchange of a layer's gradients should run beside the backward GEMMs of the layers below,
 // but the persistent GEMM kernel holds every SM with one large CTA, and NCCL's CTAs (hundreds of threads, ~100
 // registers each) cannot share an SM with it, so they wait for GEMM CTAs to leave.  The kernel here is built to
-// co-reside: 64 CTAs of 512 threads, 64 registers, no shared-memory tile.
+// co-reside: the GEMM CTA leaves about 11 K of an SM's 64 K registers and a few KB of shared memory free, so the exchange
+// runs as 128 CTAs of 128 threads at no more than 85 registers each (one fits beside the GEMM CTA of every SM it lands
+// on), with no shared-memory tile.  A larger CTA would not fit and would wait for a GEMM CTA to leave, then keep that SM
+// from the next GEMM launch for as long as the exchange waits on its peers.
 //
 // Setup (one process per GPU): every rank allocates the gradient bucket and a small flag block with
 // tenmo_dp_p2p_alloc, the ranks exchange the two CUDA IPC handles out of band (the host's job, like NCCL's unique id),
@@ -14,34 +17,39 @@
 //   reduce-scatter: rank r owns shard r of the range and adds the W copies of it in rank order 0..W-1 (peer copies
 //       are read over NVLink with 16-byte loads) into its own bucket -- every element is added once, by its owner,
 //       so all ranks end with identical bits;
-//   wait until every peer has reduced its shard; all-gather: copy the peers' reduced shards into the own bucket;
-//   wait until every peer has finished reading this rank's bucket (the next backward pass overwrites it).
-// The three waits are flags in peer memory, one per (phase, source rank, CTA): CTA b of a rank only ever depends on
+//       and the owner writes each finished element straight into EVERY rank's bucket (plain peer stores: the all-gather
+//       travels as pushes while the reduce-scatter's loads are still coming in, so both NVLink directions are busy);
+//   wait until every peer has finished its shard: its pushes have then landed here (it fenced before it raised its flag)
+//       and it has finished reading this rank's bucket (the next backward pass may overwrite it).
+// The two waits are flags in peer memory, one per (phase, source rank, CTA): CTA b of a rank only ever depends on
 // CTA b of its peers (a shard is cut into chunks dealt round-robin to the CTAs, identically on every rank), so no
 // grid-wide synchronisation is needed.  Flags carry the call's epoch (monotonic), so nothing is ever reset.
 // The epoch lives on the device: a word of this rank's own flag block counts the calls that have completed, every CTA
 // reads it on entry and the last CTA to leave advances it, so a call that is replayed from a captured CUDA graph
 // takes the next epoch like an eagerly launched one.
 // Every wait is bounded (2 s): on expiry the CTA raises the context status word and returns.
-// No multicast, no TMA: plain peer loads and stores.  Roofline: NVLink, 2 * (W-1)/W * 4 * count bytes read per rank.
+// No multicast, no TMA: plain peer loads and stores.  Roofline: NVLink, (W-1)/W * 4 * count bytes per rank in EACH
+// direction (gradient copies read in, finished elements written out, at the same time).
 //
-// dp_p2p_sgd_kernel is the same exchange with the optimiser sharded over the ranks (the bucket then holds the
+// dp_p2p_kernel<.., true> is the same exchange with the optimiser sharded over the ranks (the bucket then holds the
 // gradients AND the parameters): the owner of a shard adds the W gradient copies, applies SGD-momentum to its shard of
 // the parameters (its velocities never leave the rank), and the all-gather phase distributes updated PARAMETERS
 // instead of summed gradients, writing their 3xTF32 lo plane as they land.  Per rank the optimiser touches 1/W of the
 // parameters instead of all of them, and no separate SGD launch follows the exchange.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
 
-constexpr int P2P_CTAS = 64;
-constexpr int P2P_THREADS = 512;
+constexpr int P2P_CTAS = 128;
+constexpr int P2P_THREADS = 128;      // co-resident form; the stand-alone form runs P2P_THREADS_BIG per CTA
+constexpr int P2P_THREADS_BIG = 512;
 constexpr int P2P_MAX_WORLD = 8;
 constexpr int P2P_FLAG_WORDS = 3 * P2P_MAX_WORLD * P2P_CTAS;
 constexpr int P2P_EPOCH_WORD = P2P_FLAG_WORDS;       // own block only: number of completed calls
 constexpr int P2P_TICKET_WORD = P2P_FLAG_WORDS + 1;  // own block only: CTAs of the running call that have left
 constexpr int P2P_FLAG_ALLOC_WORDS = P2P_FLAG_WORDS + 64;
-constexpr int P2P_CHUNK = 4 * P2P_THREADS;  // floats per chunk: one float4 per thread
 constexpr uint64_t P2P_WAIT_LIMIT_NS = 2000000000ull;
 
 struct P2PArgs {
@@ -66,10 +74,11 @@ __device__ __forceinline__ uint64_t p2p_now_ns() {
 
 // Signal "CTA b of this rank has reached `phase` of call `epoch`" to every rank, then wait for the same from every
 // rank's CTA b.  False if a wait ran out.
-__device__ bool p2p_barrier(const P2PArgs& a, uint32_t epoch, int phase, int* ok_smem) {
+__device__ bool p2p_barrier(const P2PArgs& a, uint32_t epoch, int phase) {
     __threadfence_system();  // this thread's bucket writes are visible system-wide before the flag is
     __syncthreads();
     const int t = threadIdx.x;
+    int ok = 1;
     if (t < a.world) {
         uint32_t* dst = a.flags[t] + (phase * P2P_MAX_WORLD + a.rank) * P2P_CTAS + blockIdx.x;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
@@ -80,24 +89,18 @@ __device__ bool p2p_barrier(const P2PArgs& a, uint32_t epoch, int phase, int* ok
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
             if ((int32_t)(v - epoch) >= 0) break;
             if ((it & 63u) == 63u && p2p_now_ns() - t0 > P2P_WAIT_LIMIT_NS) {
-                *ok_smem = 0;
+                ok = 0;
                 break;
             }
         }
     }
-    __syncthreads();
-    return *ok_smem != 0;
+    return __syncthreads_and(ok) != 0;  // no shared memory: the kernel must fit beside a CTA that uses almost all of it
 }
 
 // Epoch of the running call: one more than the calls this rank has completed (every CTA reads the word before any
 // CTA of the same call can advance it, because the advance happens after ALL of them have left).
-__device__ uint32_t p2p_enter(const P2PArgs& a, int* ok_smem, uint32_t* epoch_smem) {
-    if (threadIdx.x == 0) {
-        *ok_smem = 1;
-        *epoch_smem = *reinterpret_cast<volatile uint32_t*>(a.flags[a.rank] + P2P_EPOCH_WORD) + 1u;
-    }
-    __syncthreads();
-    return *epoch_smem;
+__device__ uint32_t p2p_enter(const P2PArgs& a) {
+    return *reinterpret_cast<volatile uint32_t*>(a.flags[a.rank] + P2P_EPOCH_WORD) + 1u;
 }
 // Every CTA leaves through here (also after a wait ran out): the last one advances the epoch and re-arms the ticket.
 __device__ void p2p_leave(const P2PArgs& a, uint32_t epoch, bool timed_out) {
@@ -125,10 +128,14 @@ __device__ __forceinline__ void p2p_sgd_one(float& p, float g, float& v, const P
     }
 }
 
-__global__ void __launch_bounds__(P2P_THREADS) dp_p2p_allreduce_kernel(const P2PArgs a) {
-    __shared__ int ok_smem;
-    __shared__ uint32_t epoch_smem;
-    const uint32_t epoch = p2p_enter(a, &ok_smem, &epoch_smem);
+// One kernel body for both exchanges.  WT: the world size rounded up to 2, 4 or 8 (loop bounds known at compile time).
+// SGD: the sharded-optimiser form.  A thread keeps 8 / WT chunks x WT copies = eight 16-byte gradient loads in flight per
+// turn whatever the world size, so that the NVLink round trip (a few microseconds) is paid once per eight loads.
+template <int WT, bool SGD, int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS == P2P_THREADS ? 6 : 1) dp_p2p_kernel(const P2PArgs a) {
+    constexpr int U = 8 / WT;
+    constexpr int P2P_CHUNK = 4 * THREADS;  // floats per chunk: one float4 per thread
+    const uint32_t epoch = p2p_enter(a);
     const int W = a.world, r = a.rank, b = blockIdx.x, t = threadIdx.x;
     // shards: equal sizes, multiples of a chunk's float4 granularity; the last may be short or empty
     const int64_t sz = ((a.count + W - 1) / W + 3) & ~(int64_t)3;
@@ -136,175 +143,140 @@ __global__ void __launch_bounds__(P2P_THREADS) dp_p2p_allreduce_kernel(const P2P
         const int64_t lo = (int64_t)p * sz;
         return lo >= a.count ? (int64_t)0 : (a.count - lo < sz ? a.count - lo : sz);
     };
-    const bool vec = ((a.off | sz) & 3) == 0;  // buckets come from cudaMalloc: 16-byte alignment follows from the offsets
+    const bool has_v = SGD && a.momentum > 0.f;
+    // buckets come from cudaMalloc: 16-byte alignment follows from the offsets
+    const bool vec = ((a.off | a.p_off | sz) & 3) == 0 &&
+                     (!SGD || ((reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.lo)) & 15u) == 0);
+    const int64_t src_off = SGD ? a.p_off : a.off;       // what the all-gather phase distributes: parameters or sums
+    float* const mine = a.buf[r] + src_off;              // this rank's copy of it
+    const int64_t turn = (int64_t)gridDim.x * U * P2P_CHUNK;
 
-    if (!p2p_barrier(a, epoch, 0, &ok_smem)) { p2p_leave(a, epoch, true); return; }
+    if (!p2p_barrier(a, epoch, 0)) { p2p_leave(a, epoch, true); return; }
 
-    {   // reduce-scatter: this rank's shard, chunks b, b + CTAS, ...
-        const int64_t base = a.off + (int64_t)r * sz, len = shard_len(r);
-        for (int64_t c0 = (int64_t)b * P2P_CHUNK; c0 < len; c0 += (int64_t)P2P_CTAS * P2P_CHUNK) {
-            const int64_t j = c0 + 4 * t;
-            if (j >= len) continue;
-            if (vec && j + 3 < len) {
-                // all W loads are issued before the first add: one NVLink round trip per element, not W
-                float4 v[P2P_MAX_WORLD];
-#pragma unroll
-                for (int p = 0; p < P2P_MAX_WORLD; ++p)
-                    if (p < W) v[p] = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + base + j));
-                float4 acc = v[0];
-#pragma unroll
-                for (int p = 1; p < P2P_MAX_WORLD; ++p)
-                    if (p < W) { acc.x += v[p].x; acc.y += v[p].y; acc.z += v[p].z; acc.w += v[p].w; }
-                *reinterpret_cast<float4*>(a.buf[r] + base + j) = acc;
-            } else {
-                for (int e = 0; e < 4 && j + e < len; ++e) {
-                    float acc = __ldcg(a.buf[0] + base + j + e);
-                    for (int p = 1; p < W; ++p) acc += __ldcg(a.buf[p] + base + j + e);
-                    a.buf[r][base + j + e] = acc;
-                }
-            }
-        }
-    }
-
-    if (!p2p_barrier(a, epoch, 1, &ok_smem)) { p2p_leave(a, epoch, true); return; }
-
-    // all-gather: the peers' reduced shards (the same chunk of every peer in one go, so that W-1 loads are in flight)
-    for (int64_t c0 = (int64_t)b * P2P_CHUNK; c0 < sz; c0 += (int64_t)P2P_CTAS * P2P_CHUNK) {
-        const int64_t j = c0 + 4 * t;
-        float4 v[P2P_MAX_WORLD];
-        bool full[P2P_MAX_WORLD];
-#pragma unroll
-        for (int q = 1; q < P2P_MAX_WORLD; ++q) {
-            full[q] = false;
-            if (q < W) {
-                const int p = (r + q) % W;  // start with the next rank: the ranks do not all read the same peer at once
-                full[q] = vec && j + 3 < shard_len(p);
-                if (full[q]) v[q] = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + a.off + (int64_t)p * sz + j));
-            }
-        }
-#pragma unroll
-        for (int q = 1; q < P2P_MAX_WORLD; ++q) {
-            if (q < W) {
-                const int p = (r + q) % W;
-                const int64_t base = a.off + (int64_t)p * sz, len = shard_len(p);
-                if (full[q]) {
-                    *reinterpret_cast<float4*>(a.buf[r] + base + j) = v[q];
-                } else {
-                    for (int e = 0; e < 4 && j + e < len; ++e) a.buf[r][base + j + e] = __ldcg(a.buf[p] + base + j + e);
-                }
-            }
-        }
-    }
-
-    p2p_leave(a, epoch, !p2p_barrier(a, epoch, 2, &ok_smem));
-}
-
-// Reduce-scatter of the gradients, SGD-momentum on the own shard of the parameters, all-gather of the updated
-// parameters (with their lo plane).  Same shards, chunks, flags and waits as the kernel above.
-__global__ void __launch_bounds__(P2P_THREADS) dp_p2p_sgd_kernel(const P2PArgs a) {
-    __shared__ int ok_smem;
-    __shared__ uint32_t epoch_smem;
-    const uint32_t epoch = p2p_enter(a, &ok_smem, &epoch_smem);
-    const int W = a.world, r = a.rank, b = blockIdx.x, t = threadIdx.x;
-    const int64_t sz = ((a.count + W - 1) / W + 3) & ~(int64_t)3;
-    auto shard_len = [&](int p) {
-        const int64_t lo = (int64_t)p * sz;
-        return lo >= a.count ? (int64_t)0 : (a.count - lo < sz ? a.count - lo : sz);
-    };
-    const bool has_v = a.momentum > 0.f;
-    const bool vec = ((a.off | a.p_off | sz) & 3) == 0 && ((reinterpret_cast<uintptr_t>(a.v) | reinterpret_cast<uintptr_t>(a.lo)) & 15u) == 0;
-    float* const P = a.buf[r] + a.p_off;  // this rank's copy of the parameters of the range
-
-    if (!p2p_barrier(a, epoch, 0, &ok_smem)) { p2p_leave(a, epoch, true); return; }
-
-    {   // own shard: sum the W gradient copies in rank order, then the optimiser step
+    {   // own shard: the W gradient copies added in rank order (every element once, by its owner), then the optimiser
         const int64_t base = (int64_t)r * sz, len = shard_len(r);
-        for (int64_t c0 = (int64_t)b * P2P_CHUNK; c0 < len; c0 += (int64_t)P2P_CTAS * P2P_CHUNK) {
-            const int64_t j = c0 + 4 * t;
-            if (j >= len) continue;
-            const int64_t i = base + j;  // index inside the range
-            if (vec && j + 3 < len) {
-                float4 gv[P2P_MAX_WORLD];
+        for (int64_t c0 = (int64_t)b * U * P2P_CHUNK; c0 < len; c0 += turn) {
+            float4 gv[U][WT];
+            bool full[U];
 #pragma unroll
-                for (int p = 0; p < P2P_MAX_WORLD; ++p)
-                    if (p < W) gv[p] = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + a.off + i));
-                float4 pp = *reinterpret_cast<const float4*>(P + i);
-                float4 vv = has_v ? *reinterpret_cast<const float4*>(a.v + i) : make_float4(0, 0, 0, 0);
-                float4 g = gv[0];
+            for (int u = 0; u < U; ++u) {
+                const int64_t j = c0 + (int64_t)u * P2P_CHUNK + 4 * t;
+                full[u] = vec && j + 3 < len;
+                if (full[u]) {
 #pragma unroll
-                for (int p = 1; p < P2P_MAX_WORLD; ++p)
-                    if (p < W) { g.x += gv[p].x; g.y += gv[p].y; g.z += gv[p].z; g.w += gv[p].w; }
-                p2p_sgd_one(pp.x, g.x, vv.x, a, has_v);
-                p2p_sgd_one(pp.y, g.y, vv.y, a, has_v);
-                p2p_sgd_one(pp.z, g.z, vv.z, a, has_v);
-                p2p_sgd_one(pp.w, g.w, vv.w, a, has_v);
-                *reinterpret_cast<float4*>(P + i) = pp;
-                if (has_v) *reinterpret_cast<float4*>(a.v + i) = vv;
-                if (i + 3 < a.lo_count) {
-                    *reinterpret_cast<float4*>(a.lo + i) =
-                        make_float4(tenmo_tf32_lo(pp.x), tenmo_tf32_lo(pp.y), tenmo_tf32_lo(pp.z), tenmo_tf32_lo(pp.w));
-                } else {
-                    const float e4[4] = {pp.x, pp.y, pp.z, pp.w};
-                    for (int e = 0; e < 4; ++e)
-                        if (i + e < a.lo_count) a.lo[i + e] = tenmo_tf32_lo(e4[e]);
-                }
-            } else {
-                for (int e = 0; e < 4 && j + e < len; ++e) {
-                    float g = __ldcg(a.buf[0] + a.off + i + e);
-                    for (int p = 1; p < W; ++p) g += __ldcg(a.buf[p] + a.off + i + e);
-                    float pp = P[i + e], vv = has_v ? a.v[i + e] : 0.f;
-                    p2p_sgd_one(pp, g, vv, a, has_v);
-                    P[i + e] = pp;
-                    if (has_v) a.v[i + e] = vv;
-                    if (i + e < a.lo_count) a.lo[i + e] = tenmo_tf32_lo(pp);
+                    for (int p = 0; p < WT; ++p)
+                        if (p < W) gv[u][p] = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + a.off + base + j));
                 }
             }
-        }
-    }
-
-    if (!p2p_barrier(a, epoch, 1, &ok_smem)) { p2p_leave(a, epoch, true); return; }
-
-    // all-gather of the updated parameters: the peers' shards, the same chunk of every peer in one go
-    for (int64_t c0 = (int64_t)b * P2P_CHUNK; c0 < sz; c0 += (int64_t)P2P_CTAS * P2P_CHUNK) {
-        const int64_t j = c0 + 4 * t;
-        float4 pv[P2P_MAX_WORLD];
-        bool full[P2P_MAX_WORLD];
 #pragma unroll
-        for (int q = 1; q < P2P_MAX_WORLD; ++q) {
-            full[q] = false;
-            if (q < W) {
-                const int p = (r + q) % W;
-                full[q] = vec && j + 3 < shard_len(p);
-                if (full[q]) pv[q] = __ldcg(reinterpret_cast<const float4*>(a.buf[p] + a.p_off + (int64_t)p * sz + j));
-            }
-        }
+            for (int u = 0; u < U; ++u) {
+                const int64_t j = c0 + (int64_t)u * P2P_CHUNK + 4 * t;
+                const int64_t i = base + j;  // index inside the range
+                if (full[u]) {
+                    float4 g = gv[u][0];
 #pragma unroll
-        for (int q = 1; q < P2P_MAX_WORLD; ++q) {
-            if (q < W) {
-                const int p = (r + q) % W;
-                const int64_t i = (int64_t)p * sz + j, len = shard_len(p);
-                if (full[q]) {
-                    *reinterpret_cast<float4*>(P + i) = pv[q];
-                    if (i + 3 < a.lo_count) {
-                        *reinterpret_cast<float4*>(a.lo + i) = make_float4(tenmo_tf32_lo(pv[q].x), tenmo_tf32_lo(pv[q].y),
-                                                                           tenmo_tf32_lo(pv[q].z), tenmo_tf32_lo(pv[q].w));
+                    for (int p = 1; p < WT; ++p)
+                        if (p < W) { g.x += gv[u][p].x; g.y += gv[u][p].y; g.z += gv[u][p].z; g.w += gv[u][p].w; }
+                    if (!SGD) {
+#pragma unroll
+                        for (int p = 0; p < WT; ++p)  // the finished sum goes to every rank's bucket, this one's included
+                            if (p < W) *reinterpret_cast<float4*>(a.buf[p] + src_off + i) = g;
                     } else {
-                        const float e4[4] = {pv[q].x, pv[q].y, pv[q].z, pv[q].w};
-                        for (int e = 0; e < 4; ++e)
-                            if (i + e < a.lo_count) a.lo[i + e] = tenmo_tf32_lo(e4[e]);
+                        float4 pp = __ldcs(reinterpret_cast<const float4*>(mine + i));
+                        float4 vv = has_v ? __ldcs(reinterpret_cast<const float4*>(a.v + i)) : make_float4(0, 0, 0, 0);
+                        p2p_sgd_one(pp.x, g.x, vv.x, a, has_v);
+                        p2p_sgd_one(pp.y, g.y, vv.y, a, has_v);
+                        p2p_sgd_one(pp.z, g.z, vv.z, a, has_v);
+                        p2p_sgd_one(pp.w, g.w, vv.w, a, has_v);
+#pragma unroll
+                        for (int p = 0; p < WT; ++p)  // the updated parameters go to every rank's copy, this one's included
+                            if (p < W) *reinterpret_cast<float4*>(a.buf[p] + src_off + i) = pp;
+                        if (has_v) __stcs(reinterpret_cast<float4*>(a.v + i), vv);
+                        if (i + 3 < a.lo_count) {
+                            __stcs(reinterpret_cast<float4*>(a.lo + i),
+                                   make_float4(tenmo_tf32_lo(pp.x), tenmo_tf32_lo(pp.y), tenmo_tf32_lo(pp.z), tenmo_tf32_lo(pp.w)));
+                        } else {
+                            const float e4[4] = {pp.x, pp.y, pp.z, pp.w};
+                            for (int e = 0; e < 4; ++e)
+                                if (i + e < a.lo_count) a.lo[i + e] = tenmo_tf32_lo(e4[e]);
+                        }
                     }
                 } else {
                     for (int e = 0; e < 4 && j + e < len; ++e) {
-                        const float x = __ldcg(a.buf[p] + a.p_off + i + e);
-                        P[i + e] = x;
-                        if (i + e < a.lo_count) a.lo[i + e] = tenmo_tf32_lo(x);
+                        float g = __ldcg(a.buf[0] + a.off + i + e);
+                        for (int p = 1; p < W; ++p) g += __ldcg(a.buf[p] + a.off + i + e);
+                        if (!SGD) {
+                            for (int p = 0; p < W; ++p) a.buf[p][src_off + i + e] = g;
+                        } else {
+                            float pp = mine[i + e], vv = has_v ? a.v[i + e] : 0.f;
+                            p2p_sgd_one(pp, g, vv, a, has_v);
+                            for (int p = 0; p < W; ++p) a.buf[p][src_off + i + e] = pp;
+                            if (has_v) a.v[i + e] = vv;
+                            if (i + e < a.lo_count) a.lo[i + e] = tenmo_tf32_lo(pp);
+                        }
                     }
                 }
             }
         }
     }
 
-    p2p_leave(a, epoch, !p2p_barrier(a, epoch, 2, &ok_smem));
+    // every rank's pushes into this rank's bucket have landed once its flag of this phase is seen (it fenced first); the
+    // peers are also done reading this rank's gradients, which the next backward pass may now overwrite
+    const bool ok = p2p_barrier(a, epoch, 1);
+    if (ok && SGD && a.lo_count > 0) {
+        // lo plane of the parameters the peers pushed (the own shard's was written with the update): a local pass over the
+        // SAME chunks this CTA's counterparts on the peers wrote -- their flags are the only ones it has waited for
+        for (int64_t c0 = (int64_t)b * U * P2P_CHUNK; c0 < sz; c0 += turn) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t j = c0 + (int64_t)u * P2P_CHUNK + 4 * t;
+#pragma unroll
+                for (int q = 1; q < WT; ++q) {
+                    if (q < W) {
+                        const int p = (r + q) % W;
+                        const int64_t i = (int64_t)p * sz + j, len = shard_len(p);
+                        if (vec && j + 3 < len && i + 3 < a.lo_count) {
+                            const float4 x = __ldcg(reinterpret_cast<const float4*>(mine + i));
+                            __stcs(reinterpret_cast<float4*>(a.lo + i),
+                                   make_float4(tenmo_tf32_lo(x.x), tenmo_tf32_lo(x.y), tenmo_tf32_lo(x.z), tenmo_tf32_lo(x.w)));
+                        } else {
+                            for (int e = 0; e < 4 && j + e < len; ++e)
+                                if (i + e < a.lo_count) a.lo[i + e] = tenmo_tf32_lo(__ldcg(mine + i + e));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    p2p_leave(a, epoch, !ok);
+}
+
+template <bool SGD>
+void p2p_launch(const P2PArgs& a, int grid, cudaStream_t stream, bool big) {
+    if (big) {
+        if (a.world <= 2) dp_p2p_kernel<2, SGD, P2P_THREADS_BIG><<<grid, P2P_THREADS_BIG, 0, stream>>>(a);
+        else if (a.world <= 4) dp_p2p_kernel<4, SGD, P2P_THREADS_BIG><<<grid, P2P_THREADS_BIG, 0, stream>>>(a);
+        else dp_p2p_kernel<8, SGD, P2P_THREADS_BIG><<<grid, P2P_THREADS_BIG, 0, stream>>>(a);
+    } else {
+        if (a.world <= 2) dp_p2p_kernel<2, SGD, P2P_THREADS><<<grid, P2P_THREADS, 0, stream>>>(a);
+        else if (a.world <= 4) dp_p2p_kernel<4, SGD, P2P_THREADS><<<grid, P2P_THREADS, 0, stream>>>(a);
+        else dp_p2p_kernel<8, SGD, P2P_THREADS><<<grid, P2P_THREADS, 0, stream>>>(a);
+    }
+}
+
+// CTAs per launch: P2P_CTAS unless TENMO_P2P_CTAS names fewer (every rank must use the same number: a CTA pairs with
+// the CTA of the same index on its peers).
+int p2p_grid() {
+    static int grid = 0;
+    if (!grid) {
+        grid = P2P_CTAS;
+        const char* env = getenv("TENMO_P2P_CTAS");
+        if (env) {
+            const int v = atoi(env);
+            if (v >= 1 && v <= P2P_CTAS) grid = v;
+        }
+    }
+    return grid;
 }
 
 void p2p_fill_args(tenmo_ctx* ctx, P2PArgs& a, int64_t offset, int64_t count) {
@@ -400,8 +372,8 @@ int tenmo_dp_p2p_allreduce_sum_f32(tenmo_ctx* ctx, int64_t offset, int64_t count
     TENMO_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     P2PArgs a;
     p2p_fill_args(ctx, a, offset, count);  // every rank makes the same calls in the same order
-    dp_p2p_allreduce_kernel<<<P2P_CTAS, P2P_THREADS, 0, ctx->stream>>>(a);
-    TENMO_LAUNCH_CHECK(ctx, "dp_p2p_allreduce_kernel");
+    p2p_launch<false>(a, p2p_grid(), ctx->stream, !ctx->p2p_small);
+    TENMO_LAUNCH_CHECK(ctx, "dp_p2p_kernel");
     return TENMO_OK;
 }
 
@@ -425,8 +397,14 @@ int tenmo_dp_p2p_sgd_step_f32(tenmo_ctx* ctx, int64_t grad_offset, int64_t param
     a.p_off = param_offset;
     a.v = v; a.lo = lo_count > 0 ? p_lo : nullptr; a.lo_count = lo_count;
     a.lr = lr; a.momentum = momentum; a.wd = weight_decay; a.grad_scale = grad_scale;
-    dp_p2p_sgd_kernel<<<P2P_CTAS, P2P_THREADS, 0, ctx->stream>>>(a);
-    TENMO_LAUNCH_CHECK(ctx, "dp_p2p_sgd_kernel");
+    p2p_launch<true>(a, p2p_grid(), ctx->stream, !ctx->p2p_small);
+    TENMO_LAUNCH_CHECK(ctx, "dp_p2p_kernel");
+    return TENMO_OK;
+}
+
+int tenmo_dp_p2p_set_coresident(tenmo_ctx* ctx, int on) {
+    TENMO_CHECK_CTX(ctx);
+    ctx->p2p_small = on != 0;
     return TENMO_OK;
 }
 

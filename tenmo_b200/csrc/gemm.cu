@@ -163,6 +163,8 @@ int tenmo_gemm_f32(tenmo_ctx* ctx, int algo, int64_t M, int64_t N, int64_t K, co
     return tenmo_gemm_f32_ex(ctx, algo, M, N, K, A, B, C, &o);
 }
 
+int tenmo_gemm_last_pair(tenmo_ctx* ctx) { return ctx && ctx->last_gemm_pair ? 1 : 0; }
+
 int tenmo_split_lo_f32(tenmo_ctx* ctx, const tenmo_mat* X, int64_t rows, int64_t cols, float* lo_out, int64_t capacity) {
     TENMO_CHECK_CTX(ctx);
     if (!X || !X->ptr || !lo_out) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "split_lo: NULL pointer");

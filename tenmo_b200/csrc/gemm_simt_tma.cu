@@ -342,6 +342,9 @@ cudaError_t st_launch(bool a_k, bool b_k, unsigned grid, cudaStream_t s, const C
     {                                                                                                                  \
         cudaError_t e = cudaFuncSetAttribute(gemm_simt_tma_kernel<AK, BKM, PACKED>,                                   \
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM);                    \
+        if (e == cudaSuccess) /* two CTAs per SM need the large shared-memory split of the L1 */                      \
+            e = cudaFuncSetAttribute(gemm_simt_tma_kernel<AK, BKM, PACKED>, cudaFuncAttributePreferredSharedMemoryCarveout, \
+                                     cudaSharedmemCarveoutMaxShared);                                                  \
         if (e != cudaSuccess) return e;                                                                                \
         gemm_simt_tma_kernel<AK, BKM, PACKED><<<grid, ST_THREADS, ST_SMEM, s>>>(ma, mb, sp);                          \
     }

@@ -2,16 +2,16 @@
 // (the classifier layer of a CNN: (batch, 4096) . (4096, 10)).  Every output is still ONE k-ascending fmaf chain, as in
 // the other strict kernels and in the reference's CPU loops (matmul_cpu.mojo:275-312), so the bits are the same; what
 // changes is what sits between two links of the chain.  The square-tile kernel spends a global load, a shared-memory
-// store and a block barrier per 64 links with a handful of CTAs in flight; here a CTA is four rows (one warp each,
-// lane = column), the next 128-deep slice of A and B is fetched into registers while the current one is multiplied out of
+// store and a block barrier per 64 links with a handful of CTAs in flight; here a CTA is eight rows (one warp each,
+// lane = column), the next 256-deep slice of A and B is fetched into registers while the current one is multiplied out of
 // shared memory, and a link costs one broadcast read, one conflict-free read and the FMA.
 #include "gemm_simt.cuh"
 
 namespace {
 
-constexpr int SK_ROWS = 4;            // rows (= warps) per CTA
+constexpr int SK_ROWS = 8;            // rows (= warps) per CTA
 constexpr int SK_THREADS = SK_ROWS * 32;
-constexpr int SK_KC = 128;            // k-slice staged at a time
+constexpr int SK_KC = 256;            // k-slice staged at a time: its chain of 256 links outlasts the latency of the next fetch
 constexpr int SK_BP = 33;             // pitch of a staged B row: lane n reads column n without conflicts
 
 __device__ __forceinline__ float sk_act(float v, int act) {
@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const TenmoGemm
     const int N = (int)p.N;
     const bool row_ok = m < p.M;
     constexpr int A_PER = SK_KC / 32;                       // A values per lane and slice
-    constexpr int B_PER = SK_KC / SK_ROWS;                  // B values per lane and slice: warp w takes rows w, w + 4, ...
+    constexpr int B_PER = SK_KC / SK_ROWS;                  // B values per lane and slice: warp w takes rows w, w + 8, ...
     float ra[A_PER], rb[B_PER];
     auto fetch = [&](int64_t k0) {
 #pragma unroll

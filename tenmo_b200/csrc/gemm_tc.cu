@@ -51,13 +51,21 @@ constexpr int TILE_COUNTERS = 32;            // ring of global tile counters, on
 constexpr int EP_LD = 32;  // floats per row of an epilogue warp's 32 x 32 staging block; 16-byte chunk q of row r sits at
                            // chunk q ^ (r & 7), which keeps the row-wise writes and the 4-rows-at-a-time reads conflict-free
 
-template <int BN>
+// PAIR: two CTAs on neighbouring SMs (a cluster of two) work on one 256 x BN tile with tcgen05.mma.cta_group::2: each holds
+// its own 128 rows of A and HALF of the B tile, the tensor cores read the other half from the partner's shared memory.
+// A stage is then 64 KB instead of 96 KB at BN = 256, so three stages fit where the single-CTA kernel has two, and every
+// byte of B is fetched from L2 once per pair instead of once per CTA.
+template <int BN, bool PAIR = false>
 struct TcCfg {
     static constexpr int A_TILE = BM * BK * 4;   // bytes of one plane of A per stage
-    static constexpr int B_TILE = BN * BK * 4;
+    static constexpr int B_ROWS = PAIR ? BN / 2 : BN;  // columns of the B tile this CTA stages
+    static constexpr int B_TILE = B_ROWS * BK * 4;
     static constexpr int STAGE = 2 * A_TILE + 2 * B_TILE;
-    static constexpr int STAGES = ((BN == 256) ? 2 : (BN == 128 ? 3 : 4)) * (32 / BK);
-    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/ + EPI_WARPS * 32 * EP_LD * 4 /*epilogue staging*/;
+    static constexpr int STAGES = (PAIR ? 3 : ((BN == 256) ? 2 : (BN == 128 ? 3 : 4))) * (32 / BK);
+    // No alignment slack: the dynamic array is declared 1024-byte aligned and is the CTA's only shared memory.  With BN = 256
+    // this leaves 2 KB of the SM's shared memory free, which is what lets a small CTA of another kernel (the data-parallel
+    // exchange) share the SM with this one.
+    static constexpr int SMEM = STAGES * STAGE + 256 /*barriers*/ + EPI_WARPS * 32 * EP_LD * 4 /*epilogue staging*/;
     static constexpr int TMEM_COLS = 2 * BN;     // two accumulators
 };
 
@@ -109,6 +117,51 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// ---- the same for a CTA pair (cluster of two) ----
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on the barrier at the same shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// tiled bulk copy whose completion is counted on a barrier of the pair's leader CTA (no multicast: the data lands in this
+// CTA's shared memory only)
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -159,14 +212,18 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int tiles_m, int tiles
 }
 
 // A_MN / B_MN: the operand's unit-stride axis is m (resp. n) instead of k.
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool PAIR = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_lo,
                const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_b_lo, const TcParams p) {
-    using Cfg = TcCfg<BN>;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 128B swizzle wants 1024-byte alignment
-    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    using Cfg = TcCfg<BN, PAIR>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = smem_u32(smem_raw);  // 128B swizzle wants 1024-byte alignment
+    uint8_t* smem_gen = smem_raw;
+    if (smem_base & 1023u) {  // cannot happen with the declaration above; checked because a misaligned tile would be garbage
+        if (threadIdx.x == 0) atomicOr(p.status, TENMO_DEV_TIMEOUT);
+        return;
+    }
     const uint32_t bar_base = smem_base + Cfg::STAGES * Cfg::STAGE;
     // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], sched_full[SQ],
     // sched_empty[SQ]; then the segment ring (4 ints per entry), the tmem pointer and the abort flag
@@ -183,24 +240,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // PAIR: p.tiles_m counts 256-row tiles; rank 0 of the cluster (the leader) issues the MMAs for both CTAs, owns the
+    // barriers the loads of both CTAs complete on (full) and the one both epilogues release an accumulator on (tempty)
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = crank == 0u;
     const int64_t num_tiles = (int64_t)p.tiles_m * p.tiles_n * p.total_batch;
     const int num_kb = (int)((p.K + BK - 1) / BK);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI_WARPS); }
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(full_bar(s), PAIR ? 2 : 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), PAIR ? 2 * EPI_WARPS : EPI_WARPS); }
         for (int q = 0; q < SQ; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 1 + EPI_WARPS); }  // MMA thread + the epilogue warps
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr_smem)),
-                     "r"((uint32_t)Cfg::TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {  // the pair allocates the same columns in both tensor memories: one warp of each CTA takes part
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr_smem)),
+                         "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_ptr_smem)),
+                         "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // the partner's barriers are initialised before anything arrives on them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -230,34 +299,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             auto load = [&](int64_t tile, int kb0, int kb1) -> bool {
                 int64_t batch; int tm, tn;
                 tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
-                const int m0 = tm * BM, n0 = tn * BN;
+                // PAIR: this CTA's 128 rows of the 256-row tile and its half of the tile's columns
+                const int m0 = PAIR ? tm * (2 * BM) + (int)crank * BM : tm * BM;
+                const int n0 = tn * BN + (PAIR ? (int)crank * (BN / 2) : 0);
                 const int ba = p.a_batched ? (int)batch : 0, bb = p.b_batched ? (int)batch : 0;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) return false;
                     const uint32_t sa = smem_base + stage * Cfg::STAGE;
                     const uint32_t sal = sa + Cfg::A_TILE, sb = sa + 2 * Cfg::A_TILE, sbl = sb + Cfg::B_TILE;
-                    const uint32_t bar = full_bar(stage);
-                    mbar_expect_tx(bar, (uint32_t)Cfg::STAGE);
+                    // the copies of BOTH CTAs of a pair complete on the leader's barrier: each CTA announces its own bytes
+                    const uint32_t bar = PAIR ? map_to_cta(full_bar(stage), 0u) : full_bar(stage);
+                    if (PAIR) mbar_expect_tx_cluster(bar, (uint32_t)Cfg::STAGE);
+                    else mbar_expect_tx(bar, (uint32_t)Cfg::STAGE);
                     armed |= 1u << stage;
                     const int k0 = kb * BK;
+                    auto ld = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2) {
+                        if (PAIR) tma_load_3d_pair(dst, map, bar, c0, c1, c2);
+                        else tma_load_3d(dst, map, bar, c0, c1, c2);
+                    };
                     if (!A_MN) {
-                        tma_load_3d(sa, &map_a, bar, k0, m0, ba);
-                        tma_load_3d(sal, &map_a_lo, bar, k0, m0, ba);
+                        ld(sa, &map_a, k0, m0, ba);
+                        ld(sal, &map_a_lo, k0, m0, ba);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BM / 32; ++j) {
-                            tma_load_3d(sa + j * (BK * 128), &map_a, bar, m0 + 32 * j, k0, ba);
-                            tma_load_3d(sal + j * (BK * 128), &map_a_lo, bar, m0 + 32 * j, k0, ba);
+                            ld(sa + j * (BK * 128), &map_a, m0 + 32 * j, k0, ba);
+                            ld(sal + j * (BK * 128), &map_a_lo, m0 + 32 * j, k0, ba);
                         }
                     }
                     if (!B_MN) {
-                        tma_load_3d(sb, &map_b, bar, k0, n0, bb);
-                        tma_load_3d(sbl, &map_b_lo, bar, k0, n0, bb);
+                        ld(sb, &map_b, k0, n0, bb);
+                        ld(sbl, &map_b_lo, k0, n0, bb);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 32; ++j) {
-                            tma_load_3d(sb + j * (BK * 128), &map_b, bar, n0 + 32 * j, k0, bb);
-                            tma_load_3d(sbl + j * (BK * 128), &map_b_lo, bar, n0 + 32 * j, k0, bb);
+                        for (int j = 0; j < Cfg::B_ROWS / 32; ++j) {
+                            ld(sb + j * (BK * 128), &map_b, n0 + 32 * j, k0, bb);
+                            ld(sbl + j * (BK * 128), &map_b_lo, n0 + 32 * j, k0, bb);
                         }
                     }
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
@@ -273,8 +350,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             auto draw = [&]() -> int64_t { return unit_base + (int64_t)atomicAdd(p.tile_counter, 1u); };
             const int64_t sk_total = (num_tiles - p.dp_tiles) * (int64_t)num_kb;
             const int64_t sk_q = p.sk_units ? sk_total / p.sk_units : 0, sk_r = p.sk_units ? sk_total % p.sk_units : 0;
-            int64_t unit = unit_base ? (int64_t)blockIdx.x : draw();
-            while (ok) {
+            int64_t unit = PAIR ? 0 : (unit_base ? (int64_t)blockIdx.x : draw());
+            if (PAIR) {
+                // Both CTAs of a pair must walk the same tiles in the same order without talking to each other: the tiles
+                // are dealt round-robin to the pairs (no counter, no stream-K tail).
+                const int64_t pairs = gridDim.x / 2;
+                for (int64_t t = blockIdx.x / 2; ok && t < num_tiles; t += pairs) {
+                    if (!publish((int)t, 0, num_kb, 0)) { ok = false; break; }
+                    if (!load(t, 0, num_kb)) { ok = false; break; }
+                }
+                if (ok && !publish(-1, 0, 0, 0)) ok = false;
+                unit = num_units;  // the loop below has nothing left to do
+            }
+            while (ok && !PAIR) {
                 if (unit >= num_units) { if (!publish(-1, 0, 0, 0)) ok = false; break; }
                 int64_t next = -1;
                 if (unit < p.dp_tiles) {
@@ -307,8 +395,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 unit = next;
             }
-            if (!ok) {
-                // Drain: let every copy already issued land before the CTA gives its shared memory back.
+            if (!ok && (!PAIR || leader)) {
+                // Drain: let every copy already issued land before the CTA gives its shared memory back (the leader of a
+                // pair waits for both CTAs' copies, and the pair leaves together).
                 // A stage's last armed phase: stages < `stage` were armed in the current phase, the rest in the previous.
                 for (int s = 0; s < Cfg::STAGES; ++s) {
                     if (!(armed & (1u << s))) continue;
@@ -327,8 +416,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------- MMA issuer -------------------------------
         if (lane == 0) {
+            // instruction shape: M = 128 (one CTA) or 256 (a pair: 128 rows in each CTA's tensor memory), N = BN
             constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
-                                       ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                                       ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)((PAIR ? 2 * BM : BM) >> 4) << 24);
             // K-major: rows of 128 B, 8-row groups 1024 B apart (SBO), k-step = 32 B inside the swizzle row.
             // MN-major: a tile is [32-wide mn chunk][k row of 128 B]; chunks are 4096 B apart (LBO), the
             // swizzle pattern repeats every 4 k rows = 512 B (SBO), one k-step of 8 rows = 1024 B.
@@ -351,6 +442,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 mbar_arrive(sempty_bar(sq));
                 if (++sq == SQ) { sq = 0; sphase ^= 1u; }
                 if (tile < 0) break;
+                if (PAIR && !leader) continue;  // the partner's warp only keeps the segment ring moving
                 if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -365,15 +457,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const uint64_t dal = make_desc(sal + k * A_KSTEP, A_LBO, A_SBO, A_LT);
                         const uint64_t db = make_desc(sb + k * B_KSTEP, B_LBO, B_SBO, B_LT);
                         const uint64_t dbl = make_desc(sbl + k * B_KSTEP, B_LBO, B_SBO, B_LT);
-                        umma_tf32(d_tmem, dal, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);  // a_lo * b_hi
-                        umma_tf32(d_tmem, da, dbl, idesc, 1u);                             // a_hi * b_lo
-                        umma_tf32(d_tmem, da, db, idesc, 1u);                              // a_hi * b_hi
+                        if (PAIR) {
+                            umma_tf32_pair(d_tmem, dal, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);  // a_lo * b_hi
+                            umma_tf32_pair(d_tmem, da, dbl, idesc, 1u);                             // a_hi * b_lo
+                            umma_tf32_pair(d_tmem, da, db, idesc, 1u);                              // a_hi * b_hi
+                        } else {
+                            umma_tf32(d_tmem, dal, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);  // a_lo * b_hi
+                            umma_tf32(d_tmem, da, dbl, idesc, 1u);                             // a_hi * b_lo
+                            umma_tf32(d_tmem, da, db, idesc, 1u);                              // a_hi * b_hi
+                        }
                     }
-                    umma_commit(empty_bar(stage));  // stage is free once these MMAs have read it
+                    // stage is free once these MMAs have read it (a pair: in both CTAs)
+                    if (PAIR) umma_commit_pair(empty_bar(stage)); else umma_commit(empty_bar(stage));
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit(tfull_bar(acc));  // accumulator complete
+                if (PAIR) umma_commit_pair(tfull_bar(acc)); else umma_commit(tfull_bar(acc));  // accumulator complete
                 acc_phase[acc] ^= 1u;
                 acc ^= 1;
             }
@@ -415,6 +514,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int slot = info >> 8;
             int64_t batch; int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
+            if (PAIR) tm = 2 * tm + (int)crank;  // this CTA's 128 rows of the pair's 256-row tile
             if (!warp_wait(tfull_bar(acc), acc_phase[acc])) { ok = false; break; }
             tcgen05_fence_after();
             // A thread's tcgen05.ld delivers 32 consecutive columns of ONE row, so storing straight from those
@@ -560,7 +660,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(tempty_bar(acc));
+                if (PAIR) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0u));  // both epilogues release it on the leader's barrier
+                else mbar_arrive(tempty_bar(acc));
                 if (partial) {
                     __threadfence();  // the warp's stores (ordered before this by the __syncwarp) are visible before the count
                     atomicAdd(p.sk_flags + slot, 1u);
@@ -573,7 +674,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     tcgen05_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (PAIR) cluster_sync_all();  // neither CTA gives back shared or tensor memory the other may still be addressing
+    if (threadIdx.x == 0 && PAIR) {
+        if (*abort_flag) atomicOr(p.status, TENMO_DEV_TIMEOUT);
+    }
+    if (threadIdx.x == 0 && !PAIR) {
         if (*abort_flag) atomicOr(p.status, TENMO_DEV_TIMEOUT);
         // every CTA has finished drawing tiles (and reading flags) once it is here; the last one re-arms the counter pair
         // and the fix-up flags, so that no memset sits in front of the next launch and a captured graph can be replayed
@@ -588,8 +693,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
-                     : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
     }
 }
 
@@ -726,6 +835,35 @@ cudaError_t launch_tc(bool a_mn, bool b_mn, int grid, cudaStream_t s, const CUte
     return cudaGetLastError();
 }
 
+// The CTA-pair form (BN = 256 only): `grid` CTAs in clusters of two.
+cudaError_t launch_tc_pair(bool a_mn, bool b_mn, int grid, cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mal,
+                           const CUtensorMap& mb, const CUtensorMap& mbl, const TcParams& tp) {
+    const int smem = TcCfg<256, true>::SMEM;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define TC_LAUNCH_PAIR(AM, BMJ)                                                                                        \
+    {                                                                                                                  \
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<256, AM, BMJ, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+        if (e != cudaSuccess) return e;                                                                                \
+        e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<256, AM, BMJ, true>, ma, mal, mb, mbl, tp);                       \
+        if (e != cudaSuccess) return e;                                                                                \
+    }
+    if (a_mn) { if (b_mn) TC_LAUNCH_PAIR(true, true) else TC_LAUNCH_PAIR(true, false) }
+    else { if (b_mn) TC_LAUNCH_PAIR(false, true) else TC_LAUNCH_PAIR(false, false) }
+#undef TC_LAUNCH_PAIR
+    return cudaGetLastError();
+}
+
 }  // namespace
 
 int tenmo_tma_init(tenmo_ctx* ctx) {
@@ -822,11 +960,22 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     // walking k in step; measured on 4096-wide layers, cutting the last 1.x waves pays up to x = .6 (+6 .. +14 %), above
     // that only the last, partial wave should be cut (1.73 waves as pieces: -6 %; its last .73: +6 %).  Pieces under 48
     // k-blocks do not repay the fix-up.
-    const int64_t tiles = tiles_for(bn);
+    int64_t tiles = tiles_for(bn);
     if (tiles > 0x7fffffffLL) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_tc: %lld tiles is out of range", (long long)tiles);
+    // CTA pairs (256 x 256 tiles on two SMs, three 64 KB stages, B fetched once per pair): when there are enough such tiles
+    // to give every pair at least two (the pairs walk their tiles in a fixed round-robin: no dynamic scheduler, no
+    // stream-K tail, so a short last wave is not smoothed out).  TENMO_TC_PAIR=0 / 1 turns it off / on regardless.
+    const int pairs = ctas / 2;
+    const int64_t tiles2 = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256) * p.total_batch;
+    bool use_pair = bn == 256 && pairs >= 1 && tiles2 >= 2 * (int64_t)pairs;
+    {
+        const char* env_pair = getenv("TENMO_TC_PAIR");
+        if (env_pair && bn == 256 && pairs >= 1) use_pair = atoi(env_pair) != 0;
+    }
+    if (use_pair) tiles = tiles2;
     int sk_units = 0;
     int64_t dp_tiles = tiles;
-    {
+    if (!use_pair) {
         const int64_t num_kb = (p.K + BK - 1) / BK;
         const int64_t waves = (tiles + ctas - 1) / ctas;
         const char* env_sk = getenv("TENMO_TC_STREAMK");
@@ -870,7 +1019,7 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
 
     CUtensorMap ma, mal, mb, mbl;
     const int a_box = a.mn_major ? BK : BM;
-    const int b_box = b.mn_major ? BK : bn;
+    const int b_box = b.mn_major ? BK : (use_pair ? bn / 2 : bn);  // a CTA of a pair stages half of the tile's columns
     if ((st = encode_map(ctx, &ma, p.A, a, false, a_box)) != TENMO_OK) return st;
     if ((st = encode_map(ctx, &mal, a_lo, a, true, a_box)) != TENMO_OK) return st;
     if ((st = encode_map(ctx, &mb, p.B, b, false, b_box)) != TENMO_OK) return st;
@@ -880,7 +1029,7 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     tp.C = p.C; tp.aux = p.aux; tp.bias = p.bias;
     tp.mul_mask = p.mul_mask; tp.c_lo = p.c_lo; tp.ld_clo = p.ld_clo; tp.bias_m = p.bias_m;
     tp.M = p.M; tp.N = p.N; tp.K = p.K; tp.total_batch = p.total_batch;
-    tp.tiles_m = (int)((p.M + BM - 1) / BM);
+    tp.tiles_m = use_pair ? (int)((p.M + 2 * BM - 1) / (2 * BM)) : (int)((p.M + BM - 1) / BM);
     tp.tiles_n = (int)((p.N + bn - 1) / bn);
     tp.a_batched = a.batched; tp.b_batched = b.batched;
     tp.beta = p.beta; tp.act = p.act;
@@ -893,18 +1042,20 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     tp.dp_tiles = dp_tiles;
     tp.sk_partials = sk_units ? reinterpret_cast<float*>(static_cast<char*>(ws) + a_lo_bytes + b_lo_bytes) : nullptr;
     tp.sk_flags = reinterpret_cast<unsigned int*>(ctx->dev_status) + TENMO_SK_FLAG_WORD0;
-    const int grid = sk_units ? ctas : (int)(tiles < ctas ? tiles : ctas);
+    const int grid = use_pair ? 2 * (int)(tiles < pairs ? tiles : pairs) : (sk_units ? ctas : (int)(tiles < ctas ? tiles : ctas));
     // a tile counter pair for this launch (dev_status words 64..127: [next tile, CTAs finished] x 32).  Both words
     // are zero between launches: the last CTA to leave clears them, so no memset sits in front of the kernel.
     tp.tile_counter = reinterpret_cast<unsigned int*>(ctx->dev_status) + 64 + 2 * (ctx->tile_counter_next++ % TILE_COUNTERS);
     tenmo_prof_before(ctx);
-    cudaError_t e = (bn == 256)   ? launch_tc<256>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
+    cudaError_t e = use_pair      ? launch_tc_pair(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
+                    : (bn == 256) ? launch_tc<256>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
                     : (bn == 128) ? launch_tc<128>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp)
                                   : launch_tc<64>(a.mn_major, b.mn_major, grid, ctx->stream, ma, mal, mb, mbl, tp);
     tenmo_prof_after(ctx);
     ctx->launches++;
     ctx->last_gemm_kernel = "gemm_tc_kernel";
     ctx->last_gemm_sk_units = sk_units;
+    ctx->last_gemm_pair = use_pair;
     if (e != cudaSuccess) return tenmo_set_error(ctx, TENMO_ERR_CUDA, "launch of gemm_tc_kernel failed: %s", cudaGetErrorString(e));
     return TENMO_OK;
 }

@@ -25,13 +25,13 @@ EXPORTS = [
     "tenmo_cuda_init", "tenmo_cuda_destroy", "tenmo_cuda_last_error", "tenmo_cuda_version", "tenmo_cuda_set_stream",
     "tenmo_cuda_synchronize", "tenmo_cuda_device_info", "tenmo_cuda_check_device_status", "tenmo_cuda_launch_count",
     "tenmo_cuda_profile_begin", "tenmo_cuda_profile_end", "tenmo_cuda_reserve_sms",
-    "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_gemv_f32", "tenmo_vecmat_f32", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_gemm_last_kernel", "tenmo_gemm_last_stream_k", "tenmo_cuda_wait_probe", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
+    "tenmo_gemm_f32", "tenmo_gemm_f32_ex", "tenmo_gemv_f32", "tenmo_vecmat_f32", "tenmo_split_lo_f32", "tenmo_gemm_last_algo", "tenmo_gemm_last_kernel", "tenmo_gemm_last_stream_k", "tenmo_gemm_last_pair", "tenmo_cuda_wait_probe", "tenmo_add_bias_f32", "tenmo_add_inplace_f32", "tenmo_fill_f32",
     "tenmo_relu_fwd_f32", "tenmo_relu_bwd_f32", "tenmo_sigmoid_fwd_f32", "tenmo_sigmoid_bwd_f32", "tenmo_colsum_f32",
     "tenmo_conv_out_size", "tenmo_conv2d_fwd_f32", "tenmo_conv2d_bwd_input_f32", "tenmo_conv2d_bwd_weight_f32", "tenmo_im2col_f32", "tenmo_col2im_f32", "tenmo_channel_sum_f32", "tenmo_maxpool2d_fwd_f32",
     "tenmo_maxpool2d_bwd_f32",
     "tenmo_colsum_f32_static", "tenmo_softmax_fwd_f32", "tenmo_softmax_bwd_f32", "tenmo_ce_fwd_f32", "tenmo_ce_bwd_f32", "tenmo_ce_fwd_bwd_f32", "tenmo_sgd_step_f32", "tenmo_sgd_step_lo_f32", "tenmo_accuracy_f32", "tenmo_dp_get_unique_id",
     "tenmo_dp_init", "tenmo_dp_allreduce_sum_f32", "tenmo_dp_finalize",
-    "tenmo_dp_p2p_alloc", "tenmo_dp_p2p_connect", "tenmo_dp_p2p_allreduce_sum_f32", "tenmo_dp_p2p_sgd_step_f32", "tenmo_dp_p2p_close",
+    "tenmo_dp_p2p_alloc", "tenmo_dp_p2p_connect", "tenmo_dp_p2p_allreduce_sum_f32", "tenmo_dp_p2p_sgd_step_f32", "tenmo_dp_p2p_set_coresident", "tenmo_dp_p2p_close",
 ]
 
 
@@ -111,6 +111,7 @@ def _bind(lib):
         "tenmo_gemm_last_algo": (I, [P]),
         "tenmo_gemm_last_kernel": (C.c_char_p, [P]),
         "tenmo_gemm_last_stream_k": (I, [P]),
+        "tenmo_gemm_last_pair": (I, [P]),
         "tenmo_cuda_wait_probe": (I, [P, C.c_int]),
         "tenmo_add_bias_f32": (I, [P, P, P, P, I64, I64]),
         "tenmo_add_inplace_f32": (I, [P, P, P, I64]),
@@ -146,6 +147,7 @@ def _bind(lib):
         "tenmo_dp_p2p_connect": (I, [P, I, I, P, C.c_size_t]),
         "tenmo_dp_p2p_allreduce_sum_f32": (I, [P, I64, I64]),
         "tenmo_dp_p2p_sgd_step_f32": (I, [P, I64, I64, I64, P, P, I64, F, F, F, F]),
+        "tenmo_dp_p2p_set_coresident": (I, [P, I]),
         "tenmo_dp_p2p_close": (I, [P]),
     }
     for name, (res, args) in sig.items():
@@ -272,6 +274,10 @@ class TenmoCuda:
     def gemm_last_stream_k(self) -> int:
         """Pieces of the stream-K tail of the last tensor-core GEMM launch (0: every tile computed whole)."""
         return int(self.require()._lib.tenmo_gemm_last_stream_k(self._ctx))
+
+    def gemm_last_pair(self) -> bool:
+        """True when the last tensor-core GEMM ran as CTA pairs (tcgen05 cta_group::2)."""
+        return bool(self.require()._lib.tenmo_gemm_last_pair(self._ctx))
 
     def add_bias(self, x, bias, out, M, N):
         self._call("tenmo_add_bias_f32", x, bias, out, M, N)
@@ -415,6 +421,10 @@ class TenmoCuda:
         """Exchange + SGD with the optimiser sharded over the ranks (gradients and parameters both live in the bucket)."""
         self._call("tenmo_dp_p2p_sgd_step_f32", grad_offset, param_offset, count, v or None, p_lo or None, lo_count, lr,
                    momentum, weight_decay, grad_scale)
+
+    def dp_p2p_set_coresident(self, on: bool):
+        """Small exchange CTAs that fit beside the persistent GEMM CTA (for an overlapped exchange) instead of large ones."""
+        self._call("tenmo_dp_p2p_set_coresident", 1 if on else 0)
 
     def dp_p2p_close(self):
         self._call("tenmo_dp_p2p_close")

@@ -107,12 +107,15 @@ class BatchFeed:
 class MLPTrainer(BatchFeed):
     def __init__(self, weights, biases, batch: int, lr: float = 0.01, momentum: float = 0.9, weight_decay: float = 0.0,
                  algo: str = "auto", handle: TenmoCuda | None = None, rank: int = 0, world: int = 1,
-                 unique_id: bytes | None = None, device: int | None = None, overlap: bool = True,
+                 unique_id: bytes | None = None, device: int | None = None, overlap: bool | None = None,
                  reserve_sms: int = 0, exchange: str = "nccl", all_gather_bytes=None):
         """exchange: "nccl" (tenmo_dp_allreduce_sum_f32, then SGD on every rank; needs unique_id), "p2p" (the library's
         own kernel over NVLink peer memory with the optimiser sharded over the ranks, tenmo_dp_p2p_sgd_step_f32) or
         "p2p_allreduce" (the peer-memory all-reduce, then SGD on every rank).  The p2p forms need
-        all_gather_bytes(data) -> [bytes per rank] to share the IPC handles of the bucket."""
+        all_gather_bytes(data) -> [bytes per rank] to share the IPC handles of the bucket.
+        overlap: run each layer's exchange on a side stream beside the remaining backward GEMMs.  None picks what measured
+        best on 2 to 8 B200s: on for NCCL up to 4 ranks, off otherwise -- at 1024 rows per rank every GEMM is a single wave
+        of CTAs, and anything that shares the SMs or the memory system with it costs more than the exchange it hides."""
         self.dev = torch.cuda.current_device() if device is None else device
         self.h = handle or TenmoCuda(self.dev).require()
         self.algo = {"auto": _lib.ALGO_AUTO, "simt": _lib.ALGO_SIMT_FP32, "3xtf32": _lib.ALGO_TC_3XTF32}[algo]
@@ -176,13 +179,17 @@ class MLPTrainer(BatchFeed):
         # [start, count) of each layer's weight + bias inside the flat buffers
         self.layer_span = [(offs[2 * l], offs[2 * l + 1] + (sizes[2 * l + 1] + 3) // 4 * 4 - offs[2 * l])
                            for l in range(self.L)]
-        self.overlap = overlap and world > 1
+        if overlap is None:
+            overlap = self.exchange == "nccl" and world <= 4
+        self.overlap = bool(overlap) and world > 1
         self._side = torch.cuda.Stream(self.dev) if self.overlap else None
         self._upd_ev = [None] * self.L   # per layer: recorded on the side stream after the layer's update
         self._join_each_step = False     # a captured step must end with the side stream joined
         self.reserve_sms = int(reserve_sms) if self.overlap else 0
         if self.exchange == "nccl":
             self.h.dp_init(rank, world, unique_id)
+        elif self.exchange in ("p2p", "p2p_allreduce"):
+            self.h.dp_p2p_set_coresident(self.overlap)
         if self.fused_lo:
             self.h.set_stream(torch.cuda.current_stream(self.dev).cuda_stream)
             for l in range(self.L):

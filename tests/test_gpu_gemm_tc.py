@@ -218,6 +218,7 @@ def test_tc_stream_k_tail(g, oracle, mkn, layout, monkeypatch):
     """The stream-K tail (pieces of the k-range of the last tiles, partial accumulators added by the piece that ends a
     tile): same bar as whole tiles, epilogue options honoured by the completing piece, repeatable bit for bit, and the
     flags are back to zero after every launch (three launches in a row with different inputs)."""
+    monkeypatch.setenv("TENMO_TC_PAIR", "0")   # the single-CTA kernel: the pair form has no stream-K tail
     batch = 1
     if len(mkn) == 4:
         batch, M, K, N = mkn
@@ -312,4 +313,88 @@ def test_tc_stream_k_replays_in_a_graph(g):
         ref = A.double() @ B.double()
         scale = A.double().abs() @ B.double().abs()
         assert float(((C.double() - ref).abs() / scale).max()) <= TOL
+    h.check_device_status()
+
+
+# ---- the CTA-pair form (tcgen05.mma.cta_group::2: two SMs share a 256 x 256 tile) ------------------------------------
+@pytest.fixture
+def force_pair(monkeypatch):
+    monkeypatch.setenv("TENMO_TC_PAIR", "1")   # read by the library at every launch
+
+
+PAIR_SHAPES = [(256, 64, 256), (512, 96, 512), (1000, 260, 388), (129, 36, 260), (640, 2052, 516), (2048, 512, 1024),
+               (300, 4096, 257 * 4)]  # whole tiles, ragged rows / columns, a row tile whose second CTA is empty, long k
+
+
+@pytest.mark.parametrize("mkn", PAIR_SHAPES, ids=str)
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn", "tt"])
+def test_tc_pair_matches_oracle(g, oracle, force_pair, mkn, layout):
+    M, K, N = mkn
+    if layout in ("tn", "tt") and M % 4:
+        pytest.skip("transposed A needs a 16-byte aligned leading stride")
+    rng = np.random.default_rng(M * 13 + K * 5 + N)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32)
+    Av, Bv = layouts(oracle, A, B, layout)
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    h = g.handle()
+    assert h.gemm_last_algo() == TC and h.gemm_last_pair() and h.gemm_last_stream_k() == 0
+    h.check_device_status()
+    e32 = rel_err(C, oracle.matmul(Av, Bv, threads=4).astype(np.float64), np.abs(A), np.abs(B))
+    e64 = rel_err(C, A.astype(np.float64) @ B.astype(np.float64), np.abs(A), np.abs(B))
+    assert e32 <= TOL and e64 <= 4e-6, (e32, e64)
+    # the pair form and the single-CTA form add the same products in the same order inside a tile: identical bits
+    import os
+
+    os.environ["TENMO_TC_PAIR"] = "0"
+    C1, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert not h.gemm_last_pair()
+    os.environ["TENMO_TC_STREAMK"] = "0"
+    C1, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    del os.environ["TENMO_TC_STREAMK"]
+    assert np.array_equal(C, C1)
+
+
+def test_tc_pair_epilogue_batches_and_planes(g, oracle, force_pair):
+    """Bias, ReLU with its mask, the accumulate, a row bias, a multiplier and the result's lo plane through the pair
+    kernel; a broadcast-batched product; the same call twice gives the same bits."""
+    import torch as T
+
+    from tenmo_b200 import make_mat
+
+    h = g.handle()
+    M, K, N = 520, 200, 772
+    rng = np.random.default_rng(19)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32) * 0.1
+    bias = rng.standard_normal(N).astype(np.float32)
+    Av, Bv = oracle.View.of(A), oracle.View.of(B)
+    z = oracle.add_bias(oracle.matmul(A, B), bias)
+    C, aux, _ = g.gpu_matmul(Av, Bv, algo=TC, bias=bias, act=1, want_aux=True)
+    assert h.gemm_last_pair()
+    out, mask = oracle.relu_fwd(z)
+    near_zero = np.abs(z) < 1e-4
+    assert np.allclose(C, out, rtol=1e-5, atol=1e-4) and np.array_equal(aux[~near_zero], mask[~near_zero])
+    init = rng.standard_normal((M, N), np.float32)
+    C2, _, _ = g.gpu_matmul(Av, Bv, algo=TC, beta=1.0, c_init=init)
+    assert np.allclose(C2, init + oracle.matmul(A, B), rtol=1e-5, atol=1e-4)
+    # extended options: multiplier (fused ReLU backward) and the lo plane of the stored result
+    Ad, Bd, mul = g.dev(A), g.dev(B), g.dev((rng.random((M, N)) > 0.5).astype(np.float32))
+    Cd, clo = g.empty(M, N), g.empty(M * N)
+    h.gemm_ex(M, N, K, make_mat(Ad.data_ptr(), (M, K), (K, 1)), make_mat(Bd.data_ptr(), (K, N), (N, 1)), Cd.data_ptr(), algo=TC,
+              mul_mask=mul.data_ptr(), c_lo=clo.data_ptr())
+    assert h.gemm_last_pair()
+    want = oracle.matmul(A, B) * g.host(mul)
+    got = g.host(Cd)
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-4)
+    hi = (got.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    assert np.allclose(g.host(clo).reshape(M, N), got - hi, rtol=0, atol=np.abs(got).max() * 2.0 ** -21)
+    Cd2 = g.empty(M, N)
+    h.gemm_ex(M, N, K, make_mat(Ad.data_ptr(), (M, K), (K, 1)), make_mat(Bd.data_ptr(), (K, N), (N, 1)), Cd2.data_ptr(), algo=TC,
+              mul_mask=mul.data_ptr())
+    assert T.equal(Cd, Cd2)
+    # (B, M, K) @ (1, K, N)
+    Ab = rng.standard_normal((5, 300, 64), np.float32)
+    Bb = rng.standard_normal((1, 64, 512), np.float32)
+    Cb, _, _ = g.gpu_matmul(oracle.View.of(Ab), oracle.View.of(Bb), algo=TC)
+    assert h.gemm_last_pair()
+    assert np.max(np.abs(Cb - Ab.astype(np.float64) @ Bb.astype(np.float64))) <= TOL * 64 * 4
     h.check_device_status()
