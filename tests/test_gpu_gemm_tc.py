@@ -320,6 +320,7 @@ def test_tc_stream_k_replays_in_a_graph(g):
 @pytest.fixture
 def force_pair(monkeypatch):
     monkeypatch.setenv("TENMO_TC_PAIR", "1")   # read by the library at every launch
+    monkeypatch.setenv("TENMO_TC_BN", "256")   # the pair form exists for 256-wide tiles; small products would pick narrower ones
 
 
 PAIR_SHAPES = [(256, 64, 256), (512, 96, 512), (1000, 260, 388), (129, 36, 260), (640, 2052, 516), (2048, 512, 1024),
