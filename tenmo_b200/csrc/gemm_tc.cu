@@ -347,22 +347,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // CTAs are resident.  For that the first unit must come from the counter too unless it is a whole tile.
             const int64_t num_units = p.dp_tiles + p.sk_units;
             const int64_t unit_base = (p.dp_tiles >= (int64_t)gridDim.x) ? (int64_t)gridDim.x : 0;
-            auto draw = [&]() -> int64_t { return unit_base + (int64_t)atomicAdd(p.tile_counter, 1u); };
+            // A pair cannot draw from the counter (its two CTAs must see the same sequence without talking to each other):
+            // its units are fixed by its index -- whole tiles round-robin over the pairs, then the piece of its own number.
+            int64_t s_next = blockIdx.x / 2;
+            bool s_piece_taken = false;
+            auto draw = [&]() -> int64_t {
+                if (!PAIR) return unit_base + (int64_t)atomicAdd(p.tile_counter, 1u);
+                if (s_next < p.dp_tiles) { const int64_t u = s_next; s_next += gridDim.x / 2; return u; }
+                if (!s_piece_taken) {
+                    s_piece_taken = true;
+                    const int64_t j = blockIdx.x / 2;
+                    if (j < p.sk_units) return p.dp_tiles + j;
+                }
+                return p.dp_tiles + p.sk_units;  // nothing left
+            };
             const int64_t sk_total = (num_tiles - p.dp_tiles) * (int64_t)num_kb;
             const int64_t sk_q = p.sk_units ? sk_total / p.sk_units : 0, sk_r = p.sk_units ? sk_total % p.sk_units : 0;
-            int64_t unit = PAIR ? 0 : (unit_base ? (int64_t)blockIdx.x : draw());
-            if (PAIR) {
-                // Both CTAs of a pair must walk the same tiles in the same order without talking to each other: the tiles
-                // are dealt round-robin to the pairs (no counter, no stream-K tail).
-                const int64_t pairs = gridDim.x / 2;
-                for (int64_t t = blockIdx.x / 2; ok && t < num_tiles; t += pairs) {
-                    if (!publish((int)t, 0, num_kb, 0)) { ok = false; break; }
-                    if (!load(t, 0, num_kb)) { ok = false; break; }
-                }
-                if (ok && !publish(-1, 0, 0, 0)) ok = false;
-                unit = num_units;  // the loop below has nothing left to do
-            }
-            while (ok && !PAIR) {
+            int64_t unit = PAIR ? draw() : (unit_base ? (int64_t)blockIdx.x : draw());
+            while (ok) {
                 if (unit >= num_units) { if (!publish(-1, 0, 0, 0)) ok = false; break; }
                 int64_t next = -1;
                 if (unit < p.dp_tiles) {
@@ -535,13 +537,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // memory: float4 number (8 c + q) * 128 + row, so that a warp's store covers 512 contiguous bytes; the warp of
             // the completing CTA that owns the same rows and columns reads it back the same way.  A slot's flag counts the
             // epilogue warps that have stored their part.
-            float4* const part = reinterpret_cast<float4*>(p.sk_partials + (size_t)slot * (BM * BN)) + quarter * 32 + lane;
+            // a pair parks two halves per piece: slot 2 j + rank
+            constexpr int SLOT_MUL = PAIR ? 2 : 1;
+            const int slot_add = PAIR ? (int)crank : 0;
+            float4* const part = reinterpret_cast<float4*>(p.sk_partials + (size_t)(slot * SLOT_MUL + slot_add) * (BM * BN)) + quarter * 32 + lane;
             if (npred) {
                 int got = 1;
                 if (lane == 0) {
                     const uint64_t t0 = globaltimer_ns();
                     for (int s = 0; s < npred && got; ++s) {
-                        const unsigned int* f = p.sk_flags + slot + s;
+                        const unsigned int* f = p.sk_flags + (slot + s) * SLOT_MUL + slot_add;
                         for (uint32_t it = 0;; ++it) {
                             unsigned int v;
                             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
@@ -571,7 +576,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     continue;
                 }
                 for (int s = 0; s < npred; ++s) {  // ascending k: own + partial of the first piece + the next ...
-                    const float4* src = part + (size_t)s * (BM * BN / 4) + (c * 8) * 128;
+                    const float4* src = part + (size_t)s * SLOT_MUL * (BM * BN / 4) + (c * 8) * 128;
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
                         const float4 x = __ldcg(src + q * 128);
@@ -664,7 +669,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 else mbar_arrive(tempty_bar(acc));
                 if (partial) {
                     __threadfence();  // the warp's stores (ordered before this by the __syncwarp) are visible before the count
-                    atomicAdd(p.sk_flags + slot, 1u);
+                    atomicAdd(p.sk_flags + slot * SLOT_MUL + slot_add, 1u);
                 }
             }
             acc_phase[acc] ^= 1u;
@@ -675,17 +680,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tcgen05_fence_before();
     __syncthreads();
     if (PAIR) cluster_sync_all();  // neither CTA gives back shared or tensor memory the other may still be addressing
-    if (threadIdx.x == 0 && PAIR) {
-        if (*abort_flag) atomicOr(p.status, TENMO_DEV_TIMEOUT);
-    }
-    if (threadIdx.x == 0 && !PAIR) {
+    if (threadIdx.x == 0) {
         if (*abort_flag) atomicOr(p.status, TENMO_DEV_TIMEOUT);
         // every CTA has finished drawing tiles (and reading flags) once it is here; the last one re-arms the counter pair
         // and the fix-up flags, so that no memset sits in front of the next launch and a captured graph can be replayed
         __threadfence();
         if (atomicAdd(p.tile_counter + 1, 1u) == gridDim.x - 1) {
             __threadfence();
-            for (int u = 0; u < p.sk_units; ++u) p.sk_flags[u] = 0;
+            for (int u = 0; u < p.sk_units * (PAIR ? 2 : 1); ++u) p.sk_flags[u] = 0;
             p.tile_counter[0] = 0;
             p.tile_counter[1] = 0;
             __threadfence();
@@ -962,34 +964,40 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     // k-blocks do not repay the fix-up.
     int64_t tiles = tiles_for(bn);
     if (tiles > 0x7fffffffLL) return tenmo_set_error(ctx, TENMO_ERR_INVALID, "gemm_tc: %lld tiles is out of range", (long long)tiles);
-    // CTA pairs (256 x 256 tiles on two SMs, three 64 KB stages, B fetched once per pair): when there are enough such tiles
-    // to give every pair at least two (the pairs walk their tiles in a fixed round-robin: no dynamic scheduler, no
-    // stream-K tail, so a short last wave is not smoothed out).  TENMO_TC_PAIR=0 / 1 turns it off / on regardless.
+    // CTA pairs (256 x 256 tiles on two SMs, three 64 KB stages, B fetched once per pair): whenever the 256-wide tile was
+    // chosen and there is at least one such tile for every other pair.  The pairs take whole tiles in a fixed round-robin
+    // (their two CTAs must agree on the sequence without talking) and, like the single-CTA form, cut the k-range of the
+    // last tiles into one piece per pair when the last round would be short.  TENMO_TC_PAIR=0 / 1 forces it off / on.
     const int pairs = ctas / 2;
     const int64_t tiles2 = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256) * p.total_batch;
-    bool use_pair = bn == 256 && pairs >= 1 && tiles2 >= 2 * (int64_t)pairs;
+    bool use_pair = bn == 256 && pairs >= 1 && tiles2 * 2 >= (int64_t)pairs;
     {
         const char* env_pair = getenv("TENMO_TC_PAIR");
         if (env_pair && bn == 256 && pairs >= 1) use_pair = atoi(env_pair) != 0;
     }
     if (use_pair) tiles = tiles2;
+    const int workers = use_pair ? pairs : ctas;   // units that work on tiles side by side
     int sk_units = 0;
     int64_t dp_tiles = tiles;
-    if (!use_pair) {
+    {
         const int64_t num_kb = (p.K + BK - 1) / BK;
-        const int64_t waves = (tiles + ctas - 1) / ctas;
+        const int64_t waves = (tiles + workers - 1) / workers;
         const char* env_sk = getenv("TENMO_TC_STREAMK");
-        const bool allowed = !(env_sk && atoi(env_sk) == 0) && p.ws_skip == 0 && ctas <= TENMO_SK_MAX_UNITS;
-        if (allowed && tiles % ctas != 0 && (double)tiles < 0.95 * (double)(waves * ctas)) {
-            const int64_t full = tiles / ctas;
+        bool allowed = !(env_sk && atoi(env_sk) == 0) && p.ws_skip == 0 && workers * (use_pair ? 2 : 1) <= TENMO_SK_MAX_UNITS;
+        // Pairs park and re-read two 128 KB halves per piece, so their tail pays in fewer cases (measured on 4096-wide
+        // layers): not from two full rounds up (4096^3: 260 TFLOP/s in fixed rounds, 246 with the tail), and not when a
+        // single round is already four fifths full.
+        if (use_pair && (tiles >= 2 * (int64_t)workers || (tiles < workers && tiles * 5 >= (int64_t)workers * 4))) allowed = false;
+        if (allowed && tiles % workers != 0 && (double)tiles < 0.95 * (double)(waves * workers)) {
+            const int64_t full = tiles / workers;
             int64_t dp = 0;
-            if (full >= 1) dp = ((tiles - (full - 1) * ctas) * 10 <= (int64_t)ctas * 16) ? (full - 1) * ctas : full * ctas;
-            const int64_t q = (tiles - dp) * num_kb / ctas;
+            if (full >= 1) dp = ((tiles - (full - 1) * workers) * 10 <= (int64_t)workers * 16) ? (full - 1) * workers : full * workers;
+            const int64_t q = (tiles - dp) * num_kb / workers;
             // and at most 8 partials to add into one tile
-            if (q >= 48 && q * 8 >= num_kb) { sk_units = ctas; dp_tiles = dp; }
+            if (q >= 48 && q * 8 >= num_kb) { sk_units = workers; dp_tiles = dp; }
         }
     }
-    const size_t sk_bytes = (size_t)sk_units * BM * bn * 4;
+    const size_t sk_bytes = (size_t)sk_units * (use_pair ? 2 : 1) * BM * bn * 4;
 
     // lo planes: taken from the caller when supplied (same storage geometry: outer x inner rounded up to 4,
     // batches back to back), else split here into the workspace [A_lo | B_lo]
@@ -1042,7 +1050,8 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     tp.dp_tiles = dp_tiles;
     tp.sk_partials = sk_units ? reinterpret_cast<float*>(static_cast<char*>(ws) + a_lo_bytes + b_lo_bytes) : nullptr;
     tp.sk_flags = reinterpret_cast<unsigned int*>(ctx->dev_status) + TENMO_SK_FLAG_WORD0;
-    const int grid = use_pair ? 2 * (int)(tiles < pairs ? tiles : pairs) : (sk_units ? ctas : (int)(tiles < ctas ? tiles : ctas));
+    const int grid = use_pair ? 2 * (sk_units ? pairs : (int)(tiles < pairs ? tiles : pairs))
+                              : (sk_units ? ctas : (int)(tiles < ctas ? tiles : ctas));
     // a tile counter pair for this launch (dev_status words 64..127: [next tile, CTAs finished] x 32).  Both words
     // are zero between launches: the last CTA to leave clears them, so no memset sits in front of the kernel.
     tp.tile_counter = reinterpret_cast<unsigned int*>(ctx->dev_status) + 64 + 2 * (ctx->tile_counter_next++ % TILE_COUNTERS);

@@ -338,7 +338,7 @@ def test_tc_pair_matches_oracle(g, oracle, force_pair, mkn, layout):
     Av, Bv = layouts(oracle, A, B, layout)
     C, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
     h = g.handle()
-    assert h.gemm_last_algo() == TC and h.gemm_last_pair() and h.gemm_last_stream_k() == 0
+    assert h.gemm_last_algo() == TC and h.gemm_last_pair() and h.gemm_last_stream_k() == 0   # too few k-blocks to cut here
     h.check_device_status()
     e32 = rel_err(C, oracle.matmul(Av, Bv, threads=4).astype(np.float64), np.abs(A), np.abs(B))
     e64 = rel_err(C, A.astype(np.float64) @ B.astype(np.float64), np.abs(A), np.abs(B))
@@ -398,4 +398,34 @@ def test_tc_pair_epilogue_batches_and_planes(g, oracle, force_pair):
     Cb, _, _ = g.gpu_matmul(oracle.View.of(Ab), oracle.View.of(Bb), algo=TC)
     assert h.gemm_last_pair()
     assert np.max(np.abs(Cb - Ab.astype(np.float64) @ Bb.astype(np.float64))) <= TOL * 64 * 4
+    h.check_device_status()
+
+
+@pytest.mark.parametrize("mkn", [(2048, 4096, 4096), (768, 4096, 4096), (2048, 4096, 4000)], ids=str)
+@pytest.mark.parametrize("layout", ["nn", "tn"])
+def test_tc_pair_stream_k_tail(g, oracle, mkn, layout):
+    """The CTA-pair kernel with its stream-K tail (one piece per pair, two parked halves per piece): same bar as whole tiles,
+    epilogue options honoured by the completing piece, repeatable bit for bit, flags back to zero after every launch."""
+    M, K, N = mkn
+    h = g.handle()
+    if h.device_info()["sm_count"] != 148:
+        pytest.skip("shapes chosen for 148 SMs")
+    rng = np.random.default_rng(M + K + N + 1)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    Av, Bv = layouts(oracle, A, B, layout)
+    ref64 = A.astype(np.float64) @ B.astype(np.float64)
+    scale = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64) + 1e-30
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert h.gemm_last_pair() and h.gemm_last_stream_k() == 74
+    h.check_device_status()
+    assert float(np.max(np.abs(C - ref64) / scale)) <= 1e-5   # the bar is 1e-4; partial accumulators add a rounding each
+    for _ in range(2):  # the flags were re-armed: the same bits again
+        C2, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+        assert np.array_equal(C, C2)
+    Cb, aux, _ = g.gpu_matmul(Av, Bv, algo=TC, bias=bias, act=1, want_aux=True)
+    z = ref64 + bias
+    assert float(np.max(np.abs(Cb - np.maximum(z, 0)) / scale)) <= 1e-5
+    near_zero = np.abs(z) < 1e-5 * scale
+    assert np.array_equal(aux[~near_zero], (z > 0).astype(np.float32)[~near_zero])
     h.check_device_status()
