@@ -20,6 +20,9 @@
 // empty, the k-blocks of the last tiles are cut into one equal piece per CTA (stream-K): a piece that ends inside a tile
 // parks its accumulator in the workspace, the piece that holds the tile's end adds the parked ones in ascending k and
 // runs the epilogue.  Pieces depend only on lower-numbered pieces and are drawn in ascending order.
+// Long sums.  The tensor core adds into its fp32 accumulator with truncation, so the error of one chain of same-signed
+// products grows with its length.  A k-range above 96 k-blocks therefore travels as several segments whose accumulators
+// the epilogue warps add up in fp32 (round to nearest), the running sum kept where the result goes (C or the parking slot).
 // Operand layouts.  "K-major" = the contraction index is the unit-stride axis (row-major A, or B given
 // as a transposed view); "MN-major" = the other axis is (A given as a transposed view, row-major B).
 // Both are native tcgen05 shared-memory layouts, so transposed stride views need no copy: only the
@@ -92,12 +95,21 @@ struct TcParams {
     int64_t dp_tiles;
     float* sk_partials;          // sk_units slots of BM x BN floats
     unsigned int* sk_flags;      // sk_units words, zero between launches: epilogue warps that have stored their part of slot u
+    // Longest run of k-blocks that is summed in one tensor-memory accumulator (0: no limit).  The tensor core adds into its
+    // fp32 accumulator with truncation, so on same-signed data the error of a chain grows in proportion to its length;
+    // longer ranges are cut into sub-ranges whose sums the epilogue warps add up in fp32 (round to nearest).
+    int chunk_kb;
 };
 
 // What travels from the scheduler to the MMA and epilogue warps: a tile, a range of its k-blocks, and what to do with the
 // accumulator: the normal epilogue (after adding `npred` partial accumulators found in slots slot, slot + 1, ...), or
 // park it as a partial in `slot`.
 constexpr int SEG_PARTIAL = 1;
+// A k-range longer than TcParams::chunk_kb travels as several segments: all but the last only add their accumulator to a
+// running sum (CARRY_OUT) that the following ones pick up (CARRY_IN).  The running sum lives where the range's result goes:
+// in the piece's parking slot, or in C itself.
+constexpr int SEG_CARRY_IN = 2;
+constexpr int SEG_CARRY_OUT = 4;
 __device__ __forceinline__ int seg_info(int kind, int npred, int slot) { return kind | (npred << 4) | (slot << 8); }
 
 // ---------------------------------------------------------------------------------------------------
@@ -341,6 +353,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 return true;
             };
+            // One k-range of a tile as one segment, or as several that carry a running sum (see SEG_CARRY_*).  Each segment is
+            // published just before its own loads: the ring is short.
+            auto emit = [&](int64_t tile, int kb0, int kb1, int info) -> bool {
+                const int len = kb1 - kb0;
+                const int n = (p.chunk_kb > 0 && len > p.chunk_kb) ? (len + p.chunk_kb - 1) / p.chunk_kb : 1;
+                // a result that is added to the old C (beta = 1) takes the old C as the first carry
+                const bool first_carry = !(info & SEG_PARTIAL) && p.beta != 0.f;
+                int a = kb0;
+                for (int s = 0; s < n; ++s) {
+                    const int b = kb0 + (int)((int64_t)len * (s + 1) / n);
+                    int f;
+                    if (s == n - 1) f = info | (n > 1 ? SEG_CARRY_IN : 0);
+                    else f = (info & SEG_PARTIAL) | (info & ~0xFF) | SEG_CARRY_OUT | ((s > 0 || first_carry) ? SEG_CARRY_IN : 0);
+                    if (!publish((int)tile, a, b, f)) return false;
+                    if (!load(tile, a, b)) return false;
+                    a = b;
+                }
+                return true;
+            };
             // Work units: tiles [0, dp_tiles) whole, then sk_units pieces of the linear k-block range of the remaining
             // tiles.  Units are drawn in ascending order and a piece only ever depends on pieces with a lower number,
             // which some running CTA has already drawn, so the waits of the fix-up cannot form a cycle even when not all
@@ -368,9 +399,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (unit >= num_units) { if (!publish(-1, 0, 0, 0)) ok = false; break; }
                 int64_t next = -1;
                 if (unit < p.dp_tiles) {
-                    if (!publish((int)unit, 0, num_kb, 0)) { ok = false; break; }
                     next = draw();  // fetched early: the latency hides under the loads
-                    if (!load(unit, 0, num_kb)) { ok = false; break; }
+                    if (!emit(unit, 0, num_kb, 0)) { ok = false; break; }
                 } else {
                     // piece j covers [begin, end) of the linear range.  Its tiles are walked from the last to the first: the
                     // part that does not reach its tile's end (a partial for piece j + 1 to pick up) goes first, the part
@@ -389,9 +419,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             const int64_t first = base < cut ? base / (sk_q + 1) : sk_r + (base - cut) / sk_q;
                             info = seg_info(0, (int)(j - first), (int)first);
                         }
-                        if (!publish((int)(p.dp_tiles + t), (int)(lo - base), (int)(hi - base), info)) { ok = false; break; }
                         if (next < 0) next = draw();
-                        if (!load(p.dp_tiles + t, (int)(lo - base), (int)(hi - base))) { ok = false; break; }
+                        if (!emit(p.dp_tiles + t, (int)(lo - base), (int)(hi - base), info)) { ok = false; break; }
                         hi = lo;
                     }
                 }
@@ -512,6 +541,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (++sq == SQ) { sq = 0; sphase ^= 1u; }
             if (tile < 0) break;
             const bool partial = (info & SEG_PARTIAL) != 0;
+            const bool carry_in = (info & SEG_CARRY_IN) != 0, carry_out = (info & SEG_CARRY_OUT) != 0;
+            const float beta = carry_in ? 0.f : p.beta;  // the old C came in with the carry
             int npred = (info >> 4) & 15;
             const int slot = info >> 8;
             int64_t batch; int tm, tn;
@@ -532,7 +563,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int64_t row_off0 = (batch * p.M + m_warp + row_sub) * p.N;
             const int64_t clo_off0 = (batch * p.M + m_warp + row_sub) * p.ld_clo;
             const bool plain = !p.bias && !p.bias_m && p.act == TENMO_ACT_NONE && !p.aux && !p.mul_mask && !p.c_lo &&
-                               p.beta == 0.f && p.c_vec;
+                               beta == 0.f && p.c_vec;
             // Stream-K fix-up.  A partial accumulator is parked in its slot in the order the registers come out of tensor
             // memory: float4 number (8 c + q) * 128 + row, so that a warp's store covers 512 contiguous bytes; the warp of
             // the completing CTA that owns the same rows and columns reads it back the same way.  A slot's flag counts the
@@ -569,10 +600,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld32(taddr + (uint32_t)(c * 32), r);
                 tmem_ld_wait();
                 if (partial) {
+                    // (a carried sum is re-read by the thread that wrote it: program order suffices)
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        part[(c * 8 + q) * 128] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                                              __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                    for (int q = 0; q < 8; ++q) {
+                        float4 x = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                        if (carry_in) {
+                            const float4 o = part[(c * 8 + q) * 128];
+                            x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+                        }
+                        part[(c * 8 + q) * 128] = x;
+                    }
                     continue;
                 }
                 for (int s = 0; s < npred; ++s) {  // ascending k: own + partial of the first piece + the next ...
@@ -593,6 +631,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                     __uint_as_float(r[q + 3]));
                 __syncwarp();
                 const int64_t n = n0 + col4;
+                if (carry_out) {
+                    // not the last sub-range of its k-range: the running sum is kept in C (each element by the thread that
+                    // will read it again)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rl = 4 * i + row_sub;
+                        float4 x4 = *reinterpret_cast<const float4*>(ebuf + rl * EP_LD + ((((lane & 7) ^ (rl & 7))) << 2));
+                        if (m_warp + rl >= p.M || n >= p.N) continue;
+                        float* d = p.C + row_off0 + (int64_t)(4 * i) * p.N + n;
+                        if (p.c_vec && n + 3 < p.N) {
+                            if (carry_in) {
+                                const float4 o = *reinterpret_cast<const float4*>(d);
+                                x4.x += o.x; x4.y += o.y; x4.z += o.z; x4.w += o.w;
+                            }
+                            *reinterpret_cast<float4*>(d) = x4;
+                        } else {
+                            const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (n + e < p.N) d[e] = carry_in ? xs[e] + d[e] : xs[e];
+                        }
+                    }
+                    __syncwarp();
+                    continue;
+                }
                 if (plain) {
                     // no epilogue options: the block goes out as it is (a handful of instructions per 16 bytes; the
                     // general path below spends ~25 per element on option checks with one warp per scheduler)
@@ -602,8 +665,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int rl = 4 * i + row_sub;
-                            const float4 x4 = *reinterpret_cast<const float4*>(ebuf + rl * EP_LD + ((((lane & 7) ^ (rl & 7))) << 2));
-                            if (m_warp + 4 * i + row_sub < p.M) *reinterpret_cast<float4*>(dst + i * step) = x4;
+                            float4 x4 = *reinterpret_cast<const float4*>(ebuf + rl * EP_LD + ((((lane & 7) ^ (rl & 7))) << 2));
+                            if (m_warp + 4 * i + row_sub < p.M) {
+                                if (carry_in) {
+                                    const float4 o = *reinterpret_cast<const float4*>(dst + i * step);
+                                    x4.x += o.x; x4.y += o.y; x4.z += o.z; x4.w += o.w;
+                                }
+                                *reinterpret_cast<float4*>(dst + i * step) = x4;
+                            }
                         }
                     }
                     __syncwarp();
@@ -624,7 +693,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const float row_bias = p.bias_m ? __ldg(p.bias_m + m) : 0.f;
                     const int64_t row_off = row_off0 + (int64_t)(4 * i) * p.N;
                     float* crow = p.C + row_off;
-                    const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
+                    float xs[4] = {x4.x, x4.y, x4.z, x4.w};
+                    if (carry_in) {
+                        if (p.c_vec && n + 3 < p.N) {
+                            const float4 o = *reinterpret_cast<const float4*>(crow + n);
+                            xs[0] += o.x; xs[1] += o.y; xs[2] += o.z; xs[3] += o.w;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (n + e < p.N) xs[e] += crow[n + e];
+                        }
+                    }
                     float v[4], mk[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -638,7 +717,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             const float4 mm = __ldg(reinterpret_cast<const float4*>(p.mul_mask + row_off + n));
                             o.x *= mm.x; o.y *= mm.y; o.z *= mm.z; o.w *= mm.w;
                         }
-                        if (p.beta != 0.f) {
+                        if (beta != 0.f) {
                             const float4 old = *reinterpret_cast<const float4*>(crow + n);
                             o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                         }
@@ -653,7 +732,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if (n + e < p.N) {
                                 float o = v[e];
                                 if (p.mul_mask) o *= __ldg(p.mul_mask + row_off + n + e);
-                                if (p.beta != 0.f) o += crow[n + e];
+                                if (beta != 0.f) o += crow[n + e];
                                 crow[n + e] = o;
                                 if (p.aux) p.aux[row_off + n + e] = mk[e];
                                 if (p.c_lo) p.c_lo[clo_off0 + (int64_t)(4 * i) * p.ld_clo + n + e] = tenmo_tf32_lo(o);
@@ -667,7 +746,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (lane == 0) {
                 if (PAIR) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0u));  // both epilogues release it on the leader's barrier
                 else mbar_arrive(tempty_bar(acc));
-                if (partial) {
+                if (partial && !carry_out) {
                     __threadfence();  // the warp's stores (ordered before this by the __syncwarp) are visible before the count
                     atomicAdd(p.sk_flags + slot * SLOT_MUL + slot_add, 1u);
                 }
@@ -1050,6 +1129,18 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     tp.dp_tiles = dp_tiles;
     tp.sk_partials = sk_units ? reinterpret_cast<float*>(static_cast<char*>(ws) + a_lo_bytes + b_lo_bytes) : nullptr;
     tp.sk_flags = reinterpret_cast<unsigned int*>(ctx->dev_status) + TENMO_SK_FLAG_WORD0;
+    // Accumulation chains of at most 96 k-blocks (K = 3072); a longer range is cut into equal sub-ranges.  Measured on a
+    // weight gradient of post-ReLU activations against softmax gradients at K = 8192: one chain is off by 1.2e-4 of
+    // sum |a||b| (the bar is 1e-4), chains of 64 k-blocks by 2.9e-5.  The extra passes of the epilogue warps run beside the
+    // next sub-range's MMAs: 8192^3 is unchanged within the run-to-run spread, a K = 4096 product (two sub-ranges) loses
+    // 3.5 %.  TENMO_TC_CHUNK=<k-blocks> overrides (0: never cut).  Not when the old C is added after an activation or a
+    // mask: there C cannot hold the running sum.
+    tp.chunk_kb = 3072 / BK;
+    {
+        const char* env_ck = getenv("TENMO_TC_CHUNK");
+        if (env_ck && atoi(env_ck) >= 0) tp.chunk_kb = atoi(env_ck);
+    }
+    if (p.beta != 0.f && (p.act != TENMO_ACT_NONE || p.mul_mask)) tp.chunk_kb = 0;
     const int grid = use_pair ? 2 * (sk_units ? pairs : (int)(tiles < pairs ? tiles : pairs))
                               : (sk_units ? ctas : (int)(tiles < ctas ? tiles : ctas));
     // a tile counter pair for this launch (dev_status words 64..127: [next tile, CTAs finished] x 32).  Both words

@@ -403,7 +403,7 @@ def test_tc_pair_epilogue_batches_and_planes(g, oracle, force_pair):
 
 @pytest.mark.parametrize("mkn", [(2048, 4096, 4096), (768, 4096, 4096), (2048, 4096, 4000)], ids=str)
 @pytest.mark.parametrize("layout", ["nn", "tn"])
-def test_tc_pair_stream_k_tail(g, oracle, mkn, layout):
+def test_tc_pair_stream_k_tail(g, oracle, force_pair, mkn, layout):
     """The CTA-pair kernel with its stream-K tail (one piece per pair, two parked halves per piece): same bar as whole tiles,
     epilogue options honoured by the completing piece, repeatable bit for bit, flags back to zero after every launch."""
     M, K, N = mkn
@@ -429,3 +429,105 @@ def test_tc_pair_stream_k_tail(g, oracle, mkn, layout):
     near_zero = np.abs(z) < 1e-5 * scale
     assert np.array_equal(aux[~near_zero], (z > 0).astype(np.float32)[~near_zero])
     h.check_device_status()
+
+
+# ---- long accumulation chains are cut into sub-ranges that the epilogue warps add up --------------------------------
+CHUNK_SHAPES = [(256, 512, 256), (200, 516, 300), (1000, 772, 132), (129, 640, 262), (640, 2052, 388)]
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("mkn", CHUNK_SHAPES, ids=str)
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+def test_tc_cut_accumulation_matches_oracle(g, oracle, monkeypatch, mkn, layout, pair):
+    """TENMO_TC_CHUNK=4 makes every k-range above six k-blocks travel as several carried segments: plain result, result
+    with every epilogue option, accumulate into C (the old C is the first carry), a column count that is not a multiple
+    of four (scalar stores), both kernel forms."""
+    M, K, N = mkn
+    if layout == "tn" and M % 4:
+        pytest.skip("transposed A needs a 16-byte aligned leading stride")
+    if layout != "nt" and N % 4:
+        pytest.skip("row-major B needs a 16-byte aligned leading stride")
+    monkeypatch.setenv("TENMO_TC_CHUNK", "4")
+    monkeypatch.setenv("TENMO_TC_PAIR", str(pair))
+    if pair:
+        monkeypatch.setenv("TENMO_TC_BN", "256")
+    h = g.handle()
+    rng = np.random.default_rng(M * 3 + K * 11 + N)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    init = rng.standard_normal((M, N), np.float32)
+    Av, Bv = layouts(oracle, A, B, layout)
+    ref64 = A.astype(np.float64) @ B.astype(np.float64)
+    scale = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64) + 1e-30
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert h.gemm_last_algo() == TC and h.gemm_last_pair() == bool(pair)
+    h.check_device_status()
+    assert float(np.max(np.abs(C - ref64) / scale)) <= 1e-5
+    Cb, aux, _ = g.gpu_matmul(Av, Bv, algo=TC, bias=bias, act=1, want_aux=True)
+    z = ref64 + bias
+    assert float(np.max(np.abs(Cb - np.maximum(z, 0)) / scale)) <= 1e-5
+    near_zero = np.abs(z) < 1e-5 * scale
+    assert np.array_equal(aux[~near_zero], (z > 0).astype(np.float32)[~near_zero])
+    Ca, _, _ = g.gpu_matmul(Av, Bv, algo=TC, beta=1.0, c_init=init, bias=bias)
+    assert float(np.max(np.abs(Ca - (init + z)) / (scale + np.abs(init)))) <= 1e-5
+    # accumulate after an activation: C cannot hold the running sum, the range is summed in one chain as before
+    Cr, _, _ = g.gpu_matmul(Av, Bv, algo=TC, beta=1.0, c_init=init, act=1)
+    assert float(np.max(np.abs(Cr - (init + np.maximum(ref64, 0))) / (scale + np.abs(init)))) <= 1e-5
+    h.check_device_status()
+    monkeypatch.setenv("TENMO_TC_CHUNK", "0")
+    C0, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    assert float(np.max(np.abs(C - C0) / scale)) <= 4e-6
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+def test_tc_cut_accumulation_with_stream_k(g, oracle, monkeypatch, pair):
+    """Pieces of the stream-K tail that are themselves cut: parked partials carry their sum in the slot, completing pieces
+    in C."""
+    h = g.handle()
+    if h.device_info()["sm_count"] != 148:
+        pytest.skip("shape chosen for 148 SMs")
+    monkeypatch.setenv("TENMO_TC_CHUNK", "16")
+    monkeypatch.setenv("TENMO_TC_PAIR", str(pair))
+    monkeypatch.setenv("TENMO_TC_BN", "256")
+    M, K, N = 2048, 4096, 4096
+    rng = np.random.default_rng(77 + pair)
+    A, B = rng.standard_normal((M, K), np.float32), rng.standard_normal((K, N), np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    Av, Bv = oracle.View.of(A), oracle.View.of(B)
+    ref64 = A.astype(np.float64) @ B.astype(np.float64) + bias
+    scale = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64) + 1e-30
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=TC, bias=bias)
+    assert h.gemm_last_stream_k() > 0 and h.gemm_last_pair() == bool(pair)
+    h.check_device_status()
+    assert float(np.max(np.abs(C - ref64) / scale)) <= 1e-5
+    C2, _, _ = g.gpu_matmul(Av, Bv, algo=TC, bias=bias)
+    assert np.array_equal(C, C2)
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+def test_tc_long_chain_of_same_signed_products(g, monkeypatch, pair):
+    """The tensor core adds into its accumulator with truncation, so a chain of same-signed products drifts in proportion to
+    its length (K = 8192 in one chain: about 1e-4 of sum |a||b|, the bar itself).  The kernel cuts chains above 96 k-blocks
+    and adds the sub-sums in fp32 with rounding: a weight gradient of post-ReLU activations against one-sided gradients
+    stays well inside the bar."""
+    monkeypatch.setenv("TENMO_TC_PAIR", str(pair))
+    monkeypatch.setenv("TENMO_TC_STREAMK", "0")
+    monkeypatch.setenv("TENMO_TC_BN", "256")
+    M, K, N = 2048, 8192, 1024
+    rng = np.random.default_rng(5)
+    A = np.maximum(rng.standard_normal((K, M), np.float32), 0)      # activations, stored (batch, features): used transposed
+    B = np.abs(rng.standard_normal((K, N), np.float32)) * np.float32(1e-4)
+    from oracle.ref import View
+
+    Av, Bv = View.of(A).t(), View.of(B)
+    C, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    h = g.handle()
+    assert h.gemm_last_algo() == TC and h.gemm_last_pair() == bool(pair) and h.gemm_last_stream_k() == 0
+    h.check_device_status()
+    ref64 = A.T.astype(np.float64) @ B.astype(np.float64)   # all terms >= 0: sum |a||b| is the result itself
+    cut = float(np.max(np.abs(C - ref64) / ref64))
+    assert cut <= 8e-5, cut
+    monkeypatch.setenv("TENMO_TC_CHUNK", "0")
+    C1, _, _ = g.gpu_matmul(Av, Bv, algo=TC)
+    one_chain = float(np.max(np.abs(C1 - ref64) / ref64))
+    assert cut < 0.6 * one_chain, (cut, one_chain)
