@@ -433,7 +433,7 @@ def measure_cnn(h, rank, world, local_rank, timed, args, rng, gen):
         "ms_per_step": ms / args.mlp_steps, "scaling": "strong", "global_batch": gbc, "per_rank_batch": hi - lo,
         "steps": args.mlp_steps, "check_after_3_steps": check,
         "config": "(256,3,32,32) U[0,1): conv3x3 3->32 pad1, ReLU, maxpool2, conv3x3 32->64 pad1, ReLU, maxpool2, "
-                  "Linear 4096->10, softmax-CE, SGD momentum 0.9; convolutions as im2col + strict-fp32 GEMM",
+                  "Linear 4096->10, softmax-CE, SGD momentum 0.9; convolutions by the implicit-GEMM kernels (strict fp32, ReLU mask fused into the backward loads)",
     }
     res["exchange"] = cnn.exchange
     if world > 1:

@@ -99,6 +99,7 @@ struct TcParams {
     // fp32 accumulator with truncation, so on same-signed data the error of a chain grows in proportion to its length;
     // longer ranges are cut into sub-ranges whose sums the epilogue warps add up in fp32 (round to nearest).
     int chunk_kb;
+    int group_m;  // row tiles per group of the tile order
 };
 
 // What travels from the scheduler to the MMA and epilogue warps: a tile, a range of its k-blocks, and what to do with the
@@ -210,8 +211,7 @@ __device__ __forceinline__ float act_apply(float v, int act) {
 
 // Tile order: groups of GROUP_M row tiles are walked column by column, so that the tiles running at
 // the same time share A and B panels in L2.
-constexpr int GROUP_M = 16;
-__device__ __forceinline__ void tile_coords(int64_t tile, int tiles_m, int tiles_n, int64_t* batch, int* tm, int* tn) {
+__device__ __forceinline__ void tile_coords(int64_t tile, int tiles_m, int tiles_n, int GROUP_M, int64_t* batch, int* tm, int* tn) {
     const int64_t per_batch = (int64_t)tiles_m * tiles_n;
     *batch = tile / per_batch;
     const int t = (int)(tile % per_batch);
@@ -310,7 +310,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             };
             auto load = [&](int64_t tile, int kb0, int kb1) -> bool {
                 int64_t batch; int tm, tn;
-                tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
+                tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, &batch, &tm, &tn);
                 // PAIR: this CTA's 128 rows of the 256-row tile and its half of the tile's columns
                 const int m0 = PAIR ? tm * (2 * BM) + (int)crank * BM : tm * BM;
                 const int n0 = tn * BN + (PAIR ? (int)crank * (BN / 2) : 0);
@@ -546,7 +546,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int npred = (info >> 4) & 15;
             const int slot = info >> 8;
             int64_t batch; int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, &batch, &tm, &tn);
+            tile_coords(tile, p.tiles_m, p.tiles_n, p.group_m, &batch, &tm, &tn);
             if (PAIR) tm = 2 * tm + (int)crank;  // this CTA's 128 rows of the pair's 256-row tile
             if (!warp_wait(tfull_bar(acc), acc_phase[acc])) { ok = false; break; }
             tcgen05_fence_after();
@@ -1135,6 +1135,13 @@ int tenmo_gemm_tc_launch(tenmo_ctx* ctx, const TenmoGemmParams& p) {
     // next sub-range's MMAs: 8192^3 is unchanged within the run-to-run spread, a K = 4096 product (two sub-ranges) loses
     // 3.5 %.  TENMO_TC_CHUNK=<k-blocks> overrides (0: never cut).  Not when the old C is added after an activation or a
     // mask: there C cannot hold the running sum.
+    // Tile order: groups of 16 row tiles walked column by column.  Measured at 8192^3 with CTA pairs: groups of 16 / 8 / 4
+    // read 10.2 / 9.3 / 12.0 GB from DRAM per launch, speeds within the run-to-run spread.  TENMO_TC_GROUP_M overrides.
+    tp.group_m = 16;
+    {
+        const char* env_gm = getenv("TENMO_TC_GROUP_M");
+        if (env_gm && atoi(env_gm) >= 1) tp.group_m = atoi(env_gm);
+    }
     tp.chunk_kb = 3072 / BK;
     {
         const char* env_ck = getenv("TENMO_TC_CHUNK");

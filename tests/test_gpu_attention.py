@@ -1,4 +1,4 @@
-"""Broadcast-batched and attention-shaped matmul with full autograd backward (BASELINE config 3).
+"""Broadcast-batched and attention-shaped matmul with full autograd backward (384 x (512, 64) heads and (32, 512, 768) @ (1, 768, 768)).
 
 Small shapes go through the strict-fp32 kernel and are compared with the oracle chain element by element;
 the full-size shapes (B*H = 384, S = 512, D = 64 and (32,512,768)@(1,768,768)) go through the tensor-core

@@ -12,7 +12,7 @@ def xavier(rng, dims):
 
 
 def test_mnist_shaped_training_bit_consistent_accuracy(oracle):
-    """BASELINE config 1 shapes, synthetic data: 60 free-running steps, eager; argmax and the correct-count are
+    """MNIST-shaped MLP (784-128-32-10, batch 64), synthetic data: 60 free-running steps, eager; argmax and the correct-count are
     bit-identical to the oracle's at every step (strict-fp32 GEMM, sequential small reductions, unfused SGD)."""
     from tenmo_b200.trainer import MLPTrainer
 
