@@ -60,7 +60,7 @@ def test_graph_replay_equals_eager(oracle):
 
 
 def test_wide_mlp_tensor_core_step_matches_oracle(oracle):
-    """A scaled-down wide MLP (config 4 layout: Linear+ReLU x3, Linear, softmax-CE) on the 3xTF32 kernel."""
+    """A scaled-down wide MLP (Linear+ReLU x3, Linear, softmax-CE) on the 3xTF32 kernel."""
     from tenmo_b200.trainer import MLPTrainer
 
     rng = np.random.default_rng(9)
