@@ -343,8 +343,8 @@ int tenmo_dp_finalize(tenmo_ctx* ctx);
  * handles; the ranks share their handle blocks out of band, rank-major, and every rank calls tenmo_dp_p2p_connect
  * with all of them.  tenmo_dp_p2p_allreduce_sum_f32 then sums bucket[offset, offset + count) over the ranks in place,
  * asynchronously on the context stream: every element is added once, in rank order, by the rank that owns its
- * shard, so all ranks end with identical bits.  All ranks must make the same calls in the same order.  The kernel is
- * small enough to run beside the persistent GEMM kernels; its waits on the peers are bounded (2 s) and report through
+ * shard, so all ranks end with identical bits.  All ranks must make the same calls in the same order.  Its waits on the
+ * peers are bounded (2 s) and report through
  * tenmo_cuda_check_device_status.  At most 8 ranks, all on one node.  tenmo_dp_p2p_close unmaps and frees; the ranks
  * must have finished using each other's buckets (a host barrier) before any of them calls it. */
 #define TENMO_DP_P2P_HANDLE_BYTES 128

@@ -1,12 +1,13 @@
 // Data-parallel gradient exchange over NVLink peer memory: a sum all-reduce written as ONE kernel per call.
 //
-// Why not only NCCL: the exchange of a layer's gradients should run beside the backward GEMMs of the layers below,
-// but the persistent GEMM kernel holds every SM with one large CTA, and NCCL's CTAs (hundreds of threads, ~100
-// registers each) cannot share an SM with it, so they wait for GEMM CTAs to leave.  The kernel here is built to
-// co-reside: the GEMM CTA leaves about 11 K of an SM's 64 K registers and a few KB of shared memory free, so the exchange
-// runs as 128 CTAs of 128 threads at no more than 85 registers each (one fits beside the GEMM CTA of every SM it lands
-// on), with no shared-memory tile.  A larger CTA would not fit and would wait for a GEMM CTA to leave, then keep that SM
-// from the next GEMM launch for as long as the exchange waits on its peers.
+// Why not only NCCL: one launch per layer does the reduce-scatter, (optionally) the optimiser on the rank's own shard and
+// the all-gather, with peer loads and stores only, and it can be replayed from a captured CUDA graph.  Two geometries:
+//   * stand-alone (default): 128 CTAs of 512 threads, eight 16-byte peer loads in flight per thread;
+//   * co-resident (tenmo_dp_p2p_set_coresident): 128 CTAs of 128 threads at no more than 85 registers and without any
+//     shared memory, so that one fits beside the persistent GEMM CTA of an SM (which leaves about 11 K of the 64 K
+//     registers and 2 KB of shared memory free) when the exchange is issued on a side stream beside the backward GEMMs.
+//     NCCL's CTAs cannot do that: they wait for GEMM CTAs to leave.  Measured, the overlap only pays while the GEMMs
+//     beside it have several rounds of tiles; beside single-round GEMMs (1024 rows per rank) it costs more than it hides.
 //
 // Setup (one process per GPU): every rank allocates the gradient bucket and a small flag block with
 // tenmo_dp_p2p_alloc, the ranks exchange the two CUDA IPC handles out of band (the host's job, like NCCL's unique id),
@@ -21,7 +22,7 @@
 //       travels as pushes while the reduce-scatter's loads are still coming in, so both NVLink directions are busy);
 //   wait until every peer has finished its shard: its pushes have then landed here (it fenced before it raised its flag)
 //       and it has finished reading this rank's bucket (the next backward pass may overwrite it).
-// The two waits are flags in peer memory, one per (phase, source rank, CTA): CTA b of a rank only ever depends on
+// The two waits are flags in peer memory, one word per (phase, source rank, CTA): CTA b of a rank only ever depends on
 // CTA b of its peers (a shard is cut into chunks dealt round-robin to the CTAs, identically on every rank), so no
 // grid-wide synchronisation is needed.  Flags carry the call's epoch (monotonic), so nothing is ever reset.
 // The epoch lives on the device: a word of this rank's own flag block counts the calls that have completed, every CTA
