@@ -258,3 +258,49 @@ CONV_BWD = [
          stride=2, dilation=1, pad=1, out_shape=(2, 4, 4, 4), dbias=[32.0, 32.0, 32.0, 32.0],
          dk_plane=[[18.0, 24.0, 24.0], [24.0, 32.0, 32.0], [24.0, 32.0, 32.0]]),
 ]
+
+# ---- tests/test_blas.mojo: the reference's own C-ABI seam (BLASHandle.matmul over cblas_sgemm, blashandle.mojo:108-251) ----
+# ta / tb: the call's transpose_A / transpose_B flags; "C" full result, "C00" the one element the reference asserts,
+# "dA" / "dB" gradients of sum(C).
+BLAS_SEAM = [
+    # :77-91
+    dict(name="simple_f32", A=[[1.0, 2.0], [3.0, 4.0]], B=[[5.0, 6.0], [7.0, 8.0]], ta=False, tb=False,
+         C=[[19.0, 22.0], [43.0, 50.0]]),
+    # :109-123  A @ I = A
+    dict(name="identity", A=[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], B=[[1.0, 0.0, 0.0], [0.0, 1.0, 0.0], [0.0, 0.0, 1.0]],
+         ta=False, tb=False, C=[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]]),
+    # :126-144
+    dict(name="rectangular", A=[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]],
+         B=[[1.0, 2.0, 3.0, 4.0], [5.0, 6.0, 7.0, 8.0], [9.0, 10.0, 11.0, 12.0]], ta=False, tb=False, shape=(2, 4), C00=38.0),
+    # :150-170  A^T @ B
+    dict(name="transpose_a", A=[[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]], B=[[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]], ta=True, tb=False,
+         shape=(2, 2), C00=35.0),
+    # :173-190  A @ B^T
+    dict(name="transpose_b", A=[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], B=[[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], ta=False, tb=True,
+         shape=(2, 2), C00=14.0),
+    # :193-210  A^T @ B^T
+    dict(name="transpose_both", A=[[1.0, 2.0], [3.0, 4.0]], B=[[5.0, 6.0], [7.0, 8.0]], ta=True, tb=True, shape=(2, 2), C00=23.0),
+    # :258-285  gradients of sum(A @ B)
+    dict(name="backward_simple", A=[[1.0, 2.0], [3.0, 4.0]], B=[[5.0, 6.0], [7.0, 8.0]], ta=False, tb=False,
+         dA=[[11.0, 15.0], [11.0, 15.0]], dB=[[4.0, 4.0], [6.0, 6.0]]),
+    # :640-694  gradients of sum(A^T @ B) (the values the reference prints as its expectation)
+    dict(name="case_2_At_B", A=[[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]],
+         B=[[7.0, 8.0, 9.0], [10.0, 11.0, 12.0], [13.0, 14.0, 15.0]], ta=True, tb=False,
+         dA=[[24.0, 24.0], [33.0, 33.0], [42.0, 42.0]], dB=[[3.0, 3.0, 3.0], [7.0, 7.0, 7.0], [11.0, 11.0, 11.0]]),
+]
+# :216-232 ones(100,100) @ ones(100,100): every element 100;  :469-486 ones(100,1) @ ones(1,100): every element 1
+BLAS_SEAM_ONES = [dict(M=100, K=100, N=100, value=100.0), dict(M=100, K=1, N=100, value=1.0)]
+# :1033-1088 central difference of sum(A @ B) in A[0,0] with eps 1e-4 against the analytic gradient, tolerance 0.014
+BLAS_SEAM_FD = dict(A=[[1.0, 2.0], [3.0, 4.0]], B=[[5.0, 6.0], [7.0, 8.0]], eps=1e-4, tol=0.014, dA00=11.0)
+
+# ---- tests/test_dot.mojo: vector . vector ----
+DOT = [
+    dict(a=[1.0, 2.0, 3.0], b=[4.0, 5.0, 6.0], value=32.0),        # :18-24, gradients :108-116 (da = b, db = a)
+    dict(a=[1.0, 1.0, 1.0, 1.0], b=[2.0, 3.0, 4.0, 5.0], value=14.0),   # :27-33
+    dict(a=[1.0, -2.0, 3.0], b=[-1.0, 2.0, -3.0], value=-14.0),     # :36-42
+    dict(a=[3.0], b=[7.0], value=21.0),                              # :45-50
+    dict(a=[1.0, 0.0], b=[0.0, 1.0], value=0.0),                     # :53-59
+    dict(a=[3.0, 7.0, 2.0], b=[1.0, 1.0, 1.0], value=12.0),          # :137-145 (gradients: ones and a)
+]
+# :148-160  loss = d + d with d = a . b: gradients 2 b and 2 a
+DOT_CHAINED = dict(a=[1.0, 2.0, 3.0], b=[4.0, 5.0, 6.0], da=[8.0, 10.0, 12.0], db=[2.0, 4.0, 6.0])

@@ -234,3 +234,79 @@ def test_gemv_rejects_a_matrix_without_a_unit_stride(g):
     with pytest.raises(TenmoError):
         xv, yv = g.empty(4), g.empty(4)
         g.handle().gemv(4, 4, make_mat(A.data_ptr(), (4, 4), (32, 2)), xv.data_ptr(), 1, yv.data_ptr())
+
+
+# ---- the reference's own C-ABI seam (tests/test_blas.mojo) and dot (tests/test_dot.mojo) ---------------------------------
+from tests.test_oracle_reference_literals import seam_views  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def tm():
+    import tenmo_b200.tensor as tensor
+
+    tensor.handle()
+    tensor.set_gemm_algo("simt")
+    return tensor
+
+
+@pytest.mark.parametrize("case", kat.BLAS_SEAM, ids=lambda c: c["name"])
+def test_blas_seam_literals_through_the_c_abi(g, oracle, case):
+    """blas.matmul(A, B, transpose_A, transpose_B) becomes tenmo_gemm_f32 on stride views of the stored operands."""
+    _, _, Av, Bv = seam_views(oracle, case)
+    C, _, _ = g.gpu_matmul(Av, Bv)
+    g.handle().check_device_status()
+    assert np.array_equal(C, oracle.matmul(Av, Bv))
+    if "C" in case:
+        assert np.array_equal(C, f32(case["C"]))
+    if "shape" in case:
+        assert C.shape == case["shape"] and C[0, 0] == np.float32(case["C00"])
+
+
+@pytest.mark.parametrize("case", [c for c in kat.BLAS_SEAM if "dA" in c], ids=lambda c: c["name"])
+def test_blas_seam_gradients_through_the_host_mirror(tm, case):
+    A = tm.Tensor.d2(case["A"], requires_grad=True)
+    B = tm.Tensor.d2(case["B"], requires_grad=True)
+    left = A.transpose() if case["ta"] else A
+    right = B.transpose() if case["tb"] else B
+    left.matmul(right).sum().backward()
+    assert A.grad().all_close(f32(case["dA"])) and B.grad().all_close(f32(case["dB"]))
+
+
+@pytest.mark.parametrize("case", kat.BLAS_SEAM_ONES, ids=lambda c: f"{c['M']}x{c['K']}x{c['N']}")
+def test_blas_seam_ones(g, oracle, case):
+    A, B = np.ones((case["M"], case["K"]), np.float32), np.ones((case["K"], case["N"]), np.float32)
+    C, _, _ = g.gpu_matmul(oracle.View.of(A), oracle.View.of(B))
+    assert C.shape == (case["M"], case["N"]) and np.all(C == np.float32(case["value"]))
+
+
+def test_blas_seam_finite_difference(g, oracle):
+    c = kat.BLAS_SEAM_FD
+    A, B = f32(c["A"]), f32(c["B"])
+    plus, minus = A.copy(), A.copy()
+    plus[0, 0] += np.float32(c["eps"])
+    minus[0, 0] -= np.float32(c["eps"])
+    V = oracle.View
+    lp = np.float32(g.gpu_matmul(V.of(plus), V.of(B))[0].sum(dtype=np.float32))
+    lm = np.float32(g.gpu_matmul(V.of(minus), V.of(B))[0].sum(dtype=np.float32))
+    analytic = g.gpu_matmul(V.of(np.ones((2, 2), np.float32)), V.of(B).t())[0][0, 0]
+    assert analytic == np.float32(c["dA00"]) and abs(float(analytic) - float((lp - lm) / np.float32(2 * c["eps"]))) < c["tol"]
+
+
+@pytest.mark.parametrize("case", kat.DOT, ids=lambda c: str(c["value"]))
+def test_dot_literals(tm, case):
+    a = tm.Tensor.d1(case["a"], requires_grad=True)
+    b = tm.Tensor.d1(case["b"], requires_grad=True)
+    d = a.matmul(b)
+    assert d.item() == case["value"]
+    d.backward()
+    assert a.grad().all_close(f32(case["b"])) and b.grad().all_close(f32(case["a"]))   # d(a.b)/da = b, /db = a
+
+
+def test_dot_gradients_accumulate_like_the_chained_case(tm):
+    # tests/test_dot.mojo:148-160 uses loss = d + d; two backward passes of d accumulate the same 2 b and 2 a
+    c = kat.DOT_CHAINED
+    a = tm.Tensor.d1(c["a"], requires_grad=True)
+    b = tm.Tensor.d1(c["b"], requires_grad=True)
+    for _ in range(2):
+        a.matmul(b).backward()
+    assert a.grad().all_close(f32(c["da"])) and b.grad().all_close(f32(c["db"]))

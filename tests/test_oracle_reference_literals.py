@@ -198,3 +198,59 @@ def test_conv_backward_literals(oracle, case):
         assert out.shape == tuple(case["out_shape"])
     dx, dk, db = oracle.conv2d_bwd(np.ones_like(out), x, k, **kw)
     check_conv_backward(case, dx, dk, db)
+
+
+# ---- the reference's own C-ABI seam (BLASHandle.matmul) and dot -------------------------------------------------------
+def seam_views(oracle, case):
+    """Operands of a BLAS-seam case as the views the call multiplies: a transpose flag is a stride view, as in the
+    backward GEMMs."""
+    A, B = f32(case["A"]), f32(case["B"])
+    Av, Bv = oracle.View.of(A), oracle.View.of(B)
+    return A, B, (Av.t() if case["ta"] else Av), (Bv.t() if case["tb"] else Bv)
+
+
+def seam_gradients(oracle, case):
+    """Gradients of sum(op(A) @ op(B)) with respect to the STORED A and B (matmul.mojo:24-54 applied to the views)."""
+    A, B, Av, Bv = seam_views(oracle, case)
+    M, N = Av.shape[-2], Bv.shape[-1]
+    G = oracle.View.of(np.ones((M, N), np.float32))
+    d_opA = oracle.matmul(G, Bv.t())   # gradient of the view op(A)
+    d_opB = oracle.matmul(Av.t(), G)
+    return (d_opA.T if case["ta"] else d_opA), (d_opB.T if case["tb"] else d_opB)
+
+
+@pytest.mark.parametrize("case", kat.BLAS_SEAM, ids=lambda c: c["name"])
+def test_blas_seam_literals(oracle, case):
+    _, _, Av, Bv = seam_views(oracle, case)
+    C = oracle.matmul(Av, Bv)
+    if "C" in case:
+        assert np.array_equal(C, f32(case["C"]))
+    if "shape" in case:
+        assert C.shape == case["shape"] and C[0, 0] == np.float32(case["C00"])
+    if "dA" in case:
+        dA, dB = seam_gradients(oracle, case)
+        assert np.array_equal(dA, f32(case["dA"])) and np.array_equal(dB, f32(case["dB"]))
+
+
+@pytest.mark.parametrize("case", kat.BLAS_SEAM_ONES, ids=lambda c: f"{c['M']}x{c['K']}x{c['N']}")
+def test_blas_seam_ones(oracle, case):
+    C = oracle.matmul(np.ones((case["M"], case["K"]), np.float32), np.ones((case["K"], case["N"]), np.float32))
+    assert C.shape == (case["M"], case["N"]) and np.all(C == np.float32(case["value"]))
+
+
+def test_blas_seam_finite_difference(oracle):
+    c = kat.BLAS_SEAM_FD
+    A, B = f32(c["A"]), f32(c["B"])
+    plus, minus = A.copy(), A.copy()
+    plus[0, 0] += np.float32(c["eps"])
+    minus[0, 0] -= np.float32(c["eps"])
+    fd = (np.float32(oracle.matmul(plus, B).sum(dtype=np.float32)) - np.float32(oracle.matmul(minus, B).sum(dtype=np.float32))) / np.float32(2 * c["eps"])
+    analytic = oracle.matmul(np.ones((2, 2), np.float32), oracle.View.of(B).t())[0, 0]
+    assert analytic == np.float32(c["dA00"]) and abs(float(analytic) - float(fd)) < c["tol"]
+
+
+@pytest.mark.parametrize("case", kat.DOT, ids=lambda c: str(c["value"]))
+def test_dot_literals(oracle, case):
+    a, b = f32(case["a"]), f32(case["b"])
+    d = oracle.matmul(a[None, :], b[:, None])   # dot as the (1,k) @ (k,1) product the GPU path runs
+    assert d.shape == (1, 1) and d[0, 0] == np.float32(case["value"])
