@@ -188,3 +188,29 @@ class CNNTrainer(BatchFeed):
 
     def grads(self) -> dict:
         return {n: t.detach().cpu().numpy() for n, t in self.g.items()}
+
+    # Module index of each parameterised layer inside Sequential(Conv2D, ReLU, MaxPool2d, Conv2D, ReLU, MaxPool2d, Flatten,
+    # Linear): the reference names checkpoint entries "<index>.weight" / "<index>.bias" (numpy_interop.mojo:166-196;
+    # tests/test_checkpoint.mojo:41-54 shows the numbering skipping layers without parameters).
+    _CKPT_INDEX = {"conv1": 0, "conv2": 3, "fc": 7}
+
+    def state_dict(self) -> dict:
+        """Parameters under the reference's checkpoint names plus the SGD velocities (flat, in parameter order)."""
+        torch.cuda.synchronize(self.dev)
+        out = {}
+        for n, t in self.p.items():
+            layer, kind = n.split(".")
+            out[f"{self._CKPT_INDEX[layer]}.{kind}"] = t.detach().cpu().numpy().copy()
+        out["__velocity__"] = self.V.detach().cpu().numpy().copy()
+        return out
+
+    def load_state_dict(self, sd: dict):
+        for n, t in self.p.items():
+            layer, kind = n.split(".")
+            src = np.ascontiguousarray(sd[f"{self._CKPT_INDEX[layer]}.{kind}"], np.float32)
+            if src.shape != tuple(t.shape):
+                raise ValueError(f"checkpoint entry for {n} has shape {src.shape}, the model holds {tuple(t.shape)}")
+            t.copy_(torch.from_numpy(src))
+        if "__velocity__" in sd:
+            self.V.copy_(torch.from_numpy(np.ascontiguousarray(sd["__velocity__"], np.float32)))
+        torch.cuda.synchronize(self.dev)

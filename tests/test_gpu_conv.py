@@ -178,3 +178,30 @@ def test_cifar_shaped_cnn_step_matches_oracle(g, oracle):
     tr.step(X, y, update=False)
     assert tr.loss_value() < first
     g.handle().check_device_status()
+
+
+def test_cnn_checkpoint_round_trip_with_the_reference_key_names(g, tmp_path):
+    """state_dict uses "<module index>.weight" / ".bias" as the reference's save_checkpoint does for
+    Sequential(Conv2D, ReLU, MaxPool2d, Conv2D, ReLU, MaxPool2d, Flatten, Linear) (tests/test_checkpoint.mojo:41-54,
+    102-117); a trainer restored from the file continues with the same bits, momentum included."""
+    from tenmo_b200.cnn import CNNTrainer
+
+    rng = np.random.default_rng(56)
+    B = 8
+    X = rng.uniform(0, 1, (B, 3, 32, 32)).astype(np.float32)
+    y = rng.integers(0, 10, B)
+    a = CNNTrainer(_cnn_params(rng), batch=B, handle=g.handle())
+    for _ in range(3):
+        a.step(X, y)
+    sd = a.state_dict()
+    assert sorted(k for k in sd if not k.startswith("__")) == ["0.bias", "0.weight", "3.bias", "3.weight", "7.bias", "7.weight"]
+    assert sd["0.weight"].shape == (32, 3, 3, 3) and sd["3.weight"].shape == (64, 32, 3, 3) and sd["7.weight"].shape == (4096, 10)
+    np.save(tmp_path / "cnn.npy", sd, allow_pickle=True)
+    b = CNNTrainer(_cnn_params(np.random.default_rng(57)), batch=B, handle=g.handle())
+    b.load_state_dict(np.load(tmp_path / "cnn.npy", allow_pickle=True).item())
+    for tr in (a, b):
+        tr.step(X, y)
+    torch.cuda.synchronize()
+    pa, pb = a.params(), b.params()
+    assert all(np.array_equal(pa[n], pb[n]) for n in pa)
+    g.handle().check_device_status()
