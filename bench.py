@@ -42,6 +42,18 @@ def host_cores() -> int:
         return os.cpu_count() or 1
 
 
+def host_isa() -> str:
+    """What the CPU baseline's code can use: the oracle is built for AVX2 + FMA (one build runs on every host); the
+    host's widest vector extension is named beside it."""
+    try:
+        with open("/proc/cpuinfo") as f:
+            flags = next((line.split(":", 1)[1].split() for line in f if line.startswith("flags")), [])
+    except OSError:
+        flags = []
+    widest = "AVX-512" if "avx512f" in flags else "AVX2" if "avx2" in flags else "unknown"
+    return f"built for AVX2+FMA, host has {widest}"
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one-pass ncu captures of this file's own
 # workloads.  A number taken under a profiler is never timed here; only the byte counts are carried over.
 NCU_TRAFFIC_BYTES = {
@@ -90,7 +102,8 @@ def cpu_baseline(budget_s: float = 20.0):
         secs = cpu_fwd_bwd(size, threads)
     flops = 6.0 * size ** 3
     return dict(value=flops / secs / 1e12, unit=UNIT, cores=threads, kind="port",
-                sample=f"one fwd+bwd at {size}^3 ({secs:.2f} s), oracle port of matmul_cpu.mojo, {threads} threads over row tiles")
+                sample=f"one fwd+bwd at {size}^3 ({secs:.2f} s), oracle port of matmul_cpu.mojo, {threads} threads over row tiles; "
+                       f"{host_isa()}")
 
 
 def gemm_workload_text(S: int) -> str:
@@ -126,7 +139,8 @@ def run_reference_arm(args):
     dt = time.perf_counter() - t0
     flops = 6.0 * size ** 3 * args.steps
     value = flops / dt / 1e12
-    sample = f"each step = one fwd+bwd at {size}^3 on {threads} host threads (oracle port; the Mojo reference cannot be built here)"
+    sample = (f"each step = one fwd+bwd at {size}^3 on {threads} host threads (oracle port; the Mojo reference cannot be built "
+              f"here); {host_isa()}")
     workload = gemm_workload_text(args.size)
     if size != args.size:
         workload += f" [CPU arm: timed at {size}^3, extrapolated to {args.size}^3 as a rate]"
@@ -965,8 +979,8 @@ def run_kernel_rooflines(args, h=None, collect=None):
             "algorithmic_bytes": alg_bytes,
             "note": note}
         if collect is not None:
-            collect[name] = {"gbs": gbs, "frac": gbs / peaks["hbm_gbs"], "avg_launch_ms": ms, "algorithmic_bytes": alg_bytes,
-                             "note": note}
+            collect[name] = {"gbs": gbs, "frac": gbs / peaks["hbm_gbs"], "frac_of_nominal_8tbs": gbs / 8000.0,
+                             "avg_launch_ms": ms, "algorithmic_bytes": alg_bytes, "note": note}
         else:
             print(json.dumps(entry), flush=True)
 
