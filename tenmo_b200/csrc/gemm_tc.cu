@@ -521,7 +521,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         int sq = 0;
         uint32_t sphase = 0;
-        // Lane 0 does the waiting and the warp follows its verdict, so the warp never diverges around the
+        // Lane 0 does the waiting and the warp follows its result, so the warp never diverges around the
         // warp-collective tcgen05.ld below, not even when a wait is abandoned.
         auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool {
             int got = 1;
