@@ -22,6 +22,17 @@ def shard_rows(global_batch: int, rank: int, world: int) -> tuple[int, int]:
     return rank * per, (rank + 1) * per
 
 
+def optimizer_shard(count: int, rank: int, world: int) -> tuple[int, int]:
+    """[lo, hi) of the `count` floats of a layer whose gradients rank `rank` sums and whose optimiser state it owns in
+    the sharded exchange (tenmo_dp_p2p_sgd_step_f32): equal shards rounded up to four floats, the last ones short or
+    empty.  The same arithmetic as the kernel's, so that checkpoints can gather and re-deal the momentum."""
+    if not 0 <= rank < world or count < 0:
+        raise ValueError(f"rank {rank} / world {world} / count {count}")
+    sz = ((count + world - 1) // world + 3) // 4 * 4
+    lo = min(count, rank * sz)
+    return lo, min(count, lo + sz)
+
+
 def exchange_unique_id(get_unique_id, rank: int, world: int, broadcast_bytes) -> bytes | None:
     """Rank 0 draws the 128-byte NCCL id (``get_unique_id()``), everyone receives it through
     ``broadcast_bytes(buf: bytearray, src=0)`` -- any out-of-band channel (a torch.distributed gloo / nccl

@@ -27,7 +27,7 @@ import torch
 
 from . import lib as _lib
 from .lib import TenmoCuda, make_mat
-from .parallel import shard_rows
+from .parallel import optimizer_shard, shard_rows
 
 
 class BatchFeed:
@@ -469,9 +469,7 @@ class MLPTrainer(BatchFeed):
         """1.0 where this rank owns the optimiser state (the shards tenmo_dp_p2p_sgd_step_f32 deals per layer)."""
         m = torch.zeros(self.numel, dtype=torch.float32, device=f"cuda:{self.dev}")
         for start, count in self.layer_span:
-            sz = ((count + self.world - 1) // self.world + 3) // 4 * 4
-            lo = min(count, self.rank * sz)
-            hi = min(count, lo + sz)
+            lo, hi = optimizer_shard(count, self.rank, self.world)
             m[start + lo:start + hi] = 1.0
         return m
 

@@ -14,8 +14,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from tenmo_b200.parallel import (DeviceFloats, averaged_gradients, connect_peer_buckets, exchange_unique_id, shard_rows,
-                                 torch_all_gather_bytes, torch_broadcast_bytes)
+from tenmo_b200.parallel import (DeviceFloats, averaged_gradients, connect_peer_buckets, exchange_unique_id, optimizer_shard,
+                                 shard_rows, torch_all_gather_bytes, torch_broadcast_bytes)
 
 
 def test_shard_rows():
@@ -101,3 +101,82 @@ def test_device_floats_interface():
     d = DeviceFloats(0xABC000, 12)
     iface = d.__cuda_array_interface__
     assert iface["shape"] == (12,) and iface["typestr"] == "<f4" and iface["data"] == (0xABC000, False)
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("count", [0, 1, 3, 4, 10, 1000, 4096 * 1000, 16777216, 16777219])
+def test_optimizer_shards_tile_the_layer(count, world):
+    """The shards of the sharded-optimiser exchange cover [0, count) once, in rank order, every boundary but the end a
+    multiple of four floats (16-byte accesses), sizes differing by less than one rounded shard."""
+    spans = [optimizer_shard(count, r, world) for r in range(world)]
+    assert spans[0][0] == 0 and spans[-1][1] == count
+    for (lo, hi), (nlo, _) in zip(spans, spans[1:]):
+        assert lo <= hi == nlo and hi % 4 == 0 or hi == count
+    assert all(lo % 4 == 0 or lo == count for lo, _ in spans)
+    sz = max(hi - lo for lo, hi in spans)
+    assert sz <= (count + world - 1) // world + 3
+    with pytest.raises(ValueError):
+        optimizer_shard(8, 2, 2)
+
+
+def _sharded_worker(rank, world, port, out_dir):
+    """The algorithm of tenmo_dp_p2p_sgd_step_f32 on the host: every rank holds its own gradient copy; the owner of a
+    shard adds the W copies in rank order, applies SGD-momentum with grad_scale = 1/world to its shard of the parameters
+    (its velocities never leave the rank) and the updated shards are gathered by everyone."""
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    from oracle import ref
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        count, lr, mom = 1003, 0.05, 0.9
+        rng = np.random.default_rng(7)
+        p0 = rng.standard_normal(count).astype(np.float32)                    # identical replicas
+        grads = [rng.standard_normal(count).astype(np.float32) for _ in range(world)]   # rank r computed grads[r]
+        vel_full = np.zeros(count, np.float32)
+        p_ref = p0.copy()
+        p_mine, v_mine = p0.copy(), np.zeros(count, np.float32)              # v_mine: only the own shard is ever touched
+        scale = np.float32(1.0 / world)
+        for step in range(3):
+            # reference: sum in rank order, scaled, one SGD step over everything (the all-reduce + SGD form)
+            total = grads[0].copy()
+            for g in grads[1:]:
+                total = total + g
+            ref.sgd_step(p_ref, total * scale, vel_full, lr, mom)
+            # sharded: gather every rank's copy of MY shard (the peer loads), sum in rank order, update my shard
+            lo, hi = optimizer_shard(count, rank, world)
+            mine = torch.from_numpy(grads[rank].copy())
+            copies = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(copies, mine)
+            s = copies[0].numpy()[lo:hi].copy()
+            for c in copies[1:]:
+                s = s + c.numpy()[lo:hi]
+            shard_p, shard_v = p_mine[lo:hi].copy(), v_mine[lo:hi].copy()
+            ref.sgd_step(shard_p, s * scale, shard_v, lr, mom)
+            v_mine[lo:hi] = shard_v
+            # the push of the updated parameters: every rank receives every shard
+            padded = np.zeros(count, np.float32)
+            padded[lo:hi] = shard_p
+            t = torch.from_numpy(padded)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)                          # disjoint shards: the sum is the gather
+            p_mine = t.numpy().copy()
+            grads = [g * np.float32(0.5) + np.float32(0.1) for g in grads]    # next step's gradients
+        # the checkpoint's gather of the sharded momentum
+        tv = torch.from_numpy(v_mine.copy())
+        dist.all_reduce(tv, op=dist.ReduceOp.SUM)
+        np.save(os.path.join(out_dir, f"sh{rank}.npy"),
+                np.array([float(np.array_equal(p_mine, p_ref)), float(np.array_equal(tv.numpy(), vel_full)),
+                          float(np.count_nonzero(np.delete(v_mine, np.arange(lo, hi))))]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_optimiser_equals_allreduce_then_sgd(tmp_path):
+    world = 2
+    mp.spawn(_sharded_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        same_params, same_velocity, stray = np.load(tmp_path / f"sh{r}.npy")
+        assert same_params == 1.0 and same_velocity == 1.0 and stray == 0.0
